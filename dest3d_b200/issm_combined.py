@@ -1,0 +1,237 @@
+"""ISSM chunked scan: the reference's Python interface on top of the B200 C ABI.
+
+Mirrors `issm_triton/issm_combined.py:16-54` of the reference: `ISSM_chunk_scan_combined` has the
+same positional/keyword arguments, return convention and gradient dtypes, so
+`models/dest_module.py:600-611` can call it unchanged.  Two keyword-only extensions:
+`reverse=True` scans from the last point to the first without flipped copies (what
+models/dest_module.py:567-573 does with four torch.flip calls), and `path` selects the kernels
+("auto", "simt", "tensor").
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+
+_PATHS = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tensor": _lib.PATH_TENSOR}
+
+
+def _row_major_last(t):
+    """Kernels need a unit stride in the last dimension (the reference has the same rule,
+    issm_combined.py:72-81)."""
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus, dt_limit,
+                 reverse, path):
+    """Validate like the reference (issm_combined.py:58-82) and build the parameter struct.
+    Returns (params, keepalive list)."""
+    if not x.is_cuda:
+        raise RuntimeError("ISSM_chunk_scan_combined runs on CUDA tensors only; there is no CPU path")
+    batch, seqlen, nheads, headdim = x.shape
+    _, _, ngroups, dstate = B.shape
+    assert nheads % ngroups == 0
+    assert B.shape == (batch, seqlen, ngroups, dstate)
+    assert dt.shape == (batch, seqlen, nheads, dstate)
+    assert A.shape == (nheads, dstate)
+    assert C.shape == B.shape
+    if z is not None:
+        assert z.shape == x.shape
+    if D is not None:
+        assert D.shape == (nheads, headdim) or D.shape == (nheads,)
+    if initial_states is not None:
+        assert initial_states.shape == (batch, nheads, headdim, dstate)
+    io = x.dtype
+    keep = []
+
+    def act(t):
+        t = _row_major_last(t if t.dtype == io else t.to(io))
+        keep.append(t)
+        return t
+
+    def par(t):
+        t = t.detach().to(torch.float32).contiguous()
+        keep.append(t)
+        return t
+
+    xk, Bk, Ck = act(x), act(B), act(C)
+    zk = act(z) if z is not None else None
+    dtk = _row_major_last(dt if dt.dtype in (torch.float32, torch.bfloat16) else dt.float())
+    keep.append(dtk)
+    Ak = par(A)
+    Dk = par(D) if D is not None else None
+    if dt_bias is not None:
+        bias = dt_bias if dt_bias.dim() == 2 else dt_bias[:, None].expand(nheads, dstate)
+        assert bias.shape == (nheads, dstate)
+        bk = par(bias)
+    else:
+        bk = None
+    ik = None
+    if initial_states is not None:
+        ik = initial_states.to(io).contiguous()
+        keep.append(ik)
+
+    p = _lib.IssmParams()
+    p.batch, p.seqlen, p.nheads, p.headdim, p.dstate, p.ngroups, p.chunk_size = batch, seqlen, nheads, headdim, dstate, ngroups, int(chunk_size)
+    p.io_dtype, p.dt_dtype = _lib.dtype_code(io), _lib.dtype_code(dtk.dtype)
+    p.path = _PATHS[path]
+    p.has_D, p.D_has_hdim = int(D is not None), int(D is not None and D.dim() == 2)
+    p.has_z, p.has_dt_bias, p.dt_softplus = int(z is not None), int(dt_bias is not None), int(bool(dt_softplus))
+    p.has_init, p.reverse = int(initial_states is not None), int(bool(reverse))
+    p.dt_min, p.dt_max = float(dt_limit[0]), float(min(dt_limit[1], 3.0e38))
+    p.x, p.x_sb, p.x_sl, p.x_sh = xk.data_ptr(), xk.stride(0), xk.stride(1), xk.stride(2)
+    p.dt, p.dt_sb, p.dt_sl, p.dt_sh = dtk.data_ptr(), dtk.stride(0), dtk.stride(1), dtk.stride(2)
+    p.B, p.B_sb, p.B_sl, p.B_sg = Bk.data_ptr(), Bk.stride(0), Bk.stride(1), Bk.stride(2)
+    p.C, p.C_sb, p.C_sl, p.C_sg = Ck.data_ptr(), Ck.stride(0), Ck.stride(1), Ck.stride(2)
+    if zk is not None:
+        p.z, p.z_sb, p.z_sl, p.z_sh = zk.data_ptr(), zk.stride(0), zk.stride(1), zk.stride(2)
+    p.A, p.D, p.dt_bias, p.initial_states = Ak.data_ptr(), _lib.ptr(Dk), _lib.ptr(bk), _lib.ptr(ik)
+    return p, keep
+
+
+def _workspace(p, pass_, device, keep):
+    need = _lib.lib().issm_b200_workspace_bytes(C.byref(p), pass_)
+    ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=device)
+    keep.append(ws)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+
+
+def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
+             dt_softplus=False, dt_limit=(0.0, float("inf")), reverse=False, path="auto",
+             want_final=True):
+    """Forward only (no autograd).  Returns (out, out_x or None, final_states or None);
+    counterpart of `_issm_chunk_scan_combined_fwd` (issm_combined.py:57-92)."""
+    p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
+                           dt_limit, reverse, path)
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    out_x = torch.empty_like(out) if z is not None else None
+    final = torch.empty(x.shape[0], x.shape[2], x.shape[3], B.shape[-1], dtype=torch.float32, device=x.device) if want_final else None
+    p.out, p.out_sb, p.out_sl, p.out_sh = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    p.out_x, p.final_states, p.want_final = _lib.ptr(out_x), _lib.ptr(final), int(want_final)
+    _workspace(p, 0, x.device, keep)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().issm_b200_fwd(C.byref(p), _lib.stream_ptr(x.device))
+    if rc:
+        raise _lib.IssmError(rc, "issm_b200_fwd")
+    return out, out_x, final
+
+
+def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=None,
+             initial_states=None, dfinal_states=None, dt_softplus=False,
+             dt_limit=(0.0, float("inf")), reverse=False, path="auto"):
+    """Backward; counterpart of `_issm_chunk_scan_combined_bwd` (issm_combined.py:95-179).
+    `out_x` is the pre-gate output saved by the forward (only read when z is given).
+    Returns (dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinitial_states) with the reference's dtypes;
+    dA / dD / ddt_bias are float32 here and cast by the caller."""
+    p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
+                           dt_limit, reverse, path)
+    dev = x.device
+    io = x.dtype
+    doutk = _row_major_last(dout if dout.dtype == io else dout.to(io))
+    keep.append(doutk)
+    H, N = A.shape
+    dx = torch.empty(x.shape, dtype=io, device=dev)
+    ddt = torch.empty(dt.shape, dtype=torch.float32 if p.dt_dtype == _lib.F32 else torch.bfloat16, device=dev)
+    dB = torch.empty(B.shape, dtype=io, device=dev)
+    dC = torch.empty(C.shape, dtype=io, device=dev)
+    dz = torch.empty(x.shape, dtype=io, device=dev) if z is not None else None
+    dA = torch.empty(H, N, dtype=torch.float32, device=dev)
+    dbias = torch.empty(H, N, dtype=torch.float32, device=dev) if dt_bias is not None else None
+    dD = torch.empty(D.shape, dtype=torch.float32, device=dev) if D is not None else None
+    dinit = torch.empty(initial_states.shape, dtype=io, device=dev) if initial_states is not None else None
+    if z is not None:
+        # out_x was allocated contiguous by the forward
+        assert out_x is not None and out_x.is_contiguous()
+        p.out_x = out_x.data_ptr()
+        p.out_sb, p.out_sl, p.out_sh = out_x.stride(0), out_x.stride(1), out_x.stride(2)
+    p.dout, p.dout_sb, p.dout_sl, p.dout_sh = doutk.data_ptr(), doutk.stride(0), doutk.stride(1), doutk.stride(2)
+    if dfinal_states is not None:
+        dfin = dfinal_states.to(torch.float32).contiguous()
+        keep.append(dfin)
+        p.has_dfinal, p.dfinal_states = 1, dfin.data_ptr()
+    p.dx, p.ddt, p.dB, p.dC, p.dz = dx.data_ptr(), ddt.data_ptr(), dB.data_ptr(), dC.data_ptr(), _lib.ptr(dz)
+    p.dA, p.ddt_bias, p.dD, p.dinitial_states = dA.data_ptr(), _lib.ptr(dbias), _lib.ptr(dD), _lib.ptr(dinit)
+    _workspace(p, 1, dev, keep)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().issm_b200_bwd(C.byref(p), _lib.stream_ptr(dev))
+    if rc:
+        raise _lib.IssmError(rc, "issm_b200_bwd")
+    return dx, ddt, dA, dB, dC, dD, dz, dbias, dinit
+
+
+class ISSMChunkScanCombinedFn(torch.autograd.Function):
+    """autograd entry, same saved-tensor and return conventions as the reference
+    (issm_combined.py:37-54); two trailing extras (reverse, path) receive no gradient."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
+                seq_idx=None, dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False,
+                reverse=False, path="auto"):
+        if seq_idx is not None:
+            raise NotImplementedError("seq_idx (packed variable-length batches) is not supported")
+        out, out_x, final = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states,
+                                     dt_softplus, dt_limit, reverse, path, want_final=return_final_states)
+        ctx.save_for_backward(out_x, x, dt, A, B, C, D, z, dt_bias, initial_states)
+        ctx.opts = (chunk_size, dt_softplus, dt_limit, return_final_states, reverse, path)
+        return out if not return_final_states else (out, final)
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        out_x, x, dt, A, B, C, D, z, dt_bias, initial_states = ctx.saved_tensors
+        chunk_size, dt_softplus, dt_limit, return_final_states, reverse, path = ctx.opts
+        dfinal = args[0] if return_final_states and len(args) and args[0] is not None else None
+        dx, ddt, dA, dB, dC, dD, dz, dbias, dinit = issm_bwd(
+            dout, x, dt, A, B, C, out_x, chunk_size, D, z, dt_bias, initial_states, dfinal,
+            dt_softplus, dt_limit, reverse, path)
+        ddt = ddt if ddt.dtype == dt.dtype else ddt.to(dt.dtype)
+        dA = dA.to(A.dtype)
+        dB = dB if dB.dtype == B.dtype else dB.to(B.dtype)
+        dC = dC if dC.dtype == C.dtype else dC.to(C.dtype)
+        if dD is not None:
+            dD = dD.to(D.dtype)
+        if dz is not None and dz.dtype != z.dtype:
+            dz = dz.to(z.dtype)
+        if dbias is not None:
+            dbias = (dbias if dt_bias.dim() == 2 else dbias.sum(dim=1)).to(dt_bias.dtype)
+        if dinit is not None and dinit.dtype != initial_states.dtype:
+            dinit = dinit.to(initial_states.dtype)
+        return dx, ddt, dA, dB, dC, None, dD, dz, dbias, dinit, None, None, None, None, None, None
+
+
+def ISSM_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
+                             seq_idx=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
+                             return_final_states=False, *, reverse=False, path="auto"):
+    """
+    Argument:
+        x: (batch, seqlen, nheads, headdim)
+        dt: (batch, seqlen, nheads, dstate)
+        A: (nheads, dstate)
+        B: (batch, seqlen, ngroups, dstate)
+        C: (batch, seqlen, ngroups, dstate)
+        chunk_size: int (<= 256)
+        D: (nheads, headdim) or (nheads,)
+        z: (batch, seqlen, nheads, headdim)
+        dt_bias: (nheads, dstate) or (nheads,)
+        initial_states: (batch, nheads, headdim, dstate)
+        seq_idx: must be None
+        dt_softplus: Whether to apply softplus to dt
+    Return:
+        out: (batch, seqlen, nheads, headdim), or (out, final_states (batch, nheads, headdim, dstate) fp32)
+    """
+    return ISSMChunkScanCombinedFn.apply(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx,
+                                         dt_softplus, dt_limit, return_final_states, reverse, path)
+
+
+def issm_bidirectional_scan(x, x_back, dt, A, B, C, B_back, C_back, chunk_size, D=None, z=None, dt_bias=None,
+                            initial_states=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
+                            out_scale=0.5, path="auto"):
+    """Forward scan of (x, B, C) plus reversed scan of (x_back, B_back, C_back) over the SAME dt, A, D,
+    initial states, combined as out_scale * (fwd + bwd): the bidirectional block of
+    models/dest_module.py:565-575 (which averages, out_scale = 0.5) without the flipped copies.
+    All `_back` tensors are in natural point order.  Returns (out, final_states)."""
+    yf, sf = ISSM_chunk_scan_combined(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, None,
+                                      dt_softplus, dt_limit, True, reverse=False, path=path)
+    yb, sb = ISSM_chunk_scan_combined(x_back, dt, A, B_back, C_back, chunk_size, D, z, dt_bias, initial_states,
+                                      None, dt_softplus, dt_limit, True, reverse=True, path=path)
+    return (yf + yb) * out_scale, (sf + sb) * out_scale

@@ -1,0 +1,150 @@
+/* issm_b200.h - C ABI of the B200-native ISSM chunked scan and gated norms.
+ *
+ * Every entry point takes plain device pointers, element strides and sizes; no torch types.
+ * The library never allocates, frees or synchronises (except where an entry point says so):
+ * the caller owns every buffer, including the workspace, and all work is enqueued on the
+ * stream handed in.  Host-detectable problems (bad shapes, unsupported dtype, workspace too
+ * small, null pointers) are reported through the int return code before anything is launched;
+ * use issm_b200_strerror() for a message.  Device-side problems (a bounded wait that expired)
+ * are written to the optional `status` word and never trap.
+ *
+ * Reference interfaces these entry points replace (paths inside the reference project):
+ *   issm_triton/issm_combined.py:57-92    _issm_chunk_scan_combined_fwd   -> issm_b200_fwd
+ *   issm_triton/issm_combined.py:95-179   _issm_chunk_scan_combined_bwd   -> issm_b200_bwd
+ *   issm_triton/layernorm_gated.py:98-137 _layer_norm_fwd                 -> issm_b200_norm_fwd
+ *   issm_triton/layernorm_gated.py:261-325 _layer_norm_bwd                -> issm_b200_norm_bwd
+ */
+#ifndef ISSM_B200_H_
+#define ISSM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ISSM_B200_VERSION 1
+
+/* element types of the activation tensors */
+enum { ISSM_F32 = 0, ISSM_BF16 = 1 };
+
+/* which kernels serve a call */
+enum {
+  ISSM_PATH_AUTO = 0,    /* bf16 activations + supported shape -> tensor-core path, else SIMT   */
+  ISSM_PATH_SIMT = 1,    /* fp32-arithmetic SIMT kernels, any supported shape, any value range  */
+  ISSM_PATH_TENSOR = 2   /* tcgen05 path; returns ISSM_ERR_UNSUPPORTED if the shape has none    */
+};
+
+/* return codes */
+enum {
+  ISSM_OK = 0,
+  ISSM_ERR_NULL = 1,          /* a required pointer is null                     */
+  ISSM_ERR_SHAPE = 2,         /* sizes out of the supported range               */
+  ISSM_ERR_DTYPE = 3,         /* unknown dtype enum                             */
+  ISSM_ERR_WORKSPACE = 4,     /* workspace missing or smaller than required     */
+  ISSM_ERR_ALIGN = 5,         /* pointer or stride alignment not met            */
+  ISSM_ERR_UNSUPPORTED = 6,   /* requested path does not cover this shape       */
+  ISSM_ERR_CUDA = 7,          /* a CUDA runtime call failed (launch, attribute) */
+  ISSM_ERR_DEVICE_STATUS = 8  /* reserved: device status word was non-zero      */
+};
+
+/* One ISSM scan call (forward, or forward-recompute + backward).
+ *
+ * Shapes (reference: issm_triton/issm_combined.py:16-35).  All strides are in ELEMENTS; the
+ * innermost dimension of every tensor is contiguous.
+ *   x, z, out, out_x, dout, dx, dz : (batch, seqlen, nheads, headdim)   dtype io_dtype
+ *   dt, ddt                        : (batch, seqlen, nheads, dstate)    dtype dt_dtype
+ *   B, C, dB, dC                   : (batch, seqlen, ngroups, dstate)   dtype io_dtype
+ *   A, dt_bias, dA, ddt_bias       : (nheads, dstate) float, contiguous
+ *   D, dD                          : (nheads) or (nheads, headdim) float, contiguous
+ *   initial_states, dinitial_states: (batch, nheads, headdim, dstate)   dtype io_dtype, contiguous
+ *   final_states, dfinal_states    : (batch, nheads, headdim, dstate)   float, contiguous
+ * `reverse` scans from the last point to the first (equal to flipping x, dt, B, C, z along
+ * seqlen, scanning, flipping out back: models/dest_module.py:567-573) without any copy.
+ */
+typedef struct issm_params {
+  int32_t batch, seqlen, nheads, headdim, dstate, ngroups, chunk_size;
+  int32_t io_dtype, dt_dtype;
+  int32_t path;                 /* ISSM_PATH_* */
+  int32_t has_D, D_has_hdim, has_z, has_dt_bias, dt_softplus;
+  int32_t has_init, has_dfinal, reverse, want_final;
+  float dt_min, dt_max;         /* clamp applied after bias/softplus (issm_chunk_state.py:97) */
+
+  const void* x;   int64_t x_sb, x_sl, x_sh;
+  const void* dt;  int64_t dt_sb, dt_sl, dt_sh;
+  const void* B;   int64_t B_sb, B_sl, B_sg;
+  const void* C;   int64_t C_sb, C_sl, C_sg;
+  const void* z;   int64_t z_sb, z_sl, z_sh;
+  const float* A;
+  const float* D;
+  const float* dt_bias;
+  const void* initial_states;
+
+  /* forward outputs */
+  void* out;       int64_t out_sb, out_sl, out_sh;
+  void* out_x;     /* pre-gate y, same strides as out; required when has_z (saved for bwd) */
+  float* final_states;          /* required when want_final */
+
+  /* backward inputs */
+  const void* dout; int64_t dout_sb, dout_sl, dout_sh;
+  const float* dfinal_states;
+  /* backward outputs (contiguous, same shapes as the matching inputs) */
+  void* dx; void* ddt; void* dB; void* dC; void* dz;
+  float* dA; float* ddt_bias; float* dD;
+  void* dinitial_states;        /* optional */
+
+  void* workspace; size_t workspace_bytes;
+  int32_t* status;              /* optional device word, written only on a device-side error */
+} issm_params;
+
+/* Gated RMS / Layer norm over the last dimension of a (rows, hidden) matrix
+ * (issm_triton/layernorm_gated.py:35-95): y = norm(x) * silu(z) if norm_before_gate,
+ * else norm(x * silu(z)); statistics per group of group_size features. */
+typedef struct issm_norm_params {
+  int32_t rows, hidden, group_size;   /* group_size divides hidden */
+  int32_t io_dtype;                   /* x, z, y, dy, dx, dz */
+  int32_t is_rms, norm_before_gate, has_z, has_bias;
+  float eps;
+  const void* x; int64_t x_sr;        /* row strides in elements */
+  const void* z; int64_t z_sr;
+  const float* weight; const float* bias;
+  void* y; int64_t y_sr;
+  float* rstd;                        /* (rows * hidden/group_size) */
+  float* mean;                        /* same size; LayerNorm only */
+  /* backward */
+  const void* dy; int64_t dy_sr;
+  void* dx; void* dz;                 /* contiguous (rows, hidden) */
+  float* dweight; float* dbias;       /* (hidden) */
+  void* workspace; size_t workspace_bytes;
+} issm_norm_params;
+
+int issm_b200_version(void);
+const char* issm_b200_strerror(int code);
+/* sizeof(issm_params) / sizeof(issm_norm_params) as compiled, so a foreign-language binding can
+ * check its own struct declaration against the library's. */
+size_t issm_b200_sizeof_params(void);
+size_t issm_b200_sizeof_norm_params(void);
+
+/* Bytes of workspace issm_b200_fwd (pass = 0) or issm_b200_bwd (pass = 1) needs for these
+ * sizes, dtypes, flags and path; pointers in *p are ignored.  Returns 0 on invalid sizes. */
+size_t issm_b200_workspace_bytes(const issm_params* p, int pass);
+
+/* Which path (ISSM_PATH_SIMT or ISSM_PATH_TENSOR) a call with these sizes would take. */
+int issm_b200_resolve_path(const issm_params* p);
+
+int issm_b200_fwd(const issm_params* p, void* cuda_stream);
+int issm_b200_bwd(const issm_params* p, void* cuda_stream);
+
+size_t issm_b200_norm_workspace_bytes(const issm_norm_params* p, int pass);
+int issm_b200_norm_fwd(const issm_norm_params* p, void* cuda_stream);
+int issm_b200_norm_bwd(const issm_norm_params* p, void* cuda_stream);
+
+/* Number of kernel launches the library has enqueued since load (monotonic, process-wide);
+ * used by the benchmark to report how many of its own kernels ran inside a timed region. */
+uint64_t issm_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ISSM_B200_H_ */

@@ -1,0 +1,94 @@
+"""The C-ABI library builds, loads and exports every symbol the header declares; host-side
+argument validation works without a device (no compute call is made here)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if fn.endswith(".h"):
+            src = open(os.path.join(ROOT, "include", fn)).read()
+            src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+            names += re.findall(r"\b(issm_b200_\w+)\s*\(", src)
+    return sorted(set(names))
+
+
+def test_header_symbols_exported(built_lib):
+    names = declared_functions()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(built_lib, n), f"{n} declared in include/ but not exported by libissm_b200.so"
+
+
+def test_struct_layout_matches(built_lib):
+    from dest3d_b200 import _lib
+    assert built_lib.issm_b200_sizeof_params() == C.sizeof(_lib.IssmParams)
+    assert built_lib.issm_b200_sizeof_norm_params() == C.sizeof(_lib.IssmNormParams)
+    assert built_lib.issm_b200_version() == 1
+
+
+def _params(**over):
+    from dest3d_b200 import _lib
+    p = _lib.IssmParams()
+    p.batch, p.seqlen, p.nheads, p.headdim, p.dstate, p.ngroups, p.chunk_size = 2, 100, 4, 36, 64, 1, 64
+    p.io_dtype, p.dt_dtype, p.path = _lib.F32, _lib.F32, _lib.PATH_SIMT
+    p.dt_min, p.dt_max = 0.0, 3e38
+    for k, v in over.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_validation_codes_without_device(built_lib):
+    L = built_lib
+    assert L.issm_b200_fwd(None, None) == 1                                   # ISSM_ERR_NULL
+    assert L.issm_b200_fwd(C.byref(_params(seqlen=0)), None) == 2             # ISSM_ERR_SHAPE
+    assert L.issm_b200_fwd(C.byref(_params(ngroups=3)), None) == 2
+    assert L.issm_b200_fwd(C.byref(_params(chunk_size=512)), None) == 2
+    assert L.issm_b200_fwd(C.byref(_params(io_dtype=7)), None) == 3           # ISSM_ERR_DTYPE
+    assert L.issm_b200_fwd(C.byref(_params()), None) == 1                     # pointers are null
+    assert L.issm_b200_bwd(C.byref(_params()), None) == 1
+    assert b"workspace" in L.issm_b200_strerror(4)
+
+
+def test_workspace_query(built_lib):
+    L = built_lib
+    fwd = L.issm_b200_workspace_bytes(C.byref(_params()), 0)
+    bwd = L.issm_b200_workspace_bytes(C.byref(_params()), 1)
+    assert 0 < fwd < bwd
+    assert fwd % 256 == 0
+    assert L.issm_b200_workspace_bytes(C.byref(_params(seqlen=-1)), 0) == 0
+    # fp32 activations never take the tensor-core path
+    assert L.issm_b200_resolve_path(C.byref(_params(path=0))) == 1
+
+
+def test_workspace_too_small_is_reported(built_lib):
+    """Pointers set to a dummy non-null value; the call must stop at the workspace check,
+    before anything would be launched."""
+    L = built_lib
+    p = _params()
+    for f in ("x", "dt", "A", "B", "C", "out"):
+        setattr(p, f, 256)
+    p.workspace, p.workspace_bytes = 256, 16
+    assert L.issm_b200_fwd(C.byref(p), None) == 4                             # ISSM_ERR_WORKSPACE
+
+
+def test_norm_validation(built_lib):
+    from dest3d_b200 import _lib
+    p = _lib.IssmNormParams()
+    p.rows, p.hidden, p.group_size = 4, 288, 100
+    assert built_lib.issm_b200_norm_fwd(C.byref(p), None) == 2                # group does not divide hidden
+    p.group_size = 288
+    assert built_lib.issm_b200_norm_fwd(C.byref(p), None) == 1                # null pointers
+
+
+def test_operators_refuse_cpu_tensors(built_lib):
+    import torch
+    from dest3d_b200 import RMSNorm
+    with pytest.raises(RuntimeError):
+        RMSNorm(16)(torch.randn(2, 16))

@@ -1,0 +1,115 @@
+"""GPU parity of the ISSM scan (through the public interface -> C ABI) against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import issm_oracle as O
+from tests import parity
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+BENCH_OPTS = dict(dt_softplus=True, dt_limit=(1e-3, 1e-1))
+
+# (id, (b, L, H, P, N, G, Q), make_inputs kwargs, opts)
+CASES = [
+    ("tiny_ragged", (1, 257, 1, 4, 16, 1, 16), {}, BENCH_OPTS),
+    ("odd_heads", (2, 96, 3, 5, 8, 1, 32), {}, BENCH_OPTS),
+    ("short_L_lt_Q", (1, 100, 2, 36, 64, 1, 256), {}, BENCH_OPTS),
+    ("tail64", (1, 576, 2, 36, 256, 1, 256), {}, BENCH_OPTS),
+    ("c2_like", (1, 384, 2, 36, 512, 1, 128), {}, BENCH_OPTS),
+    ("groups2", (2, 80, 4, 8, 32, 2, 32), {}, BENCH_OPTS),
+    ("D_hdim", (1, 64, 2, 12, 32, 1, 32), dict(D_has_hdim=True), BENCH_OPTS),
+    ("no_z_no_D", (1, 96, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, use_z=False, use_D=False)),
+    ("dest_call", (2, 300, 8, 36, 256, 1, 256), {}, dict(use_z=False, use_dt_bias=False, dt_pre=True)),
+    ("no_init_no_final", (1, 128, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, use_initial_states=False, return_final=False, dfinal=False)),
+    ("final_no_dfinal", (1, 128, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, dfinal=False)),
+    ("reverse", (2, 200, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, reverse=True)),
+    ("reverse_tail", (1, 576, 2, 36, 256, 1, 256), {}, dict(BENCH_OPTS, reverse=True)),
+    ("noncontig", (1, 128, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, noncontig=True)),
+    ("unbounded_dt", (1, 128, 2, 36, 64, 1, 64), {}, dict(dt_softplus=True, dt_scale=5.0)),
+    ("L1", (1, 1, 2, 36, 64, 1, 64), {}, BENCH_OPTS),
+]
+
+
+def _inputs(shape, mk, opts, dtype):
+    b, L, H, P, N, G, Q = shape
+    inp = O.make_inputs(b, L, H, P, N, G=G, seed=hash(shape) % 1000, dtype=dtype, **mk)
+    if opts.get("dt_pre"):
+        # the detector's call: dt already softplus'ed (fp32), no bias, no in-kernel transform
+        inp["dt"] = torch.nn.functional.softplus(inp["dt"].float() - 4.0)
+    if opts.get("dt_scale"):
+        inp["dt"] = (inp["dt"].float() * opts["dt_scale"] + 4.0).to(dtype)   # softplus(dt - 4 + ...) reaches ~10
+    return inp, Q
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_parity_simt(case, dtype):
+    _, shape, mk, opts = case
+    inp, Q = _inputs(shape, mk, opts, dtype)
+    ref = parity.oracle_run(inp, Q, opts)
+    got = parity.cuda_run(inp, Q, opts, path="simt")
+    parity.compare(got, ref, dtype, want_final=opts.get("return_final", True))
+
+
+@pytest.mark.parametrize("name", ["tiny_f64", "ragged_heads_f64", "reftest_f32"])
+def test_golden_reference_vectors(name):
+    """Outputs and gradients produced by the reference's own pure-PyTorch scan (tests/golden)."""
+    from tests.golden.make_golden import SUB, case_inputs
+    g = np.load(os.path.join(GOLD, f"issm_{name}.npz"))
+    b, L, H, P, N, Q, seed = (int(v) for v in g["shape"])
+    inp = case_inputs(b, L, H, P, N, seed, torch.float64 if name.endswith("f64") else torch.float32)
+    chk = float(sum(inp[k].double().sum() for k in ("x", "B", "C", "dt", "A", "init")))
+    assert abs(chk - float(g["input_checksum"][0])) < 1e-6 * max(1.0, abs(chk)), "input generator drifted"
+    from dest3d_b200 import ISSM_chunk_scan_combined
+    leaves = {k: inp[k].float().cuda().requires_grad_() for k in ("x", "dt", "A", "B", "C", "init")}
+    y, fin = ISSM_chunk_scan_combined(leaves["x"], leaves["dt"], leaves["A"], leaves["B"], leaves["C"], Q,
+                                      initial_states=leaves["init"], return_final_states=True, path="simt")
+    ((y * inp["w"].float().cuda()).sum() + (fin * inp["wf"].float().cuda()).sum()).backward()
+    parity.close(y, torch.from_numpy(g["y"]), torch.float32, "out")
+    parity.close(fin, torch.from_numpy(g["final"]), torch.float32, "final")
+    for k in leaves:
+        ref = torch.from_numpy(g["d" + k])
+        got = leaves[k].grad.cpu()
+        if ref.dim() == 1 and got.dim() > 1:
+            got = got.reshape(-1)[::SUB]
+        parity.close(got, ref, torch.float32, "d" + k)
+
+
+def test_deterministic_bitwise():
+    """Two runs on the same inputs give bit-identical outputs and gradients (no atomics)."""
+    inp, Q = _inputs((2, 300, 4, 36, 64, 1, 64), {}, BENCH_OPTS, torch.float32)
+    a = parity.cuda_run(inp, Q, BENCH_OPTS, path="simt")
+    b = parity.cuda_run(inp, Q, BENCH_OPTS, path="simt")
+    for k in a:
+        if a[k] is not None:
+            assert torch.equal(a[k], b[k]), k
+
+
+def test_reverse_equals_flip():
+    """reverse=True equals flip -> scan -> flip (models/dest_module.py:567-573), bit for bit."""
+    from dest3d_b200 import ISSM_chunk_scan_combined
+    inp, Q = _inputs((2, 200, 2, 36, 64, 1, 64), {}, BENCH_OPTS, torch.float32)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    fl = lambda t: torch.flip(t, dims=[1]).contiguous()
+    kw = dict(D=c["D"], z=c["z"], dt_bias=c["dt_bias"], initial_states=c["initial_states"], dt_softplus=True,
+              dt_limit=(1e-3, 1e-1), return_final_states=True, path="simt")
+    y1, f1 = ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, reverse=True, **kw)
+    kw["z"] = fl(c["z"])
+    y2, f2 = ISSM_chunk_scan_combined(fl(c["x"]), fl(c["dt"]), c["A"], fl(c["B"]), fl(c["C"]), Q, **kw)
+    assert torch.equal(y1, torch.flip(y2, dims=[1])) and torch.equal(f1, f2)
+
+
+def test_bad_arguments_raise():
+    from dest3d_b200 import ISSM_chunk_scan_combined, _lib
+    inp, Q = _inputs((1, 64, 2, 8, 16, 1, 16), {}, BENCH_OPTS, torch.float32)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    with pytest.raises(_lib.IssmError):
+        ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], 512)          # chunk_size > 256
+    with pytest.raises(NotImplementedError):
+        ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, seq_idx=torch.zeros(1, 64, dtype=torch.int32))
+    with pytest.raises(RuntimeError):
+        ISSM_chunk_scan_combined(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], Q)  # CPU tensors

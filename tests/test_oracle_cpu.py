@@ -1,0 +1,86 @@
+"""CPU checks of the oracle itself: against the golden vectors produced by the reference's own
+code, between its two formulations, and of the features restated on top (D, z, dt transform,
+tail padding, reverse, groups)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import issm_oracle as O
+from tests.golden.make_golden import SUB, case_inputs
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.mark.parametrize("name", ["tiny_f64", "ragged_heads_f64", "reftest_f32"])
+def test_oracle_matches_reference_golden(name):
+    g = np.load(os.path.join(GOLD, f"issm_{name}.npz"))
+    b, L, H, P, N, Q, seed = (int(v) for v in g["shape"])
+    f64 = name.endswith("f64")
+    dtype = torch.float64 if f64 else torch.float32
+    inp = case_inputs(b, L, H, P, N, seed, dtype)
+    chk = float(sum(inp[k].double().sum() for k in ("x", "B", "C", "dt", "A", "init")))
+    assert abs(chk - float(g["input_checksum"][0])) < 1e-6 * max(1.0, abs(chk))
+    leaves = {k: inp[k].clone().requires_grad_() for k in ("x", "dt", "A", "B", "C", "init")}
+    y, fin = O.issm_scan_chunked(leaves["x"], leaves["dt"], leaves["A"], leaves["B"], leaves["C"], Q,
+                                 initial_states=leaves["init"], compute_dtype=dtype)
+    ((y * inp["w"]).sum() + (fin.to(dtype) * inp["wf"]).sum()).backward()
+    tol = dict(rtol=1e-5, atol=1e-6) if f64 else dict(rtol=1e-4, atol=1e-5)
+    assert torch.allclose(y.float(), torch.from_numpy(g["y"]), **tol)
+    assert torch.allclose(fin.float(), torch.from_numpy(g["final"]), **tol)
+    for k in leaves:
+        ref = torch.from_numpy(g["d" + k])
+        got = leaves[k].grad.float()
+        if ref.dim() == 1 and got.dim() > 1:
+            got = got.reshape(-1)[::SUB]
+        scale = max(1.0, ref.abs().max().item())
+        assert torch.allclose(got / scale, ref / scale, rtol=tol["rtol"] * 10, atol=tol["atol"] * 10), k
+
+
+def test_rmsnorm_oracle_matches_reference_golden():
+    g = np.load(os.path.join(GOLD, "rmsnorm_gated.npz"))
+    x, z, w = (torch.from_numpy(g[k]) for k in ("x", "z", "w"))
+    for nbg in (False, True):
+        for gs in (None, 36):
+            for use_z in (True, False):
+                key = f"nbg{int(nbg)}_gs{gs or 0}_z{int(use_z)}"
+                y = O.gated_norm_ref(x, w, None, z if use_z else None, eps=1e-5, group_size=gs, norm_before_gate=nbg)
+                assert torch.allclose(y, torch.from_numpy(g["y_" + key]), rtol=1e-5, atol=1e-6), key
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+def test_chunked_equals_recurrence_with_all_features(reverse):
+    inp = O.make_inputs(2, 75, 4, 6, 12, G=2, seed=3, dtype=torch.float64, D_has_hdim=True)
+    kw = dict(D=inp["D"], z=inp["z"], dt_bias=inp["dt_bias"], initial_states=inp["initial_states"],
+              dt_softplus=True, dt_limit=(1e-3, 1e-1), reverse=reverse, compute_dtype=torch.float64)
+    y1, f1 = O.issm_scan_chunked(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 16, **kw)
+    y2, f2 = O.issm_scan_sequential(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], None, **kw)
+    assert torch.allclose(y1, y2, rtol=1e-10, atol=1e-12) and torch.allclose(f1, f2, rtol=1e-10, atol=1e-12)
+    # chunk size must not matter
+    y3, f3 = O.issm_scan_chunked(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 64, **kw)
+    assert torch.allclose(y1, y3, rtol=1e-10, atol=1e-12) and torch.allclose(f1, f3, rtol=1e-10, atol=1e-12)
+
+
+def test_dt_transform_rules():
+    v = torch.tensor([[-30.0, -1.0, 0.0, 5.0, 25.0]]).reshape(1, 5, 1, 1)
+    out = O.dt_transform(v, torch.zeros(1, 1), True, (0.0, float("inf"))).flatten()
+    assert out[4] == 25.0 and torch.allclose(out[2], torch.tensor(0.6931472))
+    out = O.dt_transform(v, None, False, (0.0, float("inf"))).flatten()
+    assert out[0] == 0.0 and out[1] == 0.0 and out[3] == 5.0          # default limits clamp negatives to 0
+    out = O.dt_transform(v, torch.full((1,), 1.0), True, (1e-3, 1e-1)).flatten()
+    assert out.min() >= 1e-3 and out.max() <= 1e-1
+
+
+def test_bidirectional_is_average_of_two_scans():
+    inp = O.make_inputs(1, 40, 2, 4, 8, seed=5, dtype=torch.float64)
+    xb = torch.flip(inp["x"], dims=[2])
+    y, s = O.issm_scan_bidirectional(inp["x"], xb, inp["dt"], inp["A"], inp["B"], inp["C"], inp["C"], inp["B"], 16,
+                                     D=inp["D"], dt_bias=inp["dt_bias"], initial_states=inp["initial_states"],
+                                     dt_softplus=True, dt_limit=(1e-3, 1e-1), compute_dtype=torch.float64)
+    fl = lambda t: torch.flip(t, dims=[1])
+    kw = dict(D=inp["D"], dt_bias=inp["dt_bias"], initial_states=inp["initial_states"], dt_softplus=True,
+              dt_limit=(1e-3, 1e-1), compute_dtype=torch.float64)
+    yf, sf = O.issm_scan_chunked(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 16, **kw)
+    yb, sb = O.issm_scan_chunked(fl(xb), fl(inp["dt"]), inp["A"], fl(inp["C"]), fl(inp["B"]), 16, **kw)
+    assert torch.allclose(y, (yf + fl(yb)) / 2) and torch.allclose(s, (sf + sb) / 2)
