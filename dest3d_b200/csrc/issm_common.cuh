@@ -28,7 +28,7 @@ __device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p
 __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 // softplus with the reference's threshold (issm_triton/softplus.py:9-11)
 __device__ __forceinline__ float softplus_thr(float v) { return v <= 20.0f ? log1pf(expf(v)) : v; }

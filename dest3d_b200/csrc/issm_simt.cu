@@ -154,8 +154,8 @@ __global__ void k_chunk_state(Dims d, const TS* __restrict__ src, int64_t s_sb, 
             const size_t idx = base + (size_t)(r0 + r) * d.N + n;
             const float bcv = ldf(bc + b * bc_sb + (int64_t)mem_row(d, c * d.Q + r0 + r) * bc_sl + g * bc_sg + n);
             float f;
-            if (MODE == 0) f = bcv * dtv[idx] * __expf(alast - acs[idx]);
-            else f = bcv * __expf(acs[idx]);
+            if (MODE == 0) f = bcv * dtv[idx] * expf(alast - acs[idx]);
+            else f = bcv * expf(acs[idx]);
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = fmaf(xs[r][i], f, acc[i]);
           }
@@ -190,7 +190,7 @@ __global__ void k_pass_fwd(Dims d, float* __restrict__ states, const float* __re
     const float local = states[si];
     states[si] = run;
     const float alast = acs[((((size_t)b * d.H + h) * d.nc + c) * d.Q + d.Q - 1) * d.N + n];
-    run = run * __expf(alast) + local;
+    run = run * expf(alast) + local;
   }
   if (final_states) final_states[i] = run;
 }
@@ -211,7 +211,7 @@ __global__ void k_pass_bwd(Dims d, float* __restrict__ dstates, const float* __r
   const size_t gbase = (((size_t)b * d.H + h) * d.P) * d.N + n;
   for (int p = 0; p < d.P; ++p) grun[gbase + (size_t)p * d.N] = dfinal ? dfinal[gbase + (size_t)p * d.N] : 0.f;
   for (int c = d.nc - 1; c >= 0; --c) {
-    const float decay = __expf(acs[((((size_t)b * d.H + h) * d.nc + c) * d.Q + d.Q - 1) * d.N + n]);
+    const float decay = expf(acs[((((size_t)b * d.H + h) * d.nc + c) * d.Q + d.Q - 1) * d.N + n]);
     float acc = 0.f;
     const size_t sbase = ((((size_t)b * d.nc + c) * d.H + h) * d.P) * d.N + n;
     for (int p = 0; p < d.P; ++p) {
@@ -278,7 +278,7 @@ __global__ void k_scan(Dims d,
       const float* ds = dtv + base + (size_t)s * d.N;
       float acc = 0.f;
       for (int n = lane; n < d.N; n += 32)
-        acc = fmaf(ldf(cp + n) * ldf(bp + n) * ds[n], __expf(at[n] - as[n]), acc);
+        acc = fmaf(ldf(cp + n) * ldf(bp + n) * ds[n], expf(at[n] - as[n]), acc);
       acc = warp_sum(acc);
       if (lane == 0) sm[r * ldm + q] = acc;
     }
@@ -303,12 +303,12 @@ __global__ void k_scan(Dims d,
     const float* ar = acs + base + (size_t)row * d.N;
     if (!BWD) {
       const TIO* cp = Cm + b * C_sb + (int64_t)lrow * C_sl + g * C_sg;
-      for (int n = lane; n < d.N; n += 32) acc = fmaf(ldf(cp + n) * __expf(ar[n]), sp[n], acc);
+      for (int n = lane; n < d.N; n += 32) acc = fmaf(ldf(cp + n) * expf(ar[n]), sp[n], acc);
     } else {
       const TIO* bp = Bm + b * B_sb + (int64_t)lrow * B_sl + g * B_sg;
       const float* dr = dtv + base + (size_t)row * d.N;
       for (int n = lane; n < d.N; n += 32)
-        acc = fmaf(ldf(bp + n) * dr[n] * __expf(alastp[n] - ar[n]), sp[n], acc);
+        acc = fmaf(ldf(bp + n) * dr[n] * expf(alastp[n] - ar[n]), sp[n], acc);
     }
     acc = warp_sum(acc);
     if (lane == 0) {
@@ -455,8 +455,8 @@ __global__ void k_main(Dims d,
     const float aj = sA[j * 32 + lane];
     float G2 = 0.f, G1 = 0.f;
     const float* dMrow = dMt + (size_t)j * d.Q;
-    for (int s = 0; s <= j; ++s) G2 = fmaf(dMrow[s] * sBdt[s * 32 + lane], __expf(aj - sA[s * 32 + lane]), G2);
-    for (int t = j; t < rows; ++t) G1 = fmaf(dMt[(size_t)t * d.Q + j] * sC[t * 32 + lane], __expf(sA[t * 32 + lane] - aj), G1);
+    for (int s = 0; s <= j; ++s) G2 = fmaf(dMrow[s] * sBdt[s * 32 + lane], expf(aj - sA[s * 32 + lane]), G2);
+    for (int t = j; t < rows; ++t) G1 = fmaf(dMt[(size_t)t * d.Q + j] * sC[t * 32 + lane], expf(sA[t * 32 + lane] - aj), G1);
     float W = 0.f, V = 0.f;
     const int l = mem_row(d, c * d.Q + j);
     if (act) {
@@ -467,8 +467,8 @@ __global__ void k_main(Dims d,
         V = fmaf(dyr[p], S[sbase + (size_t)p * d.N + n], V);
       }
     }
-    W *= __expf(alast - aj);
-    V *= __expf(aj);
+    W *= expf(alast - aj);
+    V *= expf(aj);
     const float bd = G1 + W, cd = G2 + V;
     const float bdt = sBdt[j * 32 + lane];
     float bv = 0.f, dv = 0.f;

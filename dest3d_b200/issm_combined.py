@@ -7,7 +7,7 @@ same positional/keyword arguments, return convention and gradient dtypes, so
 models/dest_module.py:567-573 does with four torch.flip calls), and `path` selects the kernels
 ("auto", "simt", "tensor").
 """
-import ctypes as C
+import ctypes as ct
 import math
 
 import torch
@@ -91,7 +91,7 @@ def _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_s
 
 
 def _workspace(p, pass_, device, keep):
-    need = _lib.lib().issm_b200_workspace_bytes(C.byref(p), pass_)
+    need = _lib.lib().issm_b200_workspace_bytes(ct.byref(p), pass_)
     ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=device)
     keep.append(ws)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
@@ -111,7 +111,7 @@ def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_s
     p.out_x, p.final_states, p.want_final = _lib.ptr(out_x), _lib.ptr(final), int(want_final)
     _workspace(p, 0, x.device, keep)
     with torch.cuda.device(x.device):
-        rc = _lib.lib().issm_b200_fwd(C.byref(p), _lib.stream_ptr(x.device))
+        rc = _lib.lib().issm_b200_fwd(ct.byref(p), _lib.stream_ptr(x.device))
     if rc:
         raise _lib.IssmError(rc, "issm_b200_fwd")
     return out, out_x, final
@@ -154,7 +154,7 @@ def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=No
     p.dA, p.ddt_bias, p.dD, p.dinitial_states = dA.data_ptr(), _lib.ptr(dbias), _lib.ptr(dD), _lib.ptr(dinit)
     _workspace(p, 1, dev, keep)
     with torch.cuda.device(dev):
-        rc = _lib.lib().issm_b200_bwd(C.byref(p), _lib.stream_ptr(dev))
+        rc = _lib.lib().issm_b200_bwd(ct.byref(p), _lib.stream_ptr(dev))
     if rc:
         raise _lib.IssmError(rc, "issm_b200_bwd")
     return dx, ddt, dA, dB, dC, dD, dz, dbias, dinit

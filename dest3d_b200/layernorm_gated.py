@@ -1,7 +1,7 @@
 """Gated RMSNorm / LayerNorm with the reference's interface (issm_triton/layernorm_gated.py:328-427)
 on top of the B200 C ABI: `RMSNorm`, `LayerNorm`, `rmsnorm_fn`, `layernorm_fn`, `LayerNormFn`.
 """
-import ctypes as C
+import ctypes as ct
 
 import torch
 
@@ -54,7 +54,7 @@ class LayerNormFn(torch.autograd.Function):
         mean = torch.empty(p.rows * ng, dtype=torch.float32, device=x2.device) if not is_rms_norm else None
         p.y, p.y_sr, p.rstd, p.mean = y.data_ptr(), y.stride(0), rstd.data_ptr(), _lib.ptr(mean)
         with torch.cuda.device(x2.device):
-            rc = _lib.lib().issm_b200_norm_fwd(C.byref(p), _lib.stream_ptr(x2.device))
+            rc = _lib.lib().issm_b200_norm_fwd(ct.byref(p), _lib.stream_ptr(x2.device))
         if rc:
             raise _lib.IssmError(rc, "issm_b200_norm_fwd")
         ctx.save_for_backward(x2, weight, bias, mean, rstd, z2)
@@ -86,11 +86,11 @@ class LayerNormFn(torch.autograd.Function):
         p.rstd, p.mean = rstd.data_ptr(), _lib.ptr(mean)
         p.dy, p.dy_sr = dy2.data_ptr(), dy2.stride(0)
         p.dx, p.dz, p.dweight, p.dbias = dx.data_ptr(), _lib.ptr(dz), dw.data_ptr(), _lib.ptr(db)
-        need = _lib.lib().issm_b200_norm_workspace_bytes(C.byref(p), 1)
+        need = _lib.lib().issm_b200_norm_workspace_bytes(ct.byref(p), 1)
         ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=dev)
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         with torch.cuda.device(dev):
-            rc = _lib.lib().issm_b200_norm_bwd(C.byref(p), _lib.stream_ptr(dev))
+            rc = _lib.lib().issm_b200_norm_bwd(ct.byref(p), _lib.stream_ptr(dev))
         if rc:
             raise _lib.IssmError(rc, "issm_b200_norm_bwd")
         dzo = None

@@ -144,6 +144,14 @@ int issm_b200_norm_bwd(const issm_norm_params* p, void* cuda_stream);
  * used by the benchmark to report how many of its own kernels ran inside a timed region. */
 uint64_t issm_b200_launch_count(void);
 
+/* Hardware self-check of the tensor-core building blocks (no counterpart in the reference):
+ * one CTA computes D (M x N, float) = A (M x K, bf16) * B (N x K, bf16)^T with tcgen05.mma through
+ * the same shared-memory layouts and descriptors as the ISSM tensor path.  M is 64 or 128; N and K
+ * multiples of 16; kind 0 = 128-byte swizzle, 1 = interleaved core matrices.  Draw (128 x N)
+ * receives the raw TMEM lanes.  status (device int, optional) is set to 1 if the wait expired. */
+int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
+                            float* D, float* Draw, int32_t* status, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
