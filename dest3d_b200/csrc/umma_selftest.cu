@@ -21,7 +21,9 @@ __global__ void __launch_bounds__(128) k_umma_selftest(int M, int N, int K, int 
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_holder;
   uint8_t* sA = smem;
-  uint8_t* sB = smem + (size_t)M * K * 2;
+  // a SW128 operand occupies whole 128-byte rows per 64-element atom, even when K is not a multiple of 64
+  const size_t bytesA = kindA == 0 ? (size_t)M * ((K + 63) / 64) * 128 : (size_t)M * K * 2;
+  uint8_t* sB = smem + ((bytesA + 1023) & ~(size_t)1023);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int i = tid; i < M * K; i += blockDim.x) *(bf16*)(sA + st_off(kindA, M, i / K, i % K)) = A[i];
   for (int i = tid; i < N * K; i += blockDim.x) *(bf16*)(sB + st_off(kindB, N, i / K, i % K)) = B[i];
@@ -75,7 +77,9 @@ using namespace issm;
 extern "C" int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
                                        float* D, float* Draw, int32_t* status, void* stream) {
   if ((M != 64 && M != 128) || N < 16 || N > 256 || N % 16 || K < 16 || K % 16 || !A || !B || !D || !Draw) return ISSM_ERR_SHAPE;
-  const size_t smem = (size_t)(M + N) * K * 2 + 1024;
+  const size_t bytesA = kindA == 0 ? (size_t)M * ((K + 63) / 64) * 128 : (size_t)M * K * 2;
+  const size_t bytesB = kindB == 0 ? (size_t)N * ((K + 63) / 64) * 128 : (size_t)N * K * 2;
+  const size_t smem = ((bytesA + 1023) & ~(size_t)1023) + bytesB + 2048;
   if (smem > 200 * 1024) return ISSM_ERR_SHAPE;
   if (cudaFuncSetAttribute(k_umma_selftest, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ISSM_ERR_CUDA;
   ISSM_LAUNCH(k_umma_selftest, 1, 128, smem, (cudaStream_t)stream, M, N, K, kindA, kindB, (const bf16*)A, (const bf16*)B, D, Draw, status);

@@ -15,6 +15,25 @@ import torch
 from . import _lib
 
 _PATHS = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tensor": _lib.PATH_TENSOR}
+_STATUS = {}
+
+
+def _status_word(device):
+    """One int32 per device that kernels OR error bits into (bit 0: a bounded wait expired,
+    bit 1: a 64-point block exceeded the decay range of the tensor-core factorisation)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _STATUS[key]
+
+
+def device_status(device=None, reset=True):
+    """Read (and by default clear) the device status word; synchronises the device."""
+    w = _status_word(device if device is not None else torch.cuda.current_device())
+    v = int(w.item())
+    if reset and v:
+        w.zero_()
+    return v
 
 
 def _row_major_last(t):
@@ -87,6 +106,7 @@ def _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_s
     if zk is not None:
         p.z, p.z_sb, p.z_sl, p.z_sh = zk.data_ptr(), zk.stride(0), zk.stride(1), zk.stride(2)
     p.A, p.D, p.dt_bias, p.initial_states = Ak.data_ptr(), _lib.ptr(Dk), _lib.ptr(bk), _lib.ptr(ik)
+    p.status = _status_word(x.device).data_ptr()
     return p, keep
 
 

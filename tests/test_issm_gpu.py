@@ -55,6 +55,32 @@ def test_parity_simt(case, dtype):
     parity.compare(got, ref, dtype, want_final=opts.get("return_final", True))
 
 
+TENSOR_CASES = [
+    ("t_tail64", (1, 576, 2, 36, 256, 1, 256), {}, BENCH_OPTS),
+    ("t_dest_call", (2, 300, 8, 36, 256, 1, 256), {}, dict(use_z=False, use_dt_bias=False, dt_pre=True)),
+    ("t_reverse", (1, 576, 2, 36, 256, 1, 256), {}, dict(BENCH_OPTS, reverse=True)),
+    ("t_n128_p32", (2, 200, 3, 32, 128, 1, 64), {}, BENCH_OPTS),
+    ("t_short", (1, 37, 2, 36, 256, 1, 256), {}, BENCH_OPTS),
+    ("t_L1", (1, 1, 1, 36, 128, 1, 64), {}, BENCH_OPTS),
+    ("t_groups_Dhdim", (1, 130, 4, 20, 128, 2, 128), dict(D_has_hdim=True), BENCH_OPTS),
+    ("t_noncontig", (1, 128, 2, 36, 256, 1, 64), {}, dict(BENCH_OPTS, noncontig=True)),
+    ("t_no_init_no_final", (1, 192, 2, 36, 256, 1, 64), {}, dict(BENCH_OPTS, use_initial_states=False, return_final=False, dfinal=False, use_z=False, use_D=False)),
+]
+
+
+@pytest.mark.parametrize("case", TENSOR_CASES, ids=[c[0] for c in TENSOR_CASES])
+def test_parity_tensor(case):
+    """bf16 activations through the tcgen05 path (forward) against the float64 oracle."""
+    from dest3d_b200.issm_combined import device_status
+    _, shape, mk, opts = case
+    inp, Q = _inputs(shape, mk, opts, torch.bfloat16)
+    ref = parity.oracle_run(inp, Q, opts)
+    device_status()
+    got = parity.cuda_run(inp, Q, opts, path="tensor")
+    assert device_status() == 0, "tensor path raised a device status bit"
+    parity.compare(got, ref, torch.bfloat16, want_final=opts.get("return_final", True))
+
+
 @pytest.mark.parametrize("name", ["tiny_f64", "ragged_heads_f64", "reftest_f32"])
 def test_golden_reference_vectors(name):
     """Outputs and gradients produced by the reference's own pure-PyTorch scan (tests/golden)."""
