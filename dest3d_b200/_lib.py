@@ -34,7 +34,7 @@ class IssmParams(C.Structure):
         + [("out", vp), ("out_sb", i64), ("out_sl", i64), ("out_sh", i64), ("out_x", vp), ("final_states", vp)]
         + [("dout", vp), ("dout_sb", i64), ("dout_sl", i64), ("dout_sh", i64), ("dfinal_states", vp)]
         + [(n, vp) for n in ("dx", "ddt", "dB", "dC", "dz", "dA", "ddt_bias", "dD", "dinitial_states")]
-        + [("workspace", vp), ("workspace_bytes", C.c_size_t), ("status", vp)]
+        + [("workspace", vp), ("workspace_bytes", C.c_size_t), ("status", vp), ("saved_states", vp)]
     )
 
 

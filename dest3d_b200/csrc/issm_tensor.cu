@@ -1,19 +1,25 @@
-// tcgen05 tensor-core path of the ISSM scan (bf16 activations, fp32 accumulation in TMEM).
+// tcgen05 tensor-core path of the ISSM scan (bf16 activations, fp32 accumulation in TMEM): forward.
 //
 // One CTA walks one (batch, head) stream along the sequence in sub-blocks of 64 points; thread t of
 // the CTA owns state column n = t for the whole walk: it transforms dt, keeps the running
 // cumulative decay of its column, builds its column of every MMA operand, and owns TMEM lane
-// t % 128 of the running state S[n, p] (fp32).  Per sub-block (rows l, s of the block; a = cumsum
-// of dt*A inside the block, r = a at mid-block, a_last = a at the end):
-//   M[l,s]  = sum_n (C e^{a[l]-r})[l,n] (B dt e^{r-a[s]})[s,n]         tcgen05.mma  64 x 64, K = N
-//   Y[l,p]  = sum_n (C e^{a[l]})[l,n] S[p,n] + sum_{s<=l} M[l,s] x[s,p]  tcgen05.mma  64 x 48, K = N, 64
-//   S[n,p]  = e^{a_last[n]} S[n,p] + sum_l (B dt e^{a_last-a[l]})[l,n] x[l,p]   tcgen05.mma 128 x 48, K = 64
-// which is the chunked algorithm of issm_triton/issm_combined.py:57-92 (chunk state, state passing,
-// C.A.B^T, chunk scan) with a 64-row chunk, the state carried on chip instead of through HBM, and
-// the decay inside the contraction factored through the mid-block reference so that both factors
-// stay in range (half-span up to 120 in log2 units; beyond that the status word gets bit 2).
+// t % 128 of the running state S[n, p] (fp32).  Per sub-block (rows l, s; a = cumsum of dt*A
+// inside the block in log2 units, r = a at mid-block, a_last = a at the end):
+//   Cd[l,n] = C[l,n] 2^(a[l,n]-r[n])            Bd[s,n] = B[s,n] dt[s,n] 2^(r[n]-a[s,n])
+//   M[l,s]  = sum_n Cd[l,n] Bd[s,n]                                   tcgen05.mma  64 x 64, K = N
+//   Y[l,p]  = sum_n Cd[l,n] (2^r S)[p,n] + sum_{s<=l} M[l,s] x[s,p]   tcgen05.mma  64 x 48, K = N, then 64
+//   S[n,p] <- 2^(a_last-r) ( 2^r S[n,p] + sum_l Bd[l,n] x[l,p] )      tcgen05.mma 128 x 48, K = 64
+// This is the chunked algorithm of issm_triton/issm_combined.py:57-92 (dt transform + cumsum,
+// chunk state, state passing, C.A.B^T, chunk scan with D skip and silu(z) gate) with a 64-row
+// chunk and the state carried on chip instead of through HBM.  The decay inside the contraction is
+// factored through the mid-block reference so that every factor stays in range as long as the
+// half-block span of |a| is below 120 (log2 units); a violated block sets bit 1 of the status word.
+// dt (bf16), B and C rows of the next block are prefetched into shared memory by bulk (TMA) copies
+// while the current block computes.
 #include "issm_common.cuh"
 #include "umma.cuh"
+
+#include <type_traits>
 
 namespace issm {
 using namespace umma;
@@ -25,7 +31,7 @@ constexpr float LN2 = 0.6931471805599453f;
 
 struct TArgs {
   int b, L, H, P, N, G, hpg, rev;
-  int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final;
+  int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
   float dtmin, dtmax;
   const bf16* x; int64_t x_sb, x_sl, x_sh;
   const void* dt; int64_t dt_sb, dt_sl, dt_sh;
@@ -37,19 +43,22 @@ struct TArgs {
   bf16* out; int64_t o_sb, o_sl, o_sh;
   bf16* out_x;
   float* final_states;
+  bf16* saved;      // optional (b, H, nblk + 1, N, PP) bf16: state entering every 64-point block, and the final one
   int* status;
 };
 
 template <int NT>
 struct FwdSmem {
-  static constexpr int kCs = 0;
-  static constexpr int kCd = kCs + NT * 128;
-  static constexpr int kBd = kCd + NT * 128;
-  static constexpr int kBhT = kBd + NT * 128;
-  static constexpr int kSop = kBhT + NT * 128;
-  static constexpr int kXT = kSop + NT * (PP * 2);
-  static constexpr int kMm = kXT + PP * 128;
-  static constexpr int kBars = kMm + QB * 128;
+  static constexpr int kCd = 0;                         // [NT/64 atoms][64 l][128 B]
+  static constexpr int kBd = kCd + NT * 128;            // same
+  static constexpr int kSop = kBd + NT * 128;           // [NT/64 atoms][PP p][128 B]
+  static constexpr int kX = kSop + NT * (PP * 2);       // [64 l][128 B]   (p in the row)
+  static constexpr int kMm = kX + QB * 128;             // [64 l][128 B]   (s in the row)
+  static constexpr int kSdt = kMm + QB * 128;           // staging: [64][NT] bf16
+  static constexpr int kSB = kSdt + QB * NT * 2;
+  static constexpr int kSC = kSB + QB * NT * 2;
+  static constexpr int kY = kSC + QB * NT * 2;          // [64][PP] float: pre-skip, pre-gate output rows
+  static constexpr int kBars = kY + QB * PP * 4;
   static constexpr int kTotal = kBars + 64;
 };
 
@@ -59,163 +68,237 @@ __device__ __forceinline__ float softplus_fast(float v) {
   // softplus with the reference's threshold; log2-domain hardware approximations
   return v <= 20.f ? lg2f(1.f + ex2f(v * LOG2E)) * LN2 : v;
 }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+}
 
 template <int NT, typename TDT>
 __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
   using SM = FwdSmem<NT>;
+  constexpr bool kStageDt = sizeof(TDT) == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* barA = (uint64_t*)(smem + SM::kBars);
   uint64_t* barB = barA + 1;
-  uint32_t* tmem_holder = (uint32_t*)(barA + 2);
+  uint64_t* barS = barA + 2;
+  uint32_t* tmem_holder = (uint32_t*)(barA + 3);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
-  const int n = blockIdx.x * NT + tid;
-  const TDT* dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh + n;
-  const bf16* Bp = a.B + b * a.B_sb + g * a.B_sg + n;
-  const bf16* Cp = a.C + b * a.C_sb + g * a.C_sg + n;
-  const bf16* xp = a.x + b * a.x_sb + h * a.x_sh;
-  const float A2 = a.A[h * a.N + n] * LOG2E;
-  const float bias = a.has_bias ? a.bias[h * a.N + n] : 0.f;
+  const int n = tid;                                   // NT == N
+  const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
+  const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
+  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg;
+  const bf16* __restrict__ xp = a.x + b * a.x_sb + h * a.x_sh;
+  const bf16* __restrict__ zp = a.has_z ? a.z + b * a.z_sb + h * a.z_sh : nullptr;
+  const float A2 = __ldg(a.A + h * a.N + n) * LOG2E;
+  const float bias = a.has_bias ? __ldg(a.bias + h * a.N + n) : 0.f;
+  const int nblk = (a.L + QB - 1) / QB;
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
-  for (int i = tid; i < (SM::kBars - SM::kSop) / 16; i += NT) ((uint4*)(smem + SM::kSop))[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_fence_init(); }
+  for (int i = tid; i < (SM::kSdt - SM::kSop) / 16; i += NT) ((uint4*)(smem + SM::kSop))[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_holder;
   const uint32_t t_M = tmem, t_Y = tmem + 64;
-  const uint32_t t_Srow = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 128 + (tid >> 7) * PP;   // this thread's lane
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const uint32_t t_Srow = tmem + lane_base + 128 + (tid >> 7) * PP;   // this thread's TMEM lane
+
+  // bulk prefetch of the dt / B / C rows of block `blk` (one warp issues, completion on barS)
+  auto prefetch = [&](int blk) {
+    const int row0 = blk * QB, rows = min(QB, a.L - row0);
+    if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * (kStageDt ? 3 : 2));
+    __syncwarp();
+    for (int l = lane; l < rows; l += 32) {
+      const int64_t mr = trow(a, row0 + l);
+      if (kStageDt) bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + mr * a.dt_sl, NT * 2, barS);
+      bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + mr * a.B_sl, NT * 2, barS);
+      bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
+    }
+  };
+  if (warp == 1) prefetch(0);
 
   float Srow[PP];
 #pragma unroll
   for (int p = 0; p < PP; ++p) Srow[p] = 0.f;
   if (a.has_init) {
-    const bf16* ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n;
+    const bf16* __restrict__ ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n;
 #pragma unroll
     for (int p = 0; p < PP; ++p)
       if (p < a.P) Srow[p] = __bfloat162float(ip[(size_t)p * a.N]);
   }
   uint8_t* sop_col = smem + SM::kSop + (tid >> 6) * (PP * 128);
-#pragma unroll
-  for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, tid & 63)) = __float2bfloat16_rn(Srow[p]);
+  const int kcol = tid & 63;
+  bf16* savep = a.saved ? a.saved + ((((size_t)b * a.H + h) * (nblk + 1)) * a.N + n) * PP : nullptr;
 
-  const int nblk = (a.L + QB - 1) / QB;
   bool failed = false;
   uint32_t unsafe = 0;
+  int prev_rows = 0, prev_row0 = 0;
+  const int npt = (QB * a.P + NT - 1) / NT;            // x / z tile elements per thread
+  constexpr int XR = (QB * PP + NT - 1) / NT;
+  bf16 xprev[XR], zprev[XR];                           // this thread's x / z elements of the previous block
+  // out = (y + D x) * silu(z) for the tile elements this thread loaded; coalesced over p
+  auto store_tile = [&](int t_row0, int t_rows) {
+#pragma unroll
+    for (int k = 0; k < XR; ++k) {
+      const int i = tid + k * NT;
+      if (k < npt && i < t_rows * a.P) {
+        const int l = i / a.P, p = i - l * a.P;
+        float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
+        if (a.has_D) y = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : __ldg(a.D + h), __bfloat162float(xprev[k]), y);
+        const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
+        if (a.has_z) {
+          a.out_x[o] = __float2bfloat16_rn(y);
+          const float zv = __bfloat162float(zprev[k]);
+          y *= zv / (1.f + ex2f(-zv * LOG2E));
+        }
+        a.out[o] = __float2bfloat16_rn(y);
+      }
+    }
+  };
   for (int blk = 0; blk < nblk; ++blk) {
     const int row0 = blk * QB;
     const int rows = min(QB, a.L - row0);
     const uint32_t parity = blk & 1;
 
-    // ---- stage x^T (K-major over l) -------------------------------------------------------
-    for (int i = tid; i < QB * a.P; i += NT) {
-      const int l = i / a.P, p = i - l * a.P;
-      bf16 v = __float2bfloat16_rn(0.f);
-      if (l < rows) v = xp[(int64_t)trow(a, row0 + l) * a.x_sl + p];
-      *(bf16*)(smem + SM::kXT + sw128_off(p, l)) = v;
+    if (savep) {                                       // state entering this block, for the backward
+      uint4* dst = (uint4*)(savep + (size_t)blk * a.N * PP);
+#pragma unroll
+      for (int c = 0; c < PP / 8; ++c)
+        dst[c] = make_uint4(pack_bf16(Srow[c * 8], Srow[c * 8 + 1]), pack_bf16(Srow[c * 8 + 2], Srow[c * 8 + 3]),
+                            pack_bf16(Srow[c * 8 + 4], Srow[c * 8 + 5]), pack_bf16(Srow[c * 8 + 6], Srow[c * 8 + 7]));
     }
 
+    // ---- x and z tiles: coalesced global loads now, shared-memory stores after pass 1 --------
+    bf16 xr[XR], zr[XR];
+#pragma unroll
+    for (int k = 0; k < XR; ++k) {
+      xr[k] = zr[k] = __float2bfloat16_rn(0.f);
+      const int i = tid + k * NT;
+      if (k < npt && i < rows * a.P) {
+        const int l = i / a.P, p = i - l * a.P;
+        const int64_t mr = trow(a, row0 + l);
+        xr[k] = xp[mr * a.x_sl + p];
+        if (zp) zr[k] = zp[mr * a.z_sl + p];
+      }
+    }
+
+    if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
+
     // ---- pass 1: dt transform, cumulative log2-decay, references -----------------------------
+    // (full blocks run the branch-free instantiation so that the unrolled rows interleave)
     float dtv[QB];
     float acc = 0.f, r = 0.f;
+    auto pass1 = [&](auto full) {
+      constexpr bool kFull = decltype(full)::value;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
 #pragma unroll
-    for (int l = 0; l < QB; ++l) {
-      float v = 0.f;
-      if (l < rows) {
-        v = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl) + bias;
-        if (a.softplus) v = softplus_fast(v);
-        v = fminf(fmaxf(v, a.dtmin), a.dtmax);
+      for (int l = 0; l < QB; ++l) {
+        float v = 0.f;
+        if (kFull || l < rows) {
+          if (kStageDt) v = __bfloat162float(sdt[l * NT]);
+          else v = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl + n);
+          v += bias;
+          if (a.softplus) v = softplus_fast(v);
+          v = fminf(fmaxf(v, a.dtmin), a.dtmax);
+        }
+        dtv[l] = v;
+        acc = fmaf(v, A2, acc);
+        if (l == QB / 2 - 1) r = acc;
       }
-      dtv[l] = v;
-      acc = fmaf(v, A2, acc);
-      if (l == QB / 2 - 1) r = acc;
-    }
+    };
+    if (rows == QB) pass1(std::true_type{}); else pass1(std::false_type{});
     const float alast = acc;
     if (fabsf(r) > 120.f || fabsf(alast - r) > 120.f) unsafe = 1;
 
-    // ---- running state: S <- e^{a_last} S, parked in TMEM for the accumulate MMA -------------
+    // ---- running state scaled to the mid-block reference: TMEM copy (fp32) and bf16 operand ---
     {
-      const float decay = ex2f(alast);
+      const float er = ex2f(r);
 #pragma unroll
-      for (int p = 0; p < PP; ++p) Srow[p] *= decay;
+      for (int p = 0; p < PP; ++p) Srow[p] *= er;
       tmem_st16(t_Srow, Srow);
       tmem_st16(t_Srow + 16, Srow + 16);
       tmem_st16(t_Srow + 32, Srow + 32);
+      if (!a.no_output) {
+#pragma unroll
+        for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, kcol)) = __float2bfloat16_rn(Srow[p]);
+      }
       tmem_st_wait();
     }
 
-    // ---- pass 2: this column of every operand ------------------------------------------------
-    {
-      uint8_t* cs_col = smem + SM::kCs + (tid >> 6) * (QB * 128);
+    // ---- pass 2: this column of Cd and Bd ------------------------------------------------------
+    auto pass2 = [&](auto full) {
+      constexpr bool kFull = decltype(full)::value;
       uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
       uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
-      uint8_t* bh_row = smem + SM::kBhT;
-      const int k = tid & 63;
-      acc = 0.f;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+      const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
+      float ac = 0.f;
 #pragma unroll
-      for (int l0 = 0; l0 < QB; l0 += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int l = l0 + j;
-          float cv = 0.f, bv = 0.f;
-          if (l < rows) {
-            const int64_t mr = trow(a, row0 + l);
-            cv = __bfloat162float(Cp[mr * a.C_sl]);
-            bv = __bfloat162float(Bp[mr * a.B_sl]);
-          }
-          acc = fmaf(dtv[l], A2, acc);
-          const float bdt = bv * dtv[l];
-          const float cs = cv * ex2f(acc);
-          const float cd = cv * ex2f(acc - r);
-          const float bh = bdt * ex2f(alast - acc);
-          const float bd = bdt * ex2f(r - acc);
-          const uint32_t off = sw128_off(l, k);
-          *(bf16*)(cs_col + off) = __float2bfloat16_rn(cs);
-          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-          const uint32_t hb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(bh));
-          if (j & 1) packed[j >> 1] |= hb << 16; else packed[j >> 1] = hb;
+      for (int l = 0; l < QB; ++l) {
+        float cv = 0.f, bv = 0.f;
+        if (kFull || l < rows) {
+          cv = __bfloat162float(sC[l * NT]);
+          bv = __bfloat162float(sB[l * NT]);
         }
-        *(uint4*)(bh_row + sw128_chunk(tid, l0 >> 3)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        ac = fmaf(dtv[l], A2, ac);
+        const uint32_t off = sw128_off(l, kcol);
+        *(bf16*)(cd_col + off) = __float2bfloat16_rn(cv * ex2f(ac - r));
+        *(bf16*)(bd_col + off) = __float2bfloat16_rn(bv * dtv[l] * ex2f(r - ac));
+      }
+    };
+    if (rows == QB) pass2(std::true_type{}); else pass2(std::false_type{});
+    // ---- x tile [l][p] (swizzled rows) and z tile ---------------------------------------------
+#pragma unroll
+    for (int k = 0; k < XR; ++k) {
+      const int i = tid + k * NT;
+      if (k < npt && i < QB * a.P) {
+        const int l = i / a.P, p = i - l * a.P;
+        *(bf16*)(smem + SM::kX + sw128_off(l, p)) = xr[k];
       }
     }
     fence_async_smem();
     fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- MMAs: M = Cd Bd^T, Y = Cs S^T, S += BhT^T x^T ------------------------------------------
+    // ---- MMAs: M = Cd Bd^T, Y = Cd (2^r S)^T, S += Bd^T x ---------------------------------------
     if (tid == 0) {
       fence_after_sync();
       const uint32_t sb = smem_u32(smem);
+      if (!a.no_output) {
 #pragma unroll
-      for (int at = 0; at < NT / 64; ++at)
+        for (int at = 0; at < NT / 64; ++at)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint32_t ko = at * (QB * 128) + kk * 32;
-          mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
-          mma_bf16(t_Y, desc_sw128(sb + SM::kCs + ko), desc_sw128(sb + SM::kSop + at * (PP * 128) + kk * 32),
-                   idesc_bf16(64, PP), (at | kk) != 0);
-        }
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t ko = at * (QB * 128) + kk * 32;
+            mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
+            mma_bf16(t_Y, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kSop + at * (PP * 128) + kk * 32),
+                     idesc_bf16(64, PP), (at | kk) != 0);
+          }
+      }
 #pragma unroll
       for (int sl = 0; sl < NT / 128; ++sl)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          mma_bf16(tmem + 128 + sl * PP, desc_sw128(sb + SM::kBhT + sl * (128 * 128) + kk * 32),
-                   desc_sw128(sb + SM::kXT + kk * 32), idesc_bf16(128, PP), 1);
+          mma_bf16(tmem + 128 + sl * PP, desc_sw128_mn(sb + SM::kBd + sl * (2 * QB * 128) + kk * 2048, QB * 128),
+                   desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128), idesc_bf16(128, PP, 1, 1), 1);
       mma_commit(barA);
     }
+    if (warp == 1 && blk + 1 < nblk) prefetch(blk + 1);  // every thread is past its staging reads
+
+    // ---- coalesced store of the previous block's output tile ----------------------------------
+    if (blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
+#pragma unroll
+    for (int k = 0; k < XR; ++k) { xprev[k] = xr[k]; zprev[k] = zr[k]; }
+
     if (!mbar_wait(barA, parity)) failed = true;
-    if (__syncthreads_or(failed)) { failed = true; break; }
     fence_after_sync();
 
-    // ---- epilogue 1: masked M -> bf16 operand; new state -> registers and bf16 operand --------
-    if (warp < 4) {
+    // ---- epilogue 1: masked M -> bf16 operand; new state -> registers ---------------------------
+    if (warp < 4 && !a.no_output && !failed) {
       float mv[64];
       tmem_ld16(t_M + lane_base, mv);
       tmem_ld16(t_M + lane_base + 16, mv + 16);
@@ -230,23 +313,27 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
 #pragma unroll
           for (int j = 0; j < 8; j += 2) {
             const int s = c * 8 + j;
-            const float v0 = s <= l ? mv[s] : 0.f, v1 = s + 1 <= l ? mv[s + 1] : 0.f;
-            pk[j >> 1] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v0)) |
-                         ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v1)) << 16);
+            pk[j >> 1] = pack_bf16(s <= l ? mv[s] : 0.f, s + 1 <= l ? mv[s + 1] : 0.f);
           }
           *(uint4*)(smem + SM::kMm + sw128_chunk(l, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
       }
     }
-    tmem_ld16(t_Srow, Srow);
-    tmem_ld16(t_Srow + 16, Srow + 16);
-    tmem_ld16(t_Srow + 32, Srow + 32);
-    tmem_ld_wait();
+    if (!failed) {
+      tmem_ld16(t_Srow, Srow);
+      tmem_ld16(t_Srow + 16, Srow + 16);
+      tmem_ld16(t_Srow + 32, Srow + 32);
+      tmem_ld_wait();
+      const float el = ex2f(alast - r);
 #pragma unroll
-    for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, tid & 63)) = __float2bfloat16_rn(Srow[p]);
+      for (int p = 0; p < PP; ++p) Srow[p] *= el;
+    }
     fence_async_smem();
     fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(failed)) { failed = true; break; }
+    prev_rows = rows;
+    prev_row0 = row0;
+    if (a.no_output) continue;
 
     // ---- Y += tril(M) x ------------------------------------------------------------------------
     if (tid == 0) {
@@ -254,50 +341,44 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
       const uint32_t sb = smem_u32(smem);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
-        mma_bf16(t_Y, desc_sw128(sb + SM::kMm + kk * 32), desc_sw128(sb + SM::kXT + kk * 32), idesc_bf16(64, PP), 1);
+        mma_bf16(t_Y, desc_sw128(sb + SM::kMm + kk * 32), desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128),
+                 idesc_bf16(64, PP, 0, 1), 1);
       mma_commit(barB);
     }
     if (!mbar_wait(barB, parity)) failed = true;
-    if (__syncthreads_or(failed)) { failed = true; break; }
     fence_after_sync();
 
-    // ---- epilogue 2: D skip, gate, store -----------------------------------------------------
-    if (warp < 4) {
+    // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) --
+    if (warp < 4 && !failed) {
       float yv[PP];
       tmem_ld16(t_Y + lane_base, yv);
       tmem_ld16(t_Y + lane_base + 16, yv + 16);
       tmem_ld16(t_Y + lane_base + 32, yv + 32);
       tmem_ld_wait();
       const int l = warp * 16 + lane;
-      if (lane < 16 && l < rows) {
-        const int64_t mr = trow(a, row0 + l);
-        const bf16* xr = xp + mr * a.x_sl;
-        bf16* orow = a.out + b * a.o_sb + mr * a.o_sl + h * a.o_sh;
-        bf16* oxr = a.out_x ? a.out_x + b * a.o_sb + mr * a.o_sl + h * a.o_sh : nullptr;
-        const bf16* zr = a.has_z ? a.z + b * a.z_sb + mr * a.z_sl + h * a.z_sh : nullptr;
+      if (lane < 16) {
+        float4* dst = (float4*)(smem + SM::kY + l * PP * 4);
 #pragma unroll
-        for (int p = 0; p < PP; ++p) {
-          if (p < a.P) {
-            float y = yv[p];
-            if (a.has_D) y = fmaf(a.D_has_hdim ? a.D[h * a.P + p] : a.D[h], __bfloat162float(xr[p]), y);
-            if (zr) {
-              oxr[p] = __float2bfloat16_rn(y);
-              const float zv = __bfloat162float(zr[p]);
-              y *= zv / (1.f + ex2f(-zv * LOG2E));
-            }
-            orow[p] = __float2bfloat16_rn(y);
-          }
-        }
+        for (int c = 0; c < PP / 4; ++c) dst[c] = make_float4(yv[c * 4], yv[c * 4 + 1], yv[c * 4 + 2], yv[c * 4 + 3]);
       }
     }
     fence_before_sync();
   }
 
+  __syncthreads();
+  if (!failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // output tile of the last block
   if (!failed && a.want_final) {
     float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
 #pragma unroll
     for (int p = 0; p < PP; ++p)
       if (p < a.P) fp[(size_t)p * a.N] = Srow[p];
+  }
+  if (!failed && savep) {
+    uint4* dst = (uint4*)(savep + (size_t)nblk * a.N * PP);
+#pragma unroll
+    for (int c = 0; c < PP / 8; ++c)
+      dst[c] = make_uint4(pack_bf16(Srow[c * 8], Srow[c * 8 + 1]), pack_bf16(Srow[c * 8 + 2], Srow[c * 8 + 3]),
+                          pack_bf16(Srow[c * 8 + 4], Srow[c * 8 + 5]), pack_bf16(Srow[c * 8 + 6], Srow[c * 8 + 7]));
   }
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
@@ -309,10 +390,19 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 bool tensor_path_supported(const issm_params& p) {
   if (p.io_dtype != ISSM_BF16) return false;
   if (p.headdim > PP) return false;
   if (p.dstate != 128 && p.dstate != 256) return false;
+  // bulk (TMA) row copies need 16-byte aligned rows of B, C and (bf16) dt
+  if (p.B && (!aligned16(p.B) || !aligned16(p.C))) return false;
+  if ((p.B_sb | p.B_sl | p.B_sg | p.C_sb | p.C_sl | p.C_sg) & 7) return false;
+  if (p.dt_dtype == ISSM_BF16) {
+    if (p.dt && !aligned16(p.dt)) return false;
+    if ((p.dt_sb | p.dt_sl | p.dt_sh) & 7) return false;
+  }
   return true;
 }
 
@@ -337,6 +427,7 @@ static TArgs make_targs(const issm_params& p) {
   a.out_x = p.has_z ? (bf16*)p.out_x : nullptr;
   a.final_states = p.final_states;
   a.status = p.status;
+  a.saved = (bf16*)p.saved_states;
   return a;
 }
 
@@ -347,7 +438,7 @@ static int launch_fwd(const TArgs& a, cudaStream_t s) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(a.N / NT, a.H, a.b), NT, smem, s, a);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), NT, smem, s, a);
   return ISSM_OK;
 }
 

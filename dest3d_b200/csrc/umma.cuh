@@ -28,9 +28,18 @@ __device__ __forceinline__ uint64_t desc_interleave(uint32_t saddr, uint32_t lbo
   return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
          ((uint64_t)(sbo_bytes >> 4) << 32) | ((uint64_t)1 << 46);
 }
-// instruction descriptor, kind::f16, A and B bf16 K-major, D fp32
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// MN-major operand in SW128 storage: rows are indexed by k, each row holds 64 consecutive MN
+// elements (128 bytes, chunks XOR-permuted with k & 7); 8-row k-groups are 1024 bytes apart (SBO)
+// and 64-wide MN groups are `mn_group_bytes` apart (LBO).  This is the same storage as the
+// K-major SW128 layout of the transposed matrix, so one tile can feed both roles.
+__device__ __forceinline__ uint64_t desc_sw128_mn(uint32_t saddr, uint32_t mn_group_bytes) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(mn_group_bytes >> 4) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor, kind::f16, A and B bf16, D fp32; a_mn / b_mn = 1 selects an MN-major operand
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // byte offset of element (row, k) inside a SW128 atom (k < 64)

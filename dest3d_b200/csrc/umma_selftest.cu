@@ -7,10 +7,21 @@
 namespace issm {
 using namespace umma;
 
-// layout kinds: 0 = SW128 K-major, 1 = INTERLEAVE K-major
-__device__ uint32_t st_off(int kind, int rows, int row, int k) {
+// layout kinds: 0 = SW128 K-major, 1 = INTERLEAVE K-major, 2 = SW128 MN-major
+__device__ uint32_t st_off(int kind, int rows, int K, int row, int k) {
   if (kind == 0) return (uint32_t)((k >> 6) * rows * 128) + sw128_off(row, k & 63);
+  if (kind == 2) return (uint32_t)((row >> 6) * K * 128) + sw128_off(k, row & 63);
   return (uint32_t)((k >> 3) * rows * 16 + row * 16 + (k & 7) * 2);
+}
+__device__ size_t st_bytes(int kind, int rows, int K) {
+  if (kind == 0) return (size_t)rows * ((K + 63) / 64) * 128;
+  if (kind == 2) return (size_t)K * ((rows + 63) / 64) * 128;
+  return (size_t)rows * K * 2;
+}
+__device__ uint64_t st_desc(int kind, uint32_t base, int rows, int K, int k0) {
+  if (kind == 0) return desc_sw128(base + (k0 >> 6) * rows * 128 + (k0 & 63) * 2);
+  if (kind == 2) return desc_sw128_mn(base + k0 * 128, K * 128);
+  return desc_interleave(base + (k0 >> 3) * rows * 16, rows * 16, 128);
 }
 
 __global__ void __launch_bounds__(128) k_umma_selftest(int M, int N, int K, int kindA, int kindB,
@@ -22,11 +33,14 @@ __global__ void __launch_bounds__(128) k_umma_selftest(int M, int N, int K, int 
   __shared__ uint32_t tmem_holder;
   uint8_t* sA = smem;
   // a SW128 operand occupies whole 128-byte rows per 64-element atom, even when K is not a multiple of 64
-  const size_t bytesA = kindA == 0 ? (size_t)M * ((K + 63) / 64) * 128 : (size_t)M * K * 2;
+  const size_t bytesA = st_bytes(kindA, M, K);
   uint8_t* sB = smem + ((bytesA + 1023) & ~(size_t)1023);
+
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < M * K; i += blockDim.x) *(bf16*)(sA + st_off(kindA, M, i / K, i % K)) = A[i];
-  for (int i = tid; i < N * K; i += blockDim.x) *(bf16*)(sB + st_off(kindB, N, i / K, i % K)) = B[i];
+  for (int i = tid; i < (int)((bytesA + 1023) / 1024 * 1024 + st_bytes(kindB, N, K)) / 4; i += blockDim.x) ((uint32_t*)smem)[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < M * K; i += blockDim.x) *(bf16*)(sA + st_off(kindA, M, K, i / K, i % K)) = A[i];
+  for (int i = tid; i < N * K; i += blockDim.x) *(bf16*)(sB + st_off(kindB, N, K, i / K, i % K)) = B[i];
   if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(&tmem_holder, 256); tmem_relinquish(); }
   fence_async_smem();
@@ -35,15 +49,9 @@ __global__ void __launch_bounds__(128) k_umma_selftest(int M, int N, int K, int 
   fence_after_sync();
   const uint32_t tmem = tmem_holder;
   if (tid == 0) {
-    const uint32_t idesc = idesc_bf16(M, N);
-    for (int k0 = 0; k0 < K; k0 += 16) {
-      uint64_t da, db;
-      if (kindA == 0) da = desc_sw128(smem_u32(sA) + (k0 >> 6) * M * 128 + (k0 & 63) * 2);
-      else da = desc_interleave(smem_u32(sA) + (k0 >> 3) * M * 16, M * 16, 128);
-      if (kindB == 0) db = desc_sw128(smem_u32(sB) + (k0 >> 6) * N * 128 + (k0 & 63) * 2);
-      else db = desc_interleave(smem_u32(sB) + (k0 >> 3) * N * 16, N * 16, 128);
-      mma_bf16(tmem, da, db, idesc, k0 > 0);
-    }
+    const uint32_t idesc = idesc_bf16(M, N, kindA == 2, kindB == 2);
+    for (int k0 = 0; k0 < K; k0 += 16)
+      mma_bf16(tmem, st_desc(kindA, smem_u32(sA), M, K, k0), st_desc(kindB, smem_u32(sB), N, K, k0), idesc, k0 > 0);
     mma_commit(&bar);
   }
   const bool ok = mbar_wait(&bar, 0, 1u << 22);
@@ -77,8 +85,13 @@ using namespace issm;
 extern "C" int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
                                        float* D, float* Draw, int32_t* status, void* stream) {
   if ((M != 64 && M != 128) || N < 16 || N > 256 || N % 16 || K < 16 || K % 16 || !A || !B || !D || !Draw) return ISSM_ERR_SHAPE;
-  const size_t bytesA = kindA == 0 ? (size_t)M * ((K + 63) / 64) * 128 : (size_t)M * K * 2;
-  const size_t bytesB = kindB == 0 ? (size_t)N * ((K + 63) / 64) * 128 : (size_t)N * K * 2;
+  auto bytes = [](int kind, int rows, int K) -> size_t {
+    if (kind == 0) return (size_t)rows * ((K + 63) / 64) * 128;
+    if (kind == 2) return (size_t)K * ((rows + 63) / 64) * 128;
+    return (size_t)rows * K * 2;
+  };
+  if (kindA < 0 || kindA > 2 || kindB < 0 || kindB > 2) return ISSM_ERR_SHAPE;
+  const size_t bytesA = bytes(kindA, M, K), bytesB = bytes(kindB, N, K);
   const size_t smem = ((bytesA + 1023) & ~(size_t)1023) + bytesB + 2048;
   if (smem > 200 * 1024) return ISSM_ERR_SHAPE;
   if (cudaFuncSetAttribute(k_umma_selftest, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ISSM_ERR_CUDA;

@@ -96,6 +96,10 @@ typedef struct issm_params {
 
   void* workspace; size_t workspace_bytes;
   int32_t* status;              /* optional device word, written only on a device-side error */
+  /* Optional, tensor path only: (batch, nheads, ceil(seqlen/64) + 1, dstate, 48) bf16.  The forward
+   * stores the state entering every 64-point block (and the final state) here; a backward given
+   * the same buffer skips recomputing them (the reference recomputes: issm_combined.py:136-144). */
+  void* saved_states;
 } issm_params;
 
 /* Gated RMS / Layer norm over the last dimension of a (rows, hidden) matrix
@@ -147,7 +151,8 @@ uint64_t issm_b200_launch_count(void);
 /* Hardware self-check of the tensor-core building blocks (no counterpart in the reference):
  * one CTA computes D (M x N, float) = A (M x K, bf16) * B (N x K, bf16)^T with tcgen05.mma through
  * the same shared-memory layouts and descriptors as the ISSM tensor path.  M is 64 or 128; N and K
- * multiples of 16; kind 0 = 128-byte swizzle, 1 = interleaved core matrices.  Draw (128 x N)
+ * multiples of 16; kind 0 = 128-byte swizzle K-major, 1 = interleaved core matrices, 2 = 128-byte
+ * swizzle MN-major.  Draw (128 x N)
  * receives the raw TMEM lanes.  status (device int, optional) is set to 1 if the wait expired. */
 int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
                             float* D, float* Draw, int32_t* status, void* cuda_stream);

@@ -7,10 +7,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 CONFIGS = [
-    # M, N, K, kindA, kindB   (kind 0 = 128-byte swizzle, 1 = interleaved core matrices)
+    # M, N, K, kindA, kindB   (kind 0 = 128-byte swizzle K-major, 1 = interleaved core matrices)
     (128, 64, 64, 0, 0), (128, 48, 64, 0, 0), (64, 64, 256, 0, 0), (64, 48, 256, 0, 0), (64, 48, 64, 0, 0),
     (128, 64, 48, 1, 1), (128, 64, 48, 1, 0), (128, 64, 48, 0, 0), (64, 64, 48, 0, 0), (128, 48, 64, 0, 1),
     (128, 256, 64, 0, 0), (128, 64, 16, 1, 1),
+    # kind 2 = MN-major operand in 128-byte-swizzle storage (the transposed tile's K-major storage)
+    (128, 64, 64, 2, 0), (128, 64, 64, 0, 2), (128, 48, 64, 2, 2), (64, 64, 64, 2, 2), (64, 48, 256, 0, 2),
+    (128, 64, 48, 2, 0), (64, 48, 64, 2, 2),
 ]
 
 
