@@ -11,7 +11,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libissm_b200.so")
-SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "umma_selftest.cu"]
+SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "issm_tensor_bwd.cu", "umma_selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 

@@ -16,36 +16,9 @@
 // half-block span of |a| is below 120 (log2 units); a violated block sets bit 1 of the status word.
 // dt (bf16), B and C rows of the next block are prefetched into shared memory by bulk (TMA) copies
 // while the current block computes.
-#include "issm_common.cuh"
-#include "umma.cuh"
-
-#include <type_traits>
+#include "issm_tensor.cuh"
 
 namespace issm {
-using namespace umma;
-
-constexpr int QB = 64;   // rows per sub-block
-constexpr int PP = 48;   // head dim padded to an MMA-legal N
-constexpr float LOG2E = 1.4426950408889634f;
-constexpr float LN2 = 0.6931471805599453f;
-
-struct TArgs {
-  int b, L, H, P, N, G, hpg, rev;
-  int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
-  float dtmin, dtmax;
-  const bf16* x; int64_t x_sb, x_sl, x_sh;
-  const void* dt; int64_t dt_sb, dt_sl, dt_sh;
-  const bf16* B; int64_t B_sb, B_sl, B_sg;
-  const bf16* C; int64_t C_sb, C_sl, C_sg;
-  const bf16* z; int64_t z_sb, z_sl, z_sh;
-  const float* A; const float* D; const float* bias;
-  const bf16* init;
-  bf16* out; int64_t o_sb, o_sl, o_sh;
-  bf16* out_x;
-  float* final_states;
-  bf16* saved;      // optional (b, H, nblk + 1, N, PP) bf16: state entering every 64-point block, and the final one
-  int* status;
-};
 
 template <int NT>
 struct FwdSmem {
@@ -61,16 +34,6 @@ struct FwdSmem {
   static constexpr int kBars = kY + QB * PP * 4;
   static constexpr int kTotal = kBars + 64;
 };
-
-__device__ __forceinline__ int trow(const TArgs& a, int t) { return a.rev ? a.L - 1 - t : t; }
-
-__device__ __forceinline__ float softplus_fast(float v) {
-  // softplus with the reference's threshold; log2-domain hardware approximations
-  return v <= 20.f ? lg2f(1.f + ex2f(v * LOG2E)) * LN2 : v;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
-}
 
 template <int NT, typename TDT>
 __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
@@ -407,10 +370,10 @@ bool tensor_path_supported(const issm_params& p) {
 }
 
 size_t tensor_workspace_bytes(const issm_params& p, int pass) {
-  return pass == 0 ? 0 : simt_workspace_bytes(p, pass);
+  return pass == 0 ? 0 : tensor_bwd_workspace_bytes(p);
 }
 
-static TArgs make_targs(const issm_params& p) {
+TArgs make_targs(const issm_params& p) {
   TArgs a{};
   a.b = p.batch; a.L = p.seqlen; a.H = p.nheads; a.P = p.headdim; a.N = p.dstate; a.G = p.ngroups;
   a.hpg = p.nheads / p.ngroups; a.rev = p.reverse;
@@ -448,9 +411,14 @@ int tensor_fwd(const issm_params& p, cudaStream_t s) {
   return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, s) : launch_fwd<128, float>(a, s);
 }
 
-int tensor_bwd(const issm_params& p, cudaStream_t s) {
-  // the backward still runs on the SIMT kernels (same workspace layout)
-  return simt_bwd(p, s);
+// forward walk that only regenerates the block-entry states (for a backward without saved states)
+int tensor_fwd_states_only(const issm_params& p, bf16* saved, cudaStream_t s) {
+  TArgs a = make_targs(p);
+  a.saved = saved;
+  a.no_output = 1;
+  a.want_final = 0;
+  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, s) : launch_fwd<256, float>(a, s);
+  return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, s) : launch_fwd<128, float>(a, s);
 }
 
 }  // namespace issm

@@ -119,11 +119,18 @@ def _workspace(p, pass_, device, keep):
 
 def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
              dt_softplus=False, dt_limit=(0.0, float("inf")), reverse=False, path="auto",
-             want_final=True):
-    """Forward only (no autograd).  Returns (out, out_x or None, final_states or None);
-    counterpart of `_issm_chunk_scan_combined_fwd` (issm_combined.py:57-92)."""
+             want_final=True, save_states=False):
+    """Forward only (no autograd).  Returns (out, out_x or None, final_states or None), plus the
+    saved block-entry states (or None) when `save_states` is set; counterpart of
+    `_issm_chunk_scan_combined_fwd` (issm_combined.py:57-92)."""
     p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
                            dt_limit, reverse, path)
+    saved = None
+    if save_states and _lib.lib().issm_b200_resolve_path(ct.byref(p)) == _lib.PATH_TENSOR:
+        # the tensor-core backward reads the state entering every 64-point block instead of recomputing it
+        saved = torch.empty(x.shape[0], x.shape[2], (x.shape[1] + 63) // 64 + 1, B.shape[-1], 48,
+                            dtype=torch.bfloat16, device=x.device)
+        p.saved_states = saved.data_ptr()
     out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     out_x = torch.empty_like(out) if z is not None else None
     final = torch.empty(x.shape[0], x.shape[2], x.shape[3], B.shape[-1], dtype=torch.float32, device=x.device) if want_final else None
@@ -134,12 +141,12 @@ def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_s
         rc = _lib.lib().issm_b200_fwd(ct.byref(p), _lib.stream_ptr(x.device))
     if rc:
         raise _lib.IssmError(rc, "issm_b200_fwd")
-    return out, out_x, final
+    return (out, out_x, final, saved) if save_states else (out, out_x, final)
 
 
 def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=None,
              initial_states=None, dfinal_states=None, dt_softplus=False,
-             dt_limit=(0.0, float("inf")), reverse=False, path="auto"):
+             dt_limit=(0.0, float("inf")), reverse=False, path="auto", saved_states=None):
     """Backward; counterpart of `_issm_chunk_scan_combined_bwd` (issm_combined.py:95-179).
     `out_x` is the pre-gate output saved by the forward (only read when z is given).
     Returns (dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinitial_states) with the reference's dtypes;
@@ -172,6 +179,7 @@ def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=No
         p.has_dfinal, p.dfinal_states = 1, dfin.data_ptr()
     p.dx, p.ddt, p.dB, p.dC, p.dz = dx.data_ptr(), ddt.data_ptr(), dB.data_ptr(), dC.data_ptr(), _lib.ptr(dz)
     p.dA, p.ddt_bias, p.dD, p.dinitial_states = dA.data_ptr(), _lib.ptr(dbias), _lib.ptr(dD), _lib.ptr(dinit)
+    p.saved_states = _lib.ptr(saved_states)
     _workspace(p, 1, dev, keep)
     with torch.cuda.device(dev):
         rc = _lib.lib().issm_b200_bwd(ct.byref(p), _lib.stream_ptr(dev))
@@ -190,20 +198,22 @@ class ISSMChunkScanCombinedFn(torch.autograd.Function):
                 reverse=False, path="auto"):
         if seq_idx is not None:
             raise NotImplementedError("seq_idx (packed variable-length batches) is not supported")
-        out, out_x, final = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states,
-                                     dt_softplus, dt_limit, reverse, path, want_final=return_final_states)
-        ctx.save_for_backward(out_x, x, dt, A, B, C, D, z, dt_bias, initial_states)
+        need_grad = any(ctx.needs_input_grad)
+        out, out_x, final, saved = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states,
+                                            dt_softplus, dt_limit, reverse, path, want_final=return_final_states,
+                                            save_states=need_grad)
+        ctx.save_for_backward(out_x, x, dt, A, B, C, D, z, dt_bias, initial_states, saved)
         ctx.opts = (chunk_size, dt_softplus, dt_limit, return_final_states, reverse, path)
         return out if not return_final_states else (out, final)
 
     @staticmethod
     def backward(ctx, dout, *args):
-        out_x, x, dt, A, B, C, D, z, dt_bias, initial_states = ctx.saved_tensors
+        out_x, x, dt, A, B, C, D, z, dt_bias, initial_states, saved = ctx.saved_tensors
         chunk_size, dt_softplus, dt_limit, return_final_states, reverse, path = ctx.opts
         dfinal = args[0] if return_final_states and len(args) and args[0] is not None else None
         dx, ddt, dA, dB, dC, dD, dz, dbias, dinit = issm_bwd(
             dout, x, dt, A, B, C, out_x, chunk_size, D, z, dt_bias, initial_states, dfinal,
-            dt_softplus, dt_limit, reverse, path)
+            dt_softplus, dt_limit, reverse, path, saved_states=saved)
         ddt = ddt if ddt.dtype == dt.dtype else ddt.to(dt.dtype)
         dA = dA.to(A.dtype)
         dB = dB if dB.dtype == B.dtype else dB.to(B.dtype)

@@ -81,6 +81,21 @@ def test_parity_tensor(case):
     parity.compare(got, ref, torch.bfloat16, want_final=opts.get("return_final", True))
 
 
+def test_tensor_backward_without_saved_states():
+    """The C ABI backward recomputes the block-entry states when the caller kept none."""
+    from dest3d_b200 import issm_bwd, issm_fwd
+    inp, Q = _inputs((1, 200, 2, 36, 256, 1, 64), {}, BENCH_OPTS, torch.bfloat16)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    kw = dict(D=c["D"], z=c["z"], dt_bias=c["dt_bias"], initial_states=c["initial_states"], dt_softplus=True,
+              dt_limit=(1e-3, 1e-1), path="tensor")
+    out, out_x, fin, saved = issm_fwd(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, save_states=True, **kw)
+    assert saved is not None
+    g1 = issm_bwd(c["dout"], c["x"], c["dt"], c["A"], c["B"], c["C"], out_x, Q, dfinal_states=c["dfinal"], saved_states=saved, **kw)
+    g2 = issm_bwd(c["dout"], c["x"], c["dt"], c["A"], c["B"], c["C"], out_x, Q, dfinal_states=c["dfinal"], **kw)
+    for u, v in zip(g1, g2):
+        assert torch.equal(u, v)
+
+
 @pytest.mark.parametrize("name", ["tiny_f64", "ragged_heads_f64", "reftest_f32"])
 def test_golden_reference_vectors(name):
     """Outputs and gradients produced by the reference's own pure-PyTorch scan (tests/golden)."""
