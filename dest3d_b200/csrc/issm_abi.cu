@@ -61,6 +61,7 @@ extern "C" const char* issm_b200_strerror(int code) {
     case ISSM_ERR_UNSUPPORTED: return "requested path does not cover this shape";
     case ISSM_ERR_CUDA: return "a CUDA runtime call failed";
     case ISSM_ERR_DEVICE_STATUS: return "device status word is non-zero";
+    case ISSM_ERR_LIMIT: return "size exceeds the built-in scratch of the no-allocation entry point (hidden <= 1024)";
     default: return "unknown error code";
   }
 }

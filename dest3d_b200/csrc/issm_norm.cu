@@ -200,3 +200,61 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
   if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward of the gated norm for callers that must not allocate.
+//
+// Some hosts of this library cannot obtain device memory at call time: a plugin running inside an
+// inference server whose memory pool is sealed after start-up, a real-time loop where a device
+// allocation would stall every stream, or a binding in a language without a device allocator at
+// hand.  For them the per-block weight / bias gradient partials of k_norm_bwd live in the fixed
+// array below instead of a caller-provided workspace.  Every GPU that loads the library carries
+// the array (4.6 MiB) until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace issm {
+constexpr int kNoAllocMaxHidden = 1024;                 // widest row the built-in scratch covers
+constexpr int kNoAllocMaxBlocks = 148 * 4;              // == the largest grid norm_blocks() returns
+static __device__ __align__(256) float g_norm_scratch[2 * kNoAllocMaxBlocks * kNoAllocMaxHidden];
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per
+// device.  Looked up once per device (with that device current) and cached.
+static float* norm_scratch_address(int* rc) {
+  static std::atomic<float*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *rc = ISSM_ERR_CUDA; return nullptr; }
+  float* ptr = cache[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_norm_scratch) != cudaSuccess || !sym) {
+      (void)cudaGetLastError();
+      *rc = ISSM_ERR_CUDA;
+      return nullptr;
+    }
+    ptr = static_cast<float*>(sym);
+    cache[dev].store(ptr, std::memory_order_release);
+  }
+  *rc = ISSM_OK;
+  return ptr;
+}
+}  // namespace issm
+
+extern "C" int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* stream) {
+  int rc = norm_validate(p, true);
+  if (rc) return rc;
+  if (p->hidden > kNoAllocMaxHidden) return ISSM_ERR_LIMIT;
+  if (p->rows == 0) return ISSM_OK;
+  float* scratch = norm_scratch_address(&rc);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nblk = norm_blocks(*p);                      // <= kNoAllocMaxBlocks
+  const int rpb = (p->rows + nblk - 1) / nblk;
+  float* dwpart = scratch;
+  float* dbpart = scratch + (size_t)nblk * p->hidden;
+  const size_t smem = (size_t)2 * NORM_BWD_WARPS * p->hidden * sizeof(float);   // <= 32 KiB here
+  // every block writes its whole row of partials, so nothing in the scratch has to start at zero
+  if (p->io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  else ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
+  if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
+  return ISSM_OK;
+}

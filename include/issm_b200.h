@@ -46,7 +46,8 @@ enum {
   ISSM_ERR_ALIGN = 5,         /* pointer or stride alignment not met            */
   ISSM_ERR_UNSUPPORTED = 6,   /* requested path does not cover this shape       */
   ISSM_ERR_CUDA = 7,          /* a CUDA runtime call failed (launch, attribute) */
-  ISSM_ERR_DEVICE_STATUS = 8  /* reserved: device status word was non-zero      */
+  ISSM_ERR_DEVICE_STATUS = 8, /* reserved: device status word was non-zero      */
+  ISSM_ERR_LIMIT = 9          /* size beyond the built-in scratch of a no-allocation entry point */
 };
 
 /* One ISSM scan call (forward, or forward-recompute + backward).
@@ -143,6 +144,21 @@ int issm_b200_bwd(const issm_params* p, void* cuda_stream);
 size_t issm_b200_norm_workspace_bytes(const issm_norm_params* p, int pass);
 int issm_b200_norm_fwd(const issm_norm_params* p, void* cuda_stream);
 int issm_b200_norm_bwd(const issm_norm_params* p, void* cuda_stream);
+
+/* Backward of the gated norm WITHOUT any workspace (this entry point has no counterpart in the
+ * reference).  For hosts that cannot allocate device memory when they call: a server plugin whose
+ * memory pool is sealed after start-up, a latency-critical loop, or a language binding with no
+ * device allocator.  Same arguments and results as issm_b200_norm_bwd; `workspace` /
+ * `workspace_bytes` are ignored, and the per-block weight / bias gradient partials go to a fixed
+ * device array inside the library (4.6 MiB per GPU, held until the process exits).
+ *   - Limit: hidden <= 1024; a wider row returns ISSM_ERR_LIMIT and launches nothing.
+ *   - Neither this call nor anything it uses allocates or frees device memory.
+ *   - The first call on each device looks up the array's device address (the device of the call
+ *     must be current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the previous call left in
+ *     it (each call overwrites all it reads).  Two calls whose kernels overlap in time on the same
+ *     GPU - different streams, or different host threads - race on it: serialise them. */
+int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* cuda_stream);
 
 /* Number of kernel launches the library has enqueued since load (monotonic, process-wide);
  * used by the benchmark to report how many of its own kernels ran inside a timed region. */
