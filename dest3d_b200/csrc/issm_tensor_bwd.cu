@@ -158,15 +158,17 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
     if (kStageDt && !mbar_wait(barS, parity)) failed = true;
 
     // ---- pass 1: dt transform, clamp mask, cumulative log2-decay ----------------------------------
+    // (full blocks run the guard-free instantiation so that loads and rows interleave)
     float dtv[QB];
     float acc = 0.f, r = 0.f;
     uint32_t cm0 = 0, cm1 = 0;                          // bit l set: dt[l] was clamped (no gradient)
-    {
+    auto pass1 = [&](auto full) {
+      constexpr bool kFull = decltype(full)::value;
       const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
 #pragma unroll
       for (int l = 0; l < QB; ++l) {
         float v = 0.f;
-        if (l < rows) {
+        if (kFull || l < rows) {
           if (kStageDt) v = __bfloat162float(sdt[l * NT]);
           else v = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl + n);
           v += bias;
@@ -178,7 +180,8 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
         acc = fmaf(v, A2, acc);
         if (l == QB / 2 - 1) r = acc;
       }
-    }
+    };
+    if (rows == QB) pass1(std::true_type{}); else pass1(std::false_type{});
     const float alast = acc;
     if (fabsf(r) > 120.f || fabsf(alast - r) > 120.f) unsafe = 1;
 
@@ -217,24 +220,37 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
     if (!mbar_wait(barT, parity)) failed = true;
 
     // ---- pass 2: this column of Cd and Bd ---------------------------------------------------------
-    {
+    // C comes straight from global memory (L2-resident: shared by the heads of a sample), in batches of
+    // 16 independent loads
+    auto pass2 = [&](auto full) {
+      constexpr bool kFull = decltype(full)::value;
       uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
       uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
       const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+      const int64_t cstep = a.rev ? -a.C_sl : a.C_sl;
+      const bf16* __restrict__ crow = Cp + (int64_t)trow(a, row0) * a.C_sl;
       float ac = 0.f;
 #pragma unroll
-      for (int l = 0; l < QB; ++l) {
-        float cv = 0.f, bv = 0.f;
-        if (l < rows) {
-          cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + l) * a.C_sl]);
-          bv = __bfloat162float(sB[l * NT]);
+      for (int l0 = 0; l0 < QB; l0 += 16) {
+        bf16 cl[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          cl[j] = __float2bfloat16_rn(0.f);
+          if (kFull || l0 + j < rows) cl[j] = crow[(l0 + j) * cstep];
         }
-        ac = fmaf(dtv[l], A2, ac);
-        const uint32_t off = sw128_off(l, kcol);
-        *(bf16*)(cd_col + off) = __float2bfloat16_rn(cv * ex2f(ac - r));
-        *(bf16*)(bd_col + off) = __float2bfloat16_rn(bv * dtv[l] * ex2f(r - ac));
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int l = l0 + j;
+          float bv = 0.f;
+          if (kFull || l < rows) bv = __bfloat162float(sB[l * NT]);
+          ac = fmaf(dtv[l], A2, ac);
+          const uint32_t off = sw128_off(l, kcol);
+          *(bf16*)(cd_col + off) = __float2bfloat16_rn(__bfloat162float(cl[j]) * ex2f(ac - r));
+          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bv * dtv[l] * ex2f(r - ac));
+        }
       }
-    }
+    };
+    if (rows == QB) pass2(std::true_type{}); else pass2(std::false_type{});
 
     // ---- x and dy tiles, dz, dD partials -------------------------------------------------------------
 #pragma unroll
