@@ -4,16 +4,16 @@
 // the CTA owns state column n = t for the whole walk: it transforms dt, keeps the running
 // cumulative decay of its column, builds its column of every MMA operand, and owns TMEM lane
 // t % 128 of the running state S[n, p] (fp32).  Per sub-block (rows l, s; a = cumsum of dt*A
-// inside the block in log2 units, r = a at mid-block, a_last = a at the end):
-//   Cd[l,n] = C[l,n] 2^(a[l,n]-r[n])            Bd[s,n] = B[s,n] dt[s,n] 2^(r[n]-a[s,n])
+// inside the block in log2 units, relative to the block start; a_last = a at the block end):
+//   Cd[l,n] = C[l,n] 2^(a[l,n])                 Bd[s,n] = B[s,n] dt[s,n] 2^(-a[s,n])
 //   M[l,s]  = sum_n Cd[l,n] Bd[s,n]                                   tcgen05.mma  64 x 64, K = N
-//   Y[l,p]  = sum_n Cd[l,n] (2^r S)[p,n] + sum_{s<=l} M[l,s] x[s,p]   tcgen05.mma  64 x 48, K = N, then 64
-//   S[n,p] <- 2^(a_last-r) ( 2^r S[n,p] + sum_l Bd[l,n] x[l,p] )      tcgen05.mma 128 x 48, K = 64
+//   Y[l,p]  = sum_n Cd[l,n] S[p,n] + sum_{s<=l} M[l,s] x[s,p]         tcgen05.mma  64 x 48, K = N, then 64
+//   S[n,p] <- 2^(a_last) ( S[n,p] + sum_l Bd[l,n] x[l,p] )            tcgen05.mma 128 x 48, K = 64
 // This is the chunked algorithm of issm_triton/issm_combined.py:57-92 (dt transform + cumsum,
 // chunk state, state passing, C.A.B^T, chunk scan with D skip and silu(z) gate) with a 64-row
 // chunk and the state carried on chip instead of through HBM.  The decay inside the contraction is
-// factored through the mid-block reference so that every factor stays in range as long as the
-// half-block span of |a| is below 120 (log2 units); a violated block sets bit 1 of the status word.
+// factored through the block-start reference, so every factor stays in range as long as the span of
+// |a| over a 64-point block is below 120 (log2 units); a violated block sets bit 1 of the status word.
 // dt (bf16), B and C rows of the next block are prefetched into shared memory by bulk (TMA) copies
 // while the current block computes.
 #include "issm_tensor.cuh"
@@ -149,71 +149,25 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
       }
     }
 
+    // ---- running state: fp32 copy parked in TMEM for the accumulate MMA, bf16 copy as operand ------
+    tmem_st16(t_Srow, Srow);
+    tmem_st16(t_Srow + 16, Srow + 16);
+    tmem_st16(t_Srow + 32, Srow + 32);
+    if (!a.no_output) {
+#pragma unroll
+      for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, kcol)) = __float2bfloat16_rn(Srow[p]);
+    }
+    tmem_st_wait();
+
     if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
 
-    // ---- pass 1: dt transform, cumulative log2-decay, references -----------------------------
-    // (full blocks run the branch-free instantiation so that the unrolled rows interleave)
-    float dtv[QB];
-    float acc = 0.f, r = 0.f;
-    auto pass1 = [&](auto full) {
-      constexpr bool kFull = decltype(full)::value;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
-#pragma unroll
-      for (int l = 0; l < QB; ++l) {
-        float v = 0.f;
-        if (kFull || l < rows) {
-          if (kStageDt) v = __bfloat162float(sdt[l * NT]);
-          else v = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl + n);
-          v += bias;
-          if (a.softplus) v = softplus_fast(v);
-          v = fminf(fmaxf(v, a.dtmin), a.dtmax);
-        }
-        dtv[l] = v;
-        acc = fmaf(v, A2, acc);
-        if (l == QB / 2 - 1) r = acc;
-      }
-    };
-    if (rows == QB) pass1(std::true_type{}); else pass1(std::false_type{});
-    const float alast = acc;
-    if (fabsf(r) > 120.f || fabsf(alast - r) > 120.f) unsafe = 1;
+    // ---- one pass over the rows: dt transform, cumulative decay, this column of Cd and Bd --------
+    const float alast = build_operands<NT, TDT, kStageDt, true>(
+        a, rows, row0, kcol, (const bf16*)(smem + SM::kSdt) + n, dtp + n, (const bf16*)(smem + SM::kSB) + n,
+        (const bf16*)(smem + SM::kSC) + n, nullptr, smem + SM::kCd + (tid >> 6) * (QB * 128),
+        smem + SM::kBd + (tid >> 6) * (QB * 128), A2, bias);
+    if (fabsf(alast) > 120.f) unsafe = 1;
 
-    // ---- running state scaled to the mid-block reference: TMEM copy (fp32) and bf16 operand ---
-    {
-      const float er = ex2f(r);
-#pragma unroll
-      for (int p = 0; p < PP; ++p) Srow[p] *= er;
-      tmem_st16(t_Srow, Srow);
-      tmem_st16(t_Srow + 16, Srow + 16);
-      tmem_st16(t_Srow + 32, Srow + 32);
-      if (!a.no_output) {
-#pragma unroll
-        for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, kcol)) = __float2bfloat16_rn(Srow[p]);
-      }
-      tmem_st_wait();
-    }
-
-    // ---- pass 2: this column of Cd and Bd ------------------------------------------------------
-    auto pass2 = [&](auto full) {
-      constexpr bool kFull = decltype(full)::value;
-      uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
-      uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-      const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
-      float ac = 0.f;
-#pragma unroll
-      for (int l = 0; l < QB; ++l) {
-        float cv = 0.f, bv = 0.f;
-        if (kFull || l < rows) {
-          cv = __bfloat162float(sC[l * NT]);
-          bv = __bfloat162float(sB[l * NT]);
-        }
-        ac = fmaf(dtv[l], A2, ac);
-        const uint32_t off = sw128_off(l, kcol);
-        *(bf16*)(cd_col + off) = __float2bfloat16_rn(cv * ex2f(ac - r));
-        *(bf16*)(bd_col + off) = __float2bfloat16_rn(bv * dtv[l] * ex2f(r - ac));
-      }
-    };
-    if (rows == QB) pass2(std::true_type{}); else pass2(std::false_type{});
     // ---- x tile [l][p] (swizzled rows) and z tile ---------------------------------------------
 #pragma unroll
     for (int k = 0; k < XR; ++k) {
@@ -227,7 +181,7 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- MMAs: M = Cd Bd^T, Y = Cd (2^r S)^T, S += Bd^T x ---------------------------------------
+    // ---- MMAs: M = Cd Bd^T, Y = Cd S^T, S += Bd^T x ---------------------------------------
     if (tid == 0) {
       fence_after_sync();
       const uint32_t sb = smem_u32(smem);
@@ -287,7 +241,7 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
       tmem_ld16(t_Srow + 16, Srow + 16);
       tmem_ld16(t_Srow + 32, Srow + 32);
       tmem_ld_wait();
-      const float el = ex2f(alast - r);
+      const float el = ex2f(alast);
 #pragma unroll
       for (int p = 0; p < PP; ++p) Srow[p] *= el;
     }

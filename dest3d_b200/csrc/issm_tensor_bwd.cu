@@ -2,18 +2,18 @@
 //
 // Same decomposition as the forward (one CTA per (batch, head) stream, thread t = state column n,
 // 64-point sub-blocks), walked in REVERSE scan order while carrying G[n, p] = dLoss/dS (fp32, TMEM).
-// With Cd = C 2^(a-r), Bd = B dt 2^(r-a) (a: in-block cumsum of dt*A in log2 units, r = a at
-// mid-block), dy the gradient of the pre-skip / pre-gate output rows, S the state entering the
-// block (saved by the forward) and g' = 2^(a_last-r) G, S' = 2^r S, every O(rows x rows x states)
+// With Cd = C 2^a, Bd = B dt 2^-a (a: in-block cumsum of dt*A in log2 units, relative to the block
+// start), dy the gradient of the pre-skip / pre-gate output rows, S the state entering the
+// block (saved by the forward) and g' = 2^(a_last) G, every O(rows x rows x states)
 // term of issm_triton/issm_combined.py:95-179 becomes a tensor-core contraction:
 //   dM  = tril(dy x^T)                  64 x 64,  K = P      (issm_chunk_scan.py:828)
 //   M   = tril(Cd Bd^T)                 64 x 64,  K = N      (recomputed, issm_combined.py:141)
 //   BD^T[n,s] = sum_l Cd[l,n] dM[l,s] + sum_p g'[n,p] x[s,p]      128 x 64 per 128 states
-//   CD^T[n,l] = sum_s Bd[s,n] dM[l,s] + sum_p S'[n,p] dy[l,p]     128 x 64 per 128 states
+//   CD^T[n,l] = sum_s Bd[s,n] dM[l,s] + sum_p S[n,p] dy[l,p]      128 x 64 per 128 states
 //   dx[l,p]   = sum_n Bd[l,n] g'[n,p] + sum_t M[t,l] dy[t,p]       64 x 48
-//   G~[n,p]   = 2^(a_last-r) G[n,p] + sum_l Cd[l,n] dy[l,p]        128 x 48,  then G = 2^r G~
+//   G[n,p]   <- 2^(a_last) G[n,p] + sum_l Cd[l,n] dy[l,p]          128 x 48
 // and the per-(row, state) epilogue, done by the thread that owns the state column, is
-//   dC_h = 2^(a-r) CD,  dB_h = dt 2^(r-a) BD,  ddt_direct = B 2^(r-a) BD,
+//   dC_h = 2^a CD,  dB_h = dt 2^-a BD,  ddt_direct = B 2^-a BD,
 //   dacs = Cd CD - Bd BD,  ddA[l] = sum_{t>=l} dacs[t] + <S_next[n,:], G[n,:]>,
 //   ddt = (ddt_direct + ddA A) * [not clamped] * sigmoid(pre),  dA += ddA dt,  ddt_bias += ddt
 // (replacing issm_combined.py:451, issm_cabt_bmm.py:539, issm_chunk_scan.py:573/948,
@@ -155,46 +155,30 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
       }
     }
 
-    if (kStageDt && !mbar_wait(barS, parity)) failed = true;
-
-    // ---- pass 1: dt transform, clamp mask, cumulative log2-decay ----------------------------------
-    // (full blocks run the guard-free instantiation so that loads and rows interleave)
-    float dtv[QB];
-    float acc = 0.f, r = 0.f;
-    uint32_t cm0 = 0, cm1 = 0;                          // bit l set: dt[l] was clamped (no gradient)
-    auto pass1 = [&](auto full) {
-      constexpr bool kFull = decltype(full)::value;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
-#pragma unroll
-      for (int l = 0; l < QB; ++l) {
-        float v = 0.f;
-        if (kFull || l < rows) {
-          if (kStageDt) v = __bfloat162float(sdt[l * NT]);
-          else v = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl + n);
-          v += bias;
-          if (a.softplus) v = softplus_fast(v);
-          if (v < a.dtmin || v > a.dtmax) { if (l < 32) cm0 |= 1u << l; else cm1 |= 1u << (l - 32); }
-          v = fminf(fmaxf(v, a.dtmin), a.dtmax);
-        }
-        dtv[l] = v;
-        acc = fmaf(v, A2, acc);
-        if (l == QB / 2 - 1) r = acc;
-      }
-    };
-    if (rows == QB) pass1(std::true_type{}); else pass1(std::false_type{});
-    const float alast = acc;
-    if (fabsf(r) > 120.f || fabsf(alast - r) > 120.f) unsafe = 1;
-
-    // ---- state-gradient bookkeeping of this column -----------------------------------------------
-    // constant of the in-block reverse cumsum: <S leaving the block, G>
+    // ---- state bookkeeping that needs no decay: <S leaving the block, G>, and the S operand ----------
     float cst = 0.f;
 #pragma unroll
     for (int q = 0; q < PP / 2; ++q) {
       cst = fmaf(__uint_as_float(Snext[q] << 16), G[2 * q], cst);
       cst = fmaf(__uint_as_float(Snext[q] & 0xffff0000u), G[2 * q + 1], cst);
     }
+#pragma unroll
+    for (int c = 0; c < PP / 8; ++c)
+      *(uint4*)(smem + SM::kSop + c * (NT * 16) + tid * 16) = make_uint4(Scur[c * 4], Scur[c * 4 + 1], Scur[c * 4 + 2], Scur[c * 4 + 3]);
+
+    if (kStageDt && !mbar_wait(barS, parity)) failed = true;
+    if (!mbar_wait(barT, parity)) failed = true;
+
+    // ---- one pass over the rows: dt transform, cumulative decay, this column of Cd and Bd ----------
+    // (C comes straight from global memory: L2-resident, shared by the heads of a sample)
+    const float alast = build_operands<NT, TDT, kStageDt, false>(
+        a, rows, row0, kcol, (const bf16*)(smem + SM::kSdt) + n, dtp + n, (const bf16*)(smem + SM::kSB) + n,
+        nullptr, Cp, smem + SM::kCd + (tid >> 6) * (QB * 128), smem + SM::kBd + (tid >> 6) * (QB * 128), A2, bias);
+    if (fabsf(alast) > 120.f) unsafe = 1;
+
+    // ---- g' = 2^(a_last) G: fp32 copy parked in TMEM for the accumulate MMA, bf16 copy as operand ----
     {
-      const float eg = ex2f(alast - r), es = ex2f(r);
+      const float eg = ex2f(alast);
       float gs[PP];
 #pragma unroll
       for (int p = 0; p < PP; ++p) gs[p] = G[p] * eg;
@@ -202,55 +186,12 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
       tmem_st16(t_Grow + 16, gs + 16);
       tmem_st16(t_Grow + 32, gs + 32);
 #pragma unroll
-      for (int c = 0; c < PP / 8; ++c) {
+      for (int c = 0; c < PP / 8; ++c)
         *(uint4*)(smem + SM::kGop + sw128_chunk(tid, c)) =
             make_uint4(pack_bf16(gs[c * 8], gs[c * 8 + 1]), pack_bf16(gs[c * 8 + 2], gs[c * 8 + 3]),
                        pack_bf16(gs[c * 8 + 4], gs[c * 8 + 5]), pack_bf16(gs[c * 8 + 6], gs[c * 8 + 7]));
-        uint32_t sp[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t v = Scur[c * 4 + j];
-          sp[j] = pack_bf16(__uint_as_float(v << 16) * es, __uint_as_float(v & 0xffff0000u) * es);
-        }
-        *(uint4*)(smem + SM::kSop + c * (NT * 16) + tid * 16) = make_uint4(sp[0], sp[1], sp[2], sp[3]);
-      }
       tmem_st_wait();
     }
-
-    if (!mbar_wait(barT, parity)) failed = true;
-
-    // ---- pass 2: this column of Cd and Bd ---------------------------------------------------------
-    // C comes straight from global memory (L2-resident: shared by the heads of a sample), in batches of
-    // 16 independent loads
-    auto pass2 = [&](auto full) {
-      constexpr bool kFull = decltype(full)::value;
-      uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
-      uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-      const int64_t cstep = a.rev ? -a.C_sl : a.C_sl;
-      const bf16* __restrict__ crow = Cp + (int64_t)trow(a, row0) * a.C_sl;
-      float ac = 0.f;
-#pragma unroll
-      for (int l0 = 0; l0 < QB; l0 += 16) {
-        bf16 cl[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          cl[j] = __float2bfloat16_rn(0.f);
-          if (kFull || l0 + j < rows) cl[j] = crow[(l0 + j) * cstep];
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int l = l0 + j;
-          float bv = 0.f;
-          if (kFull || l < rows) bv = __bfloat162float(sB[l * NT]);
-          ac = fmaf(dtv[l], A2, ac);
-          const uint32_t off = sw128_off(l, kcol);
-          *(bf16*)(cd_col + off) = __float2bfloat16_rn(__bfloat162float(cl[j]) * ex2f(ac - r));
-          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bv * dtv[l] * ex2f(r - ac));
-        }
-      }
-    };
-    if (rows == QB) pass2(std::true_type{}); else pass2(std::false_type{});
 
     // ---- x and dy tiles, dz, dD partials -------------------------------------------------------------
 #pragma unroll
@@ -294,7 +235,6 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
         }
       mma_commit(bar1);
     }
-    if (warp == 1 && blk > 0) prefetch_dt(blk - 1);       // every thread is past pass 1
     if (!mbar_wait(bar1, parity)) failed = true;
     fence_after_sync();
 
@@ -369,41 +309,58 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
 
     // ---- epilogue 2 ------------------------------------------------------------------------------------
     if (!failed) {
-      // (a) the owner of state column n: dB_h, dC_h, ddt, in-block reverse cumsum
+      // (a) the owner of state column n: dB_h, dC_h, ddt, in-block reverse cumsum of dacs
       const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
       const uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
       const uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
-      float run = cst;
-      float ac = alast;
-#pragma unroll
-      for (int ch = 3; ch >= 0; --ch) {
+      float total = 0.f;                                  // sum over the block of dacs = Cd CD - Bd BD
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
         float bdv[16], cdv[16];
         tmem_ld16(t_BDrow + ch * 16, bdv);
         tmem_ld16(t_CDrow + ch * 16, cdv);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 15; j >= 0; --j) {
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t off = (uint32_t)((ch * 16 + j) * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          total = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], total);
+          total = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], total);
+        }
+      }
+      float prefix = 0.f, ac = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        float bdv[16], cdv[16];
+        tmem_ld16(t_BDrow + ch * 16, bdv);
+        tmem_ld16(t_CDrow + ch * 16, cdv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
           const int l = ch * 16 + j;
-          const float e1 = ex2f(ac - r), e2 = ex2f(r - ac);
-          const float bd = e2 * bdv[j], cd = e1 * cdv[j];
-          const uint32_t off = sw128_off(l, kcol);
-          const float cdo = __bfloat162float(*(const bf16*)(cd_col + off));
-          const float bdo = __bfloat162float(*(const bf16*)(bd_col + off));
-          run += cdo * cdv[j] - bdo * bdv[j];
-          const float dtl = dtv[l];
-          float gd = fmaf(run, Anat, __bfloat162float(sB[l * NT]) * bd);
-          const bool clamped = l < 32 ? (cm0 >> l) & 1u : (cm1 >> (l - 32)) & 1u;
+          const bool valid = l < rows;
+          const int64_t mr = trow(a, row0 + min(l, rows - 1));
+          const float raw = kStageDt ? __bfloat162float(sdt[l * NT]) : ldf(dtp + mr * a.dt_sl + n);
+          bool clamped = false;
+          const float dtl = valid ? dt_transform(a, raw, bias, clamped) : 0.f;
+          ac = fmaf(dtl, A2, ac);
+          const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
+          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
+                             __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
+          const float ddA = cst + total - prefix;          // sum of dacs over rows >= l, plus <S_next, G>
+          prefix += dacs;
+          float gd = fmaf(ddA, Anat, __bfloat162float(sB[l * NT]) * bd);
           if (clamped) gd = 0.f;
           else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
-          dAacc = fmaf(run, dtl, dAacc);
-          if (l < rows) {
+          dAacc = fmaf(ddA, dtl, dAacc);
+          if (valid) {
             dbacc += gd;
-            const size_t o = (((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.N + n;
+            const size_t o = (((size_t)b * a.L + mr) * a.H + h) * a.N + n;
             stf((TDT*)a.ddt + o, gd);
             a.dBh[o] = __float2bfloat16_rn(dtl * bd);
             a.dCh[o] = __float2bfloat16_rn(cd);
           }
-          ac = fmaf(-dtl, A2, ac);
         }
       }
       // (b) new state gradient
@@ -413,9 +370,8 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
         tmem_ld16(t_Grow + 16, gs + 16);
         tmem_ld16(t_Grow + 32, gs + 32);
         tmem_ld_wait();
-        const float er = ex2f(r);
 #pragma unroll
-        for (int p = 0; p < PP; ++p) G[p] = gs[p] * er;
+        for (int p = 0; p < PP; ++p) G[p] = gs[p];
       }
 #pragma unroll
       for (int q = 0; q < PP / 2; ++q) Snext[q] = Scur[q];
@@ -435,7 +391,8 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
-    if (warp == 2 && blk > 0) prefetch_B(blk - 1);        // every thread is past its B staging reads
+    if (warp == 1 && blk > 0) prefetch_dt(blk - 1);       // every thread is past its dt / B staging reads
+    if (warp == 2 && blk > 0) prefetch_B(blk - 1);
 
     // ---- coalesced dx store: dx = tile + D dy --------------------------------------------------------
 #pragma unroll
