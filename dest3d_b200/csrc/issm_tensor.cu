@@ -31,24 +31,36 @@ struct FwdSmem {
   static constexpr int kSB = kSdt + QB * NT * 2;
   static constexpr int kSC = kSB + QB * NT * 2;
   static constexpr int kY = kSC + QB * NT * 2;          // [64][PP] float: pre-skip, pre-gate output rows
-  static constexpr int kBars = kY + QB * PP * 4;
+  static constexpr int kAsum = kY + QB * PP * 4;        // [2][NT] float: per-half sums of dt*A
+  static constexpr int kBars = kAsum + 2 * NT * 4;
   static constexpr int kTotal = kBars + 64;
 };
 
+// Thread layout: 2*NT column threads + one service warp.  Column thread (n = tid % NT, half = tid / NT)
+// owns rows [32 half, 32 half + 32) of state column n in the operand pass and columns
+// [24 half, 24 half + 24) of TMEM lane n of the running state.  The service warp issues every MMA and
+// every bulk prefetch.
 template <int NT, typename TDT>
-__global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
+__global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
+  constexpr int NTH = 2 * NT;                           // column threads
+  constexpr int XR = (QB * PP + NTH - 1) / NTH;         // x / z tile elements per thread
+  constexpr int HP = PP / 2;                            // state columns per thread
+  constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* barA = (uint64_t*)(smem + SM::kBars);
   uint64_t* barB = barA + 1;
   uint64_t* barS = barA + 2;
   uint32_t* tmem_holder = (uint32_t*)(barA + 3);
+  float* sAsum = (float*)(smem + SM::kAsum);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_col = tid < NTH;
+  const bool is_svc = !is_col;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
-  const int n = tid;                                   // NT == N
+  const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
   const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
   const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg;
@@ -59,7 +71,7 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
   const int nblk = (a.L + QB - 1) / QB;
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
-  for (int i = tid; i < (SM::kSdt - SM::kSop) / 16; i += NT) ((uint4*)(smem + SM::kSop))[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (SM::kSdt - SM::kSop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kSop))[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
   fence_before_sync();
@@ -68,9 +80,9 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
   const uint32_t tmem = *tmem_holder;
   const uint32_t t_M = tmem, t_Y = tmem + 64;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const uint32_t t_Srow = tmem + lane_base + 128 + (tid >> 7) * PP;   // this thread's TMEM lane
+  const uint32_t t_S = tmem + lane_base + 128 + (n >> 7) * PP + half * HP;   // this thread's part of TMEM lane n
 
-  // bulk prefetch of the dt / B / C rows of block `blk` (one warp issues, completion on barS)
+  // bulk prefetch of the dt / B / C rows of block `blk` (service warp, completion on barS)
   auto prefetch = [&](int blk) {
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * (kStageDt ? 3 : 2));
@@ -82,34 +94,55 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
       bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
     }
   };
-  if (warp == 1) prefetch(0);
+  if (is_svc) prefetch(0);
 
-  float Srow[PP];
+  uint8_t* sop_col = smem + SM::kSop + (n >> 6) * (PP * 128);
+  const int kcol = n & 63;
+  bf16* savep = a.saved ? a.saved + ((((size_t)b * a.H + h) * (nblk + 1)) * a.N + n) * PP + half * HP : nullptr;
+  // bf16 operand copy and saved copy of this thread's HP state values
+  auto publish_state = [&](const float* sc, int blk_index) {
+    if (!a.no_output) {
 #pragma unroll
-  for (int p = 0; p < PP; ++p) Srow[p] = 0.f;
-  if (a.has_init) {
-    const bf16* __restrict__ ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n;
+      for (int j = 0; j < HP; ++j) *(bf16*)(sop_col + sw128_off(half * HP + j, kcol)) = __float2bfloat16_rn(sc[j]);
+    }
+    if (savep) {
+      uint4* dst = (uint4*)(savep + (size_t)blk_index * a.N * PP);
 #pragma unroll
-    for (int p = 0; p < PP; ++p)
-      if (p < a.P) Srow[p] = __bfloat162float(ip[(size_t)p * a.N]);
+      for (int c = 0; c < HP / 8; ++c)
+        dst[c] = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
+                            pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
+    }
+  };
+  if (is_col) {                                          // initial state -> TMEM, operand, saved[0]
+    float sc[HP];
+#pragma unroll
+    for (int j = 0; j < HP; ++j) sc[j] = 0.f;
+    if (a.has_init) {
+      const bf16* __restrict__ ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n;
+#pragma unroll
+      for (int j = 0; j < HP; ++j)
+        if (half * HP + j < a.P) sc[j] = __bfloat162float(ip[(size_t)(half * HP + j) * a.N]);
+    }
+    tmem_st16(t_S, sc);
+    tmem_st8(t_S + 16, sc + 16);
+    publish_state(sc, 0);
+    tmem_st_wait();
   }
-  uint8_t* sop_col = smem + SM::kSop + (tid >> 6) * (PP * 128);
-  const int kcol = tid & 63;
-  bf16* savep = a.saved ? a.saved + ((((size_t)b * a.H + h) * (nblk + 1)) * a.N + n) * PP : nullptr;
 
-  bool failed = false;
-  uint32_t unsafe = 0;
-  int prev_rows = 0, prev_row0 = 0;
-  const int npt = (QB * a.P + NT - 1) / NT;            // x / z tile elements per thread
-  constexpr int XR = (QB * PP + NT - 1) / NT;
-  bf16 xprev[XR], zprev[XR];                           // this thread's x / z elements of the previous block
+  // tile element k of this thread is (row lrow[k], head-dim index pcol[k]); fixed for the whole walk
+  int tl[XR];
+#pragma unroll
+  for (int k = 0; k < XR; ++k) {
+    const int i = tid + k * NTH;
+    tl[k] = (is_col && i < QB * a.P) ? (((i / a.P) << 8) | (i % a.P)) : -1;
+  }
+  bf16 xprev[XR], zprev[XR];
   // out = (y + D x) * silu(z) for the tile elements this thread loaded; coalesced over p
   auto store_tile = [&](int t_row0, int t_rows) {
 #pragma unroll
     for (int k = 0; k < XR; ++k) {
-      const int i = tid + k * NT;
-      if (k < npt && i < t_rows * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
+      const int l = tl[k] >> 8, p = tl[k] & 255;
+      if (tl[k] >= 0 && l < t_rows) {
         float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
         if (a.has_D) y = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : __ldg(a.D + h), __bfloat162float(xprev[k]), y);
         const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
@@ -122,138 +155,169 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
       }
     }
   };
+
+  bool failed = false;
+  uint32_t unsafe = 0;
+  int prev_rows = 0, prev_row0 = 0;
   for (int blk = 0; blk < nblk; ++blk) {
     const int row0 = blk * QB;
     const int rows = min(QB, a.L - row0);
     const uint32_t parity = blk & 1;
-
-    if (savep) {                                       // state entering this block, for the backward
-      uint4* dst = (uint4*)(savep + (size_t)blk * a.N * PP);
-#pragma unroll
-      for (int c = 0; c < PP / 8; ++c)
-        dst[c] = make_uint4(pack_bf16(Srow[c * 8], Srow[c * 8 + 1]), pack_bf16(Srow[c * 8 + 2], Srow[c * 8 + 3]),
-                            pack_bf16(Srow[c * 8 + 4], Srow[c * 8 + 5]), pack_bf16(Srow[c * 8 + 6], Srow[c * 8 + 7]));
-    }
-
-    // ---- x and z tiles: coalesced global loads now, shared-memory stores after pass 1 --------
+    float alast = 0.f;
     bf16 xr[XR], zr[XR];
+
+    if (is_col) {
+      // ---- x and z tile elements: coalesced global loads now, shared-memory stores after the pass ----
 #pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      xr[k] = zr[k] = __float2bfloat16_rn(0.f);
-      const int i = tid + k * NT;
-      if (k < npt && i < rows * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
-        const int64_t mr = trow(a, row0 + l);
-        xr[k] = xp[mr * a.x_sl + p];
-        if (zp) zr[k] = zp[mr * a.z_sl + p];
+      for (int k = 0; k < XR; ++k) {
+        xr[k] = zr[k] = __float2bfloat16_rn(0.f);
+        const int l = tl[k] >> 8, p = tl[k] & 255;
+        if (tl[k] >= 0 && l < rows) {
+          const int64_t mr = trow(a, row0 + l);
+          xr[k] = xp[mr * a.x_sl + p];
+          if (zp) zr[k] = zp[mr * a.z_sl + p];
+        }
       }
-    }
+      if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
 
-    // ---- running state: fp32 copy parked in TMEM for the accumulate MMA, bf16 copy as operand ------
-    tmem_st16(t_Srow, Srow);
-    tmem_st16(t_Srow + 16, Srow + 16);
-    tmem_st16(t_Srow + 32, Srow + 32);
-    if (!a.no_output) {
+      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
+      float dtv[32];
+      float asum = 0.f;
+      {
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
 #pragma unroll
-      for (int p = 0; p < PP; ++p) *(bf16*)(sop_col + sw128_off(p, kcol)) = __float2bfloat16_rn(Srow[p]);
-    }
-    tmem_st_wait();
-
-    if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
-
-    // ---- one pass over the rows: dt transform, cumulative decay, this column of Cd and Bd --------
-    const float alast = build_operands<NT, TDT, kStageDt, true>(
-        a, rows, row0, kcol, (const bf16*)(smem + SM::kSdt) + n, dtp + n, (const bf16*)(smem + SM::kSB) + n,
-        (const bf16*)(smem + SM::kSC) + n, nullptr, smem + SM::kCd + (tid >> 6) * (QB * 128),
-        smem + SM::kBd + (tid >> 6) * (QB * 128), A2, bias);
-    if (fabsf(alast) > 120.f) unsafe = 1;
-
-    // ---- x tile [l][p] (swizzled rows) and z tile ---------------------------------------------
-#pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      const int i = tid + k * NT;
-      if (k < npt && i < QB * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
-        *(bf16*)(smem + SM::kX + sw128_off(l, p)) = xr[k];
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const float raw = kStageDt ? __bfloat162float(sdt[l * NT])
+                                     : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
+          bool clamped;
+          const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
+          dtv[j] = v;
+          asum = fmaf(v, A2, asum);
+        }
       }
+      sAsum[half * NT + n] = asum;
+      named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
+      const float a0 = sAsum[n];
+      alast = a0 + sAsum[NT + n];
+      if (fabsf(alast) > 120.f) unsafe = 1;
+
+      // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
+      {
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+        const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
+        float acc = half ? a0 : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const bool valid = l < rows;
+          acc = fmaf(dtv[j], A2, acc);
+          const float cd = valid ? __bfloat162float(sC[l * NT]) * ex2f(acc) : 0.f;
+          const float bd = valid ? __bfloat162float(sB[l * NT]) * dtv[j] * ex2f(-acc) : 0.f;
+          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+        }
+      }
+      // ---- x tile [l][p] (swizzled rows) --------------------------------------------------------------
+#pragma unroll
+      for (int k = 0; k < XR; ++k)
+        if (tl[k] >= 0) *(bf16*)(smem + SM::kX + sw128_off(tl[k] >> 8, tl[k] & 255)) = xr[k];
+      fence_async_smem();
     }
-    fence_async_smem();
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- MMAs: M = Cd Bd^T, Y = Cd S^T, S += Bd^T x ---------------------------------------
-    if (tid == 0) {
-      fence_after_sync();
-      const uint32_t sb = smem_u32(smem);
-      if (!a.no_output) {
+    // ---- MMAs: M = Cd Bd^T, Y = Cd S^T, S += Bd^T x (service warp) ------------------------------------
+    if (is_svc) {
+      if (lane == 0) {
+        fence_after_sync();
+        const uint32_t sb = smem_u32(smem);
+        if (!a.no_output) {
 #pragma unroll
-        for (int at = 0; at < NT / 64; ++at)
+          for (int at = 0; at < NT / 64; ++at)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t ko = at * (QB * 128) + kk * 32;
-            mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
-            mma_bf16(t_Y, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kSop + at * (PP * 128) + kk * 32),
-                     idesc_bf16(64, PP), (at | kk) != 0);
-          }
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t ko = at * (QB * 128) + kk * 32;
+              mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
+              mma_bf16(t_Y, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kSop + at * (PP * 128) + kk * 32),
+                       idesc_bf16(64, PP), (at | kk) != 0);
+            }
+        }
+#pragma unroll
+        for (int sl = 0; sl < NT / 128; ++sl)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16(tmem + 128 + sl * PP, desc_sw128_mn(sb + SM::kBd + sl * (2 * QB * 128) + kk * 2048, QB * 128),
+                     desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128), idesc_bf16(128, PP, 1, 1), 1);
+        mma_commit(barA);
       }
-#pragma unroll
-      for (int sl = 0; sl < NT / 128; ++sl)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_bf16(tmem + 128 + sl * PP, desc_sw128_mn(sb + SM::kBd + sl * (2 * QB * 128) + kk * 2048, QB * 128),
-                   desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128), idesc_bf16(128, PP, 1, 1), 1);
-      mma_commit(barA);
+      __syncwarp();
+      if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
     }
-    if (warp == 1 && blk + 1 < nblk) prefetch(blk + 1);  // every thread is past its staging reads
 
-    // ---- coalesced store of the previous block's output tile ----------------------------------
-    if (blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
+    if (is_col) {
+      // ---- coalesced store of the previous block's output tile ----------------------------------------
+      if (blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
 #pragma unroll
-    for (int k = 0; k < XR; ++k) { xprev[k] = xr[k]; zprev[k] = zr[k]; }
+      for (int k = 0; k < XR; ++k) { xprev[k] = xr[k]; zprev[k] = zr[k]; }
 
-    if (!mbar_wait(barA, parity)) failed = true;
-    fence_after_sync();
+      if (!mbar_wait(barA, parity)) failed = true;
+      fence_after_sync();
 
-    // ---- epilogue 1: masked M -> bf16 operand; new state -> registers ---------------------------
-    if (warp < 4 && !a.no_output && !failed) {
-      float mv[64];
-      tmem_ld16(t_M + lane_base, mv);
-      tmem_ld16(t_M + lane_base + 16, mv + 16);
-      tmem_ld16(t_M + lane_base + 32, mv + 32);
-      tmem_ld16(t_M + lane_base + 48, mv + 48);
-      tmem_ld_wait();
-      if (lane < 16) {
-        const int l = warp * 16 + lane;
+      // ---- epilogue 1a: masked M -> bf16 operand (every warp takes 16-column groups of its 16 rows) ----
+      if (!a.no_output && !failed) {
+        const int l = (warp & 3) * 16 + lane;
+        for (int c16 = (warp >> 2) % NCG; c16 < 4; c16 += NCG) {
+          float mv[16];
+          tmem_ld16(t_M + lane_base + c16 * 16, mv);
+          tmem_ld_wait();
+          if (lane < 16) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t pk[4];
+            for (int c = 0; c < 2; ++c) {
+              uint32_t pk[4];
 #pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            const int s = c * 8 + j;
-            pk[j >> 1] = pack_bf16(s <= l ? mv[s] : 0.f, s + 1 <= l ? mv[s + 1] : 0.f);
+              for (int j = 0; j < 8; j += 2) {
+                const int s = c16 * 16 + c * 8 + j;
+                pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
+              }
+              *(uint4*)(smem + SM::kMm + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
           }
-          *(uint4*)(smem + SM::kMm + sw128_chunk(l, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
       }
-    }
-    if (!failed) {
-      tmem_ld16(t_Srow, Srow);
-      tmem_ld16(t_Srow + 16, Srow + 16);
-      tmem_ld16(t_Srow + 32, Srow + 32);
-      tmem_ld_wait();
-      const float el = ex2f(alast);
+      // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
+      if (!failed) {
+        float sc[HP];
+        tmem_ld16(t_S, sc);
+        tmem_ld8(t_S + 16, sc + 16);
+        tmem_ld_wait();
+        const float el = ex2f(alast);
 #pragma unroll
-      for (int p = 0; p < PP; ++p) Srow[p] *= el;
+        for (int j = 0; j < HP; ++j) sc[j] *= el;
+        tmem_st16(t_S, sc);
+        tmem_st8(t_S + 16, sc + 16);
+        publish_state(sc, blk + 1);
+        if (blk == nblk - 1 && a.want_final) {
+          float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
+#pragma unroll
+          for (int j = 0; j < HP; ++j)
+            if (half * HP + j < a.P) fp[(size_t)(half * HP + j) * a.N] = sc[j];
+        }
+        tmem_st_wait();
+      }
+      fence_async_smem();
     }
-    fence_async_smem();
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
     prev_rows = rows;
     prev_row0 = row0;
     if (a.no_output) continue;
 
-    // ---- Y += tril(M) x ------------------------------------------------------------------------
-    if (tid == 0) {
+    // ---- Y += tril(M) x ------------------------------------------------------------------------------
+    if (is_svc && lane == 0) {
       fence_after_sync();
       const uint32_t sb = smem_u32(smem);
 #pragma unroll
@@ -262,41 +326,29 @@ __global__ void __launch_bounds__(NT, 1) k_fwd_tensor(const TArgs a) {
                  idesc_bf16(64, PP, 0, 1), 1);
       mma_commit(barB);
     }
-    if (!mbar_wait(barB, parity)) failed = true;
-    fence_after_sync();
-
-    // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) --
-    if (warp < 4 && !failed) {
-      float yv[PP];
-      tmem_ld16(t_Y + lane_base, yv);
-      tmem_ld16(t_Y + lane_base + 16, yv + 16);
-      tmem_ld16(t_Y + lane_base + 32, yv + 32);
-      tmem_ld_wait();
-      const int l = warp * 16 + lane;
-      if (lane < 16) {
-        float4* dst = (float4*)(smem + SM::kY + l * PP * 4);
+    if (is_col) {
+      if (!mbar_wait(barB, parity)) failed = true;
+      fence_after_sync();
+      // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) ----
+      if (!failed) {
+        const int l = (warp & 3) * 16 + lane;
+        for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
+          float yv[16];
+          tmem_ld16(t_Y + lane_base + c16 * 16, yv);
+          tmem_ld_wait();
+          if (lane < 16) {
+            float4* dst = (float4*)(smem + SM::kY + (l * PP + c16 * 16) * 4);
 #pragma unroll
-        for (int c = 0; c < PP / 4; ++c) dst[c] = make_float4(yv[c * 4], yv[c * 4 + 1], yv[c * 4 + 2], yv[c * 4 + 3]);
+            for (int c = 0; c < 4; ++c) dst[c] = make_float4(yv[c * 4], yv[c * 4 + 1], yv[c * 4 + 2], yv[c * 4 + 3]);
+          }
+        }
       }
     }
     fence_before_sync();
   }
 
   __syncthreads();
-  if (!failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // output tile of the last block
-  if (!failed && a.want_final) {
-    float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
-#pragma unroll
-    for (int p = 0; p < PP; ++p)
-      if (p < a.P) fp[(size_t)p * a.N] = Srow[p];
-  }
-  if (!failed && savep) {
-    uint4* dst = (uint4*)(savep + (size_t)nblk * a.N * PP);
-#pragma unroll
-    for (int c = 0; c < PP / 8; ++c)
-      dst[c] = make_uint4(pack_bf16(Srow[c * 8], Srow[c * 8 + 1]), pack_bf16(Srow[c * 8 + 2], Srow[c * 8 + 3]),
-                          pack_bf16(Srow[c * 8 + 4], Srow[c * 8 + 5]), pack_bf16(Srow[c * 8 + 6], Srow[c * 8 + 7]));
-  }
+  if (is_col && !failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
     if (unsafe) atomicOr(a.status, 2);
@@ -355,7 +407,7 @@ static int launch_fwd(const TArgs& a, cudaStream_t s) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), NT, smem, s, a);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 32, smem, s, a);
   return ISSM_OK;
 }
 
