@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstdio>
 
 #include "../../include/issm_b200.h"
 
@@ -20,7 +21,10 @@ extern std::atomic<uint64_t> g_launches;
   do {                                                                              \
     kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);                     \
     issm::g_launches.fetch_add(1, std::memory_order_relaxed);                       \
-    if (cudaPeekAtLastError() != cudaSuccess) { (void)cudaGetLastError(); return ISSM_ERR_CUDA; } \
+    if (cudaPeekAtLastError() != cudaSuccess) {                                     \
+      fprintf(stderr, "issm_b200: launch of %s failed: %s\n", #kernel, cudaGetErrorString(cudaGetLastError())); \
+      return ISSM_ERR_CUDA;                                                         \
+    }                                                                               \
   } while (0)
 
 __device__ __forceinline__ float ldf(const float* p) { return *p; }

@@ -23,9 +23,10 @@ namespace issm {
 template <int NT>
 struct FwdSmem {
   static constexpr int kCd = 0;                         // [NT/64 atoms][64 l][128 B]
-  static constexpr int kBd = kCd + NT * 128;            // same
-  static constexpr int kSop = kBd + NT * 128;           // [NT/64 atoms][PP p][128 B]
-  static constexpr int kX = kSop + NT * (PP * 2);       // [64 l][128 B]   (p in the row)
+  static constexpr int kAtomB = (QB + PP) * 128;        // per 64-state atom: 64 rows of Bd, then PP rows of the state operand,
+  static constexpr int kBd = kCd + NT * 128;            //   so that M and the state term of Y come out of ONE 64 x 112 MMA
+  static constexpr int kSop = kBd + QB * 128;
+  static constexpr int kX = kBd + (NT / 64) * kAtomB;   // [64 l][128 B]   (p in the row)
   static constexpr int kMm = kX + QB * 128;             // [64 l][128 B]   (s in the row)
   static constexpr int kSdt = kMm + QB * 128;           // staging: [64][NT] bf16
   static constexpr int kSB = kSdt + QB * NT * 2;
@@ -36,16 +37,18 @@ struct FwdSmem {
   static constexpr int kTotal = kBars + 64;
 };
 
-// Thread layout: 2*NT column threads + one service warp.  Column thread (n = tid % NT, half = tid / NT)
-// owns rows [32 half, 32 half + 32) of state column n in the operand pass and columns
+// Thread layout: 2*NT column threads, one service warp, three tile-I/O warps (registers are allocated in
+// groups of four warps, so the service warp brings three more along).  Column thread (n = tid % NT,
+// half = tid / NT) owns rows [32 half, 32 half + 32) of state column n in the operand pass and columns
 // [24 half, 24 half + 24) of TMEM lane n of the running state.  The service warp issues every MMA and
-// every bulk prefetch.
+// every bulk prefetch.  The I/O warps load the x / z rows of the block, build the x operand tile and
+// store the previous block's output rows (D skip and gate applied) with coalesced accesses.
 template <int NT, typename TDT>
-__global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;                           // column threads
-  constexpr int XR = (QB * PP + NTH - 1) / NTH;         // x / z tile elements per thread
+  constexpr int NIO = 96;                               // tile-I/O threads
   constexpr int HP = PP / 2;                            // state columns per thread
   constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
@@ -58,7 +61,9 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_col = tid < NTH;
-  const bool is_svc = !is_col;
+  const bool is_svc = warp == NTH / 32;
+  const bool is_io = tid >= NTH + 32;
+  const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
   const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
@@ -71,7 +76,7 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
   const int nblk = (a.L + QB - 1) / QB;
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
-  for (int i = tid; i < (SM::kSdt - SM::kSop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kSop))[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (SM::kSdt - SM::kBd) / 16; i += blockDim.x) ((uint4*)(smem + SM::kBd))[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
   fence_before_sync();
@@ -82,21 +87,30 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   const uint32_t t_S = tmem + lane_base + 128 + (n >> 7) * PP + half * HP;   // this thread's part of TMEM lane n
 
-  // bulk prefetch of the dt / B / C rows of block `blk` (service warp, completion on barS)
+  // bulk prefetch of the dt / B / C rows of block `blk` (service warp, completion on barS).  When the
+  // B / C rows are adjacent in memory a whole tile is ONE copy; a reversed scan then finds row l of
+  // the block at staged row rows-1-l (see srow below).
   auto prefetch = [&](int blk) {
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * (kStageDt ? 3 : 2));
     __syncwarp();
+    if (a.bc_contig) {
+      const int64_t m0 = a.rev ? a.L - row0 - rows : row0;          // lowest memory row of the tile
+      if (lane == 0) bulk_g2s(smem + SM::kSB, Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2, barS);
+      if (lane == 1) bulk_g2s(smem + SM::kSC, Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2, barS);
+    }
     for (int l = lane; l < rows; l += 32) {
       const int64_t mr = trow(a, row0 + l);
       if (kStageDt) bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + mr * a.dt_sl, NT * 2, barS);
-      bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + mr * a.B_sl, NT * 2, barS);
-      bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
+      if (!a.bc_contig) {
+        bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + mr * a.B_sl, NT * 2, barS);
+        bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
+      }
     }
   };
   if (is_svc) prefetch(0);
 
-  uint8_t* sop_col = smem + SM::kSop + (n >> 6) * (PP * 128);
+  uint8_t* sop_col = smem + SM::kSop + (n >> 6) * SM::kAtomB;
   const int kcol = n & 63;
   bf16* savep = a.saved ? a.saved + ((((size_t)b * a.H + h) * (nblk + 1)) * a.N + n) * PP + half * HP : nullptr;
   // bf16 operand copy and saved copy of this thread's HP state values
@@ -129,32 +143,53 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
     tmem_st_wait();
   }
 
-  // tile element k of this thread is (row lrow[k], head-dim index pcol[k]); fixed for the whole walk
-  int tl[XR];
-#pragma unroll
-  for (int k = 0; k < XR; ++k) {
-    const int i = tid + k * NTH;
-    tl[k] = (is_col && i < QB * a.P) ? (((i / a.P) << 8) | (i % a.P)) : -1;
-  }
-  bf16 xprev[XR], zprev[XR];
-  // out = (y + D x) * silu(z) for the tile elements this thread loaded; coalesced over p
+  // I/O threads: tile element k of thread t is flat index t + k * NIO of the [64][P] tile
+  const float dscalar = (a.has_D && !a.D_has_hdim) ? __ldg(a.D + h) : 0.f;
+  // I/O threads: element k of thread t is flat index t + k * NIO of the [64][P] tile; (row, head-dim
+  // index) advance by (NIO / P, NIO % P) per element, so no division in the loops.
+  constexpr int XR = (QB * PP + NIO - 1) / NIO;          // 32
+  const int io_l0 = io_t / a.P, io_p0 = io_t % a.P, io_dl = NIO / a.P, io_dp = NIO % a.P;
+  uint32_t xkeep[XR / 2];                                // x of the block's elements, two bf16 per register
+  // out = (y + D x) * silu(z) for the output rows of a finished block; coalesced over p.  z is read
+  // here (all loads issued before the first use), x was kept from the block's tile load.
   auto store_tile = [&](int t_row0, int t_rows) {
+    uint32_t zc[XR / 2];
+    if (a.has_z) {
+      int l = io_l0, p = io_p0;
+#pragma unroll
+      for (int k = 0; k < XR; ++k) {
+        // unconditional load (row clamped into the block) so that all loads are in flight together
+        const uint32_t v = (uint32_t)__bfloat16_as_ushort(zp[(int64_t)trow(a, t_row0 + min(l, t_rows - 1)) * a.z_sl + p]);
+        if (k & 1) zc[k >> 1] |= v << 16; else zc[k >> 1] = v;
+        l += io_dl; p += io_dp;
+        if (p >= a.P) { p -= a.P; ++l; }
+      }
+    }
+    int l = io_l0, p = io_p0;
 #pragma unroll
     for (int k = 0; k < XR; ++k) {
-      const int l = tl[k] >> 8, p = tl[k] & 255;
-      if (tl[k] >= 0 && l < t_rows) {
+      if (l < t_rows) {
         float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
-        if (a.has_D) y = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : __ldg(a.D + h), __bfloat162float(xprev[k]), y);
+        const float dc = a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar;
+        y = fmaf(dc, __uint_as_float((xkeep[k >> 1] >> ((k & 1) * 16)) << 16), y);
         const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
         if (a.has_z) {
           a.out_x[o] = __float2bfloat16_rn(y);
-          const float zv = __bfloat162float(zprev[k]);
+          const float zv = __uint_as_float((zc[k >> 1] >> ((k & 1) * 16)) << 16);
           y *= zv / (1.f + ex2f(-zv * LOG2E));
         }
         a.out[o] = __float2bfloat16_rn(y);
       }
+      l += io_dl; p += io_dp;
+      if (p >= a.P) { p -= a.P; ++l; }
     }
   };
+
+  // descriptor bases (start address = shared-memory base; per-MMA byte offsets are added at issue)
+  const uint32_t sb = smem_u32(smem);
+  const uint64_t dK = desc_sw128(sb);                          // K-major operands
+  const uint64_t dMNb = desc_sw128_mn(sb, SM::kAtomB);         // Bd as [states x rows] operand: 64-state groups kAtomB apart
+  const uint64_t dMNx = desc_sw128_mn(sb, QB * 128);           // x tile as [head-dim x rows] operand
 
   bool failed = false;
   uint32_t unsafe = 0;
@@ -164,20 +199,35 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
     const int rows = min(QB, a.L - row0);
     const uint32_t parity = blk & 1;
     float alast = 0.f;
-    bf16 xr[XR], zr[XR];
-
-    if (is_col) {
-      // ---- x and z tile elements: coalesced global loads now, shared-memory stores after the pass ----
+    if (is_io) {
+      // ---- output rows of the previous block (its accumulator tile is complete once every column warp
+      //      has arrived on the named barrier), then the x rows of this block ------------------------------
+      if (blk > 0 && !a.no_output) {
+        named_barrier(9, NTH + NIO);
+        store_tile(prev_row0, prev_rows);
+      }
+      {
+        int l = io_l0, p = io_p0;
 #pragma unroll
-      for (int k = 0; k < XR; ++k) {
-        xr[k] = zr[k] = __float2bfloat16_rn(0.f);
-        const int l = tl[k] >> 8, p = tl[k] & 255;
-        if (tl[k] >= 0 && l < rows) {
-          const int64_t mr = trow(a, row0 + l);
-          xr[k] = xp[mr * a.x_sl + p];
-          if (zp) zr[k] = zp[mr * a.z_sl + p];
+        for (int k = 0; k < XR; ++k) {
+          // unconditional load (row clamped into the block) so that all loads are in flight together
+          uint32_t v = (uint32_t)__bfloat16_as_ushort(xp[(int64_t)trow(a, row0 + min(l, rows - 1)) * a.x_sl + p]);
+          if (l >= rows) v = 0;
+          if (k & 1) xkeep[k >> 1] |= v << 16; else xkeep[k >> 1] = v;
+          l += io_dl; p += io_dp;
+          if (p >= a.P) { p -= a.P; ++l; }
+        }
+        l = io_l0; p = io_p0;
+#pragma unroll
+        for (int k = 0; k < XR; ++k) {
+          if (l < QB) *(uint16_t*)(smem + SM::kX + sw128_off(l, p)) = (uint16_t)((xkeep[k >> 1] >> ((k & 1) * 16)) & 0xffffu);
+          l += io_dl; p += io_dp;
+          if (p >= a.P) { p -= a.P; ++l; }
         }
       }
+      fence_async_smem();
+    }
+    if (is_col) {
       if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
 
       // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
@@ -205,53 +255,47 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
       // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
       {
         uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB;
         const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
         const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
+        const bool flip = a.bc_contig && a.rev;            // staged B / C rows are in memory order
         float acc = half ? a0 : 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
           const bool valid = l < rows;
+          const int sl = flip ? max(rows - 1 - l, 0) : l;
           acc = fmaf(dtv[j], A2, acc);
-          const float cd = valid ? __bfloat162float(sC[l * NT]) * ex2f(acc) : 0.f;
-          const float bd = valid ? __bfloat162float(sB[l * NT]) * dtv[j] * ex2f(-acc) : 0.f;
+          const float cd = valid ? __bfloat162float(sC[sl * NT]) * ex2f(acc) : 0.f;
+          const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j] * ex2f(-acc) : 0.f;
           const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
           *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
           *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
         }
       }
-      // ---- x tile [l][p] (swizzled rows) --------------------------------------------------------------
-#pragma unroll
-      for (int k = 0; k < XR; ++k)
-        if (tl[k] >= 0) *(bf16*)(smem + SM::kX + sw128_off(tl[k] >> 8, tl[k] & 255)) = xr[k];
       fence_async_smem();
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- MMAs: M = Cd Bd^T, Y = Cd S^T, S += Bd^T x (service warp) ------------------------------------
+    // ---- MMAs: [M | Y] = Cd [Bd ; S]^T (one 64 x 112 MMA per K step), S += Bd^T x (service warp) ------
     if (is_svc) {
       if (lane == 0) {
         fence_after_sync();
-        const uint32_t sb = smem_u32(smem);
         if (!a.no_output) {
 #pragma unroll
           for (int at = 0; at < NT / 64; ++at)
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint32_t ko = at * (QB * 128) + kk * 32;
-              mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
-              mma_bf16(t_Y, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kSop + at * (PP * 128) + kk * 32),
-                       idesc_bf16(64, PP), (at | kk) != 0);
-            }
+            for (int kk = 0; kk < 4; ++kk)
+              mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * SM::kAtomB + kk * 32,
+                           idesc_bf16(64, QB + PP), (at | kk) != 0);
         }
 #pragma unroll
         for (int sl = 0; sl < NT / 128; ++sl)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_bf16(tmem + 128 + sl * PP, desc_sw128_mn(sb + SM::kBd + sl * (2 * QB * 128) + kk * 2048, QB * 128),
-                     desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128), idesc_bf16(128, PP, 1, 1), 1);
+            mma_bf16_off(tmem + 128 + sl * PP, dMNb, SM::kBd + sl * (2 * SM::kAtomB) + kk * 2048, dMNx, SM::kX + kk * 2048,
+                         idesc_bf16(128, PP, 1, 1), 1);
         mma_commit(barA);
       }
       __syncwarp();
@@ -259,11 +303,6 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
     }
 
     if (is_col) {
-      // ---- coalesced store of the previous block's output tile ----------------------------------------
-      if (blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
-#pragma unroll
-      for (int k = 0; k < XR; ++k) { xprev[k] = xr[k]; zprev[k] = zr[k]; }
-
       if (!mbar_wait(barA, parity)) failed = true;
       fence_after_sync();
 
@@ -319,11 +358,9 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
     // ---- Y += tril(M) x ------------------------------------------------------------------------------
     if (is_svc && lane == 0) {
       fence_after_sync();
-      const uint32_t sb = smem_u32(smem);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
-        mma_bf16(t_Y, desc_sw128(sb + SM::kMm + kk * 32), desc_sw128_mn(sb + SM::kX + kk * 2048, QB * 128),
-                 idesc_bf16(64, PP, 0, 1), 1);
+        mma_bf16_off(t_Y, dK, SM::kMm + kk * 32, dMNx, SM::kX + kk * 2048, idesc_bf16(64, PP, 0, 1), 1);
       mma_commit(barB);
     }
     if (is_col) {
@@ -343,12 +380,13 @@ __global__ void __launch_bounds__(2 * NT + 32, 1) k_fwd_tensor(const TArgs a) {
           }
         }
       }
+      if (blk + 1 < nblk) asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");   // output tile complete
     }
     fence_before_sync();
   }
 
   __syncthreads();
-  if (is_col && !failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
+  if (is_io && !failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
     if (unsafe) atomicOr(a.status, 2);
@@ -397,6 +435,7 @@ TArgs make_targs(const issm_params& p) {
   a.final_states = p.final_states;
   a.status = p.status;
   a.saved = (bf16*)p.saved_states;
+  a.bc_contig = (p.B_sl == p.dstate && p.C_sl == p.dstate);
   return a;
 }
 
@@ -407,7 +446,7 @@ static int launch_fwd(const TArgs& a, cudaStream_t s) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 32, smem, s, a);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a);
   return ISSM_OK;
 }
 

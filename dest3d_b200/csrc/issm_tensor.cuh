@@ -18,6 +18,7 @@ constexpr float LN2 = 0.6931471805599453f;
 struct TArgs {
   int b, L, H, P, N, G, hpg, rev;
   int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
+  int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
   float dtmin, dtmax;
   const bf16* x; int64_t x_sb, x_sl, x_sh;
   const void* dt; int64_t dt_sb, dt_sl, dt_sh;

@@ -73,6 +73,19 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// same, with the descriptors given as (precomputed base, byte offset): the offset only touches the
+// 14-bit start-address field in the low word
+__device__ __forceinline__ void mma_bf16_off(uint32_t tmem_d, uint64_t abase, uint32_t aoff, uint64_t bbase, uint32_t boff,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b32 alo, ahi, blo, bhi;\n\t.reg .b64 ad, bd;\n\t"
+      "mov.b64 {alo, ahi}, %1;\n\tmov.b64 {blo, bhi}, %3;\n\t"
+      "add.u32 alo, alo, %2;\n\tadd.u32 blo, blo, %4;\n\t"
+      "mov.b64 ad, {alo, ahi};\n\tmov.b64 bd, {blo, bhi};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, p;\n\t}"
+      ::"r"(tmem_d), "l"(abase), "r"(aoff >> 4), "l"(bbase), "r"(boff >> 4), "r"(idesc), "r"(accumulate) : "memory");
+}
 // arrive on an mbarrier once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
