@@ -146,42 +146,46 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
   // I/O threads: tile element k of thread t is flat index t + k * NIO of the [64][P] tile
   const float dscalar = (a.has_D && !a.D_has_hdim) ? __ldg(a.D + h) : 0.f;
   // I/O threads: element k of thread t is flat index t + k * NIO of the [64][P] tile; (row, head-dim
-  // index) advance by (NIO / P, NIO % P) per element, so no division in the loops.
+  // index) advance by (NIO / P, NIO % P) per element, so no division in the loops.  Elements are
+  // handled in chunks of CH: all loads of a chunk are unconditional (row clamped into the block) and in
+  // flight together; nothing is kept in registers across chunks.
   constexpr int XR = (QB * PP + NIO - 1) / NIO;          // 32
+  constexpr int CH = 8;
   const int io_l0 = io_t / a.P, io_p0 = io_t % a.P, io_dl = NIO / a.P, io_dp = NIO % a.P;
-  uint32_t xkeep[XR / 2];                                // x of the block's elements, two bf16 per register
-  // out = (y + D x) * silu(z) for the output rows of a finished block; coalesced over p.  z is read
-  // here (all loads issued before the first use), x was kept from the block's tile load.
+  auto io_next = [&](int& l, int& p) {
+    l += io_dl; p += io_dp;
+    if (p >= a.P) { p -= a.P; ++l; }
+  };
+  // out = (y + D x) * silu(z) for the output rows of a finished block; coalesced over p
   auto store_tile = [&](int t_row0, int t_rows) {
-    uint32_t zc[XR / 2];
-    if (a.has_z) {
-      int l = io_l0, p = io_p0;
-#pragma unroll
-      for (int k = 0; k < XR; ++k) {
-        // unconditional load (row clamped into the block) so that all loads are in flight together
-        const uint32_t v = (uint32_t)__bfloat16_as_ushort(zp[(int64_t)trow(a, t_row0 + min(l, t_rows - 1)) * a.z_sl + p]);
-        if (k & 1) zc[k >> 1] |= v << 16; else zc[k >> 1] = v;
-        l += io_dl; p += io_dp;
-        if (p >= a.P) { p -= a.P; ++l; }
-      }
-    }
     int l = io_l0, p = io_p0;
+#pragma unroll 1
+    for (int c = 0; c < XR / CH; ++c) {
+      bf16 xv[CH], zv[CH];
+      int lc = l, pc = p;
 #pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      if (l < t_rows) {
-        float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
-        const float dc = a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar;
-        y = fmaf(dc, __uint_as_float((xkeep[k >> 1] >> ((k & 1) * 16)) << 16), y);
-        const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
-        if (a.has_z) {
-          a.out_x[o] = __float2bfloat16_rn(y);
-          const float zv = __uint_as_float((zc[k >> 1] >> ((k & 1) * 16)) << 16);
-          y *= zv / (1.f + ex2f(-zv * LOG2E));
-        }
-        a.out[o] = __float2bfloat16_rn(y);
+      for (int k = 0; k < CH; ++k) {
+        const int64_t mr = trow(a, t_row0 + min(lc, t_rows - 1));
+        xv[k] = xp[mr * a.x_sl + pc];
+        zv[k] = a.has_z ? zp[mr * a.z_sl + pc] : __float2bfloat16_rn(0.f);
+        io_next(lc, pc);
       }
-      l += io_dl; p += io_dp;
-      if (p >= a.P) { p -= a.P; ++l; }
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        if (l < t_rows) {
+          float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
+          const float dc = a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar;
+          y = fmaf(dc, __bfloat162float(xv[k]), y);
+          const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
+          if (a.has_z) {
+            a.out_x[o] = __float2bfloat16_rn(y);
+            const float z1 = __bfloat162float(zv[k]);
+            y *= z1 / (1.f + ex2f(-z1 * LOG2E));
+          }
+          a.out[o] = __float2bfloat16_rn(y);
+        }
+        io_next(l, p);
+      }
     }
   };
 
@@ -208,21 +212,20 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
       }
       {
         int l = io_l0, p = io_p0;
+#pragma unroll 1
+        for (int c = 0; c < XR / CH; ++c) {
+          bf16 xv[CH];
+          int lc = l, pc = p;
 #pragma unroll
-        for (int k = 0; k < XR; ++k) {
-          // unconditional load (row clamped into the block) so that all loads are in flight together
-          uint32_t v = (uint32_t)__bfloat16_as_ushort(xp[(int64_t)trow(a, row0 + min(l, rows - 1)) * a.x_sl + p]);
-          if (l >= rows) v = 0;
-          if (k & 1) xkeep[k >> 1] |= v << 16; else xkeep[k >> 1] = v;
-          l += io_dl; p += io_dp;
-          if (p >= a.P) { p -= a.P; ++l; }
-        }
-        l = io_l0; p = io_p0;
+          for (int k = 0; k < CH; ++k) {
+            xv[k] = xp[(int64_t)trow(a, row0 + min(lc, rows - 1)) * a.x_sl + pc];
+            io_next(lc, pc);
+          }
 #pragma unroll
-        for (int k = 0; k < XR; ++k) {
-          if (l < QB) *(uint16_t*)(smem + SM::kX + sw128_off(l, p)) = (uint16_t)((xkeep[k >> 1] >> ((k & 1) * 16)) & 0xffffu);
-          l += io_dl; p += io_dp;
-          if (p >= a.P) { p -= a.P; ++l; }
+          for (int k = 0; k < CH; ++k) {
+            if (l < QB) *(bf16*)(smem + SM::kX + sw128_off(l, p)) = l < rows ? xv[k] : __float2bfloat16_rn(0.f);
+            io_next(l, p);
+          }
         }
       }
       fence_async_smem();
