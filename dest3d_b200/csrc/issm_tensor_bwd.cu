@@ -28,7 +28,7 @@ struct BwdSmem {
   static constexpr int kCd = 0;                         // [NT/64 atoms][64 l][128 B]
   static constexpr int kBd = kCd + NT * 128;
   static constexpr int kGop = kBd + NT * 128;           // [NT n][128 B]: g' rows, p contiguous (SW128)
-  static constexpr int kSop = kGop + NT * 128;          // [PP/8][NT n][16 B]: S' rows (interleaved)
+  static constexpr int kSop = kGop + NT * 128;          // [PP/8][NT n][16 B]: S rows (interleaved)
   static constexpr int kX = kSop + NT * (PP * 2);       // [64 l][128 B]
   static constexpr int kDy = kX + QB * 128;             // [64 l][128 B]
   static constexpr int kDMm = kDy + QB * 128;           // [64 l][128 B], s contiguous
@@ -36,16 +36,26 @@ struct BwdSmem {
   static constexpr int kDxT = kDMm;                     // [64][PP] float, aliases dMm + Mm after the MMAs
   static constexpr int kSdt = kMm + QB * 128;           // staging [64][NT] bf16
   static constexpr int kSB = kSdt + QB * NT * 2;
-  static constexpr int kRed = kSdt;                     // [XR * NT] float: dD partial reduction (after the walk)
-  static constexpr int kBars = kSB + QB * NT * 2;
+  static constexpr int kXch = kSB + QB * NT * 2;        // [4][NT] float: per-half exchange (sum dt*A, <S,G>, sum dacs)
+  static constexpr int kRed = kSdt;                     // dD reduction scratch (after the walk)
+  static constexpr int kBars = kXch + 4 * NT * 4;
   static constexpr int kTotal = kBars + 64;
 };
 
+// Thread layout (as in the forward): 2*NT column threads, one service warp, three tile-I/O warps.
+// Column thread (n = tid % NT, half = tid / NT) owns rows [32 half, 32 half + 32) of state column n in
+// the operand pass and in the (row, state) epilogue, and columns [24 half, 24 half + 24) of TMEM lane n
+// of the state gradient G, which lives in TMEM for the whole walk.
 template <int NT, typename TDT>
-__global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
   using SM = BwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
-  constexpr int XR = (QB * PP + NT - 1) / NT;
+  constexpr int NTH = 2 * NT;
+  constexpr int NIO = 96;
+  constexpr int XR = (QB * PP + NIO - 1) / NIO;         // 32 tile elements per I/O thread
+  constexpr int CH = 8;
+  constexpr int HP = PP / 2;
+  constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bar1 = (uint64_t*)(smem + SM::kBars);
@@ -53,10 +63,15 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
   uint64_t* barS = bar1 + 2;     // dt staging
   uint64_t* barT = bar1 + 3;     // B staging
   uint32_t* tmem_holder = (uint32_t*)(bar1 + 4);
+  float* sXch = (float*)(smem + SM::kXch);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_col = tid < NTH;
+  const bool is_svc = warp == NTH / 32;
+  const bool is_io = tid >= NTH + 32;
+  const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
-  const int n = tid;
+  const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
   const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
   const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg + n;
@@ -70,7 +85,7 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
   const int nblk = (a.L + QB - 1) / QB;
   const size_t bh = (size_t)b * a.H + h;
 
-  for (int i = tid; i < (SM::kSdt - SM::kGop) / 16; i += NT) ((uint4*)(smem + SM::kGop))[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (SM::kSdt - SM::kGop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kGop))[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) { mbar_init(bar1, 1); mbar_init(bar2, 1); mbar_init(barS, 1); mbar_init(barT, 1); mbar_fence_init(); }
   if (warp == 0) { tmem_alloc(tmem_holder, 512); tmem_relinquish(); }
   fence_before_sync();
@@ -78,13 +93,16 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
   fence_after_sync();
   const uint32_t tmem = *tmem_holder;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const int slab = tid >> 7;
+  const int slab = n >> 7;
   const uint32_t t_dM = tmem, t_M = tmem + 64, t_dx = tmem;
-  const uint32_t t_BDrow = tmem + lane_base + 128 + slab * 64;
-  const uint32_t t_CDrow = tmem + lane_base + 256 + slab * 64;
-  const uint32_t t_Grow = tmem + lane_base + 384 + slab * PP;
+  const uint32_t t_BD = tmem + lane_base + 128 + slab * 64 + half * 32;   // this thread's 32 rows of BD^T[n, :]
+  const uint32_t t_CD = tmem + lane_base + 256 + slab * 64 + half * 32;
+  const uint32_t t_G = tmem + lane_base + 384 + slab * PP + half * HP;    // this thread's part of G[n, :]
+  const int kcol = n & 63;
+  const bool flipB = a.bc_contig && a.rev;               // staged B rows are in memory order
 
-  auto prefetch_dt = [&](int blk) {      // warp 1
+  // ---- service warp: bulk prefetches ------------------------------------------------------------------
+  auto prefetch_dt = [&](int blk) {
     if (!kStageDt) return;
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2);
@@ -92,344 +110,445 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
     for (int l = lane; l < rows; l += 32)
       bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + (int64_t)trow(a, row0 + l) * a.dt_sl, NT * 2, barS);
   };
-  auto prefetch_B = [&](int blk) {       // warp 2
+  auto prefetch_B = [&](int blk) {
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     if (lane == 0) mbar_expect_tx(barT, (uint32_t)rows * NT * 2);
     __syncwarp();
-    for (int l = lane; l < rows; l += 32)
-      bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + (int64_t)trow(a, row0 + l) * a.B_sl, NT * 2, barT);
+    if (a.bc_contig) {
+      const int64_t m0 = a.rev ? a.L - row0 - rows : row0;
+      if (lane == 0) bulk_g2s(smem + SM::kSB, Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2, barT);
+    } else {
+      for (int l = lane; l < rows; l += 32)
+        bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + (int64_t)trow(a, row0 + l) * a.B_sl, NT * 2, barT);
+    }
   };
-  if (warp == 1) prefetch_dt(nblk - 1);
-  if (warp == 2) prefetch_B(nblk - 1);
+  if (is_svc) { prefetch_dt(nblk - 1); prefetch_B(nblk - 1); }
 
-  // gradient of the running state, and the state leaving the block (bf16 pairs)
-  float G[PP];
-  uint32_t Snext[PP / 2];
-  {
+  // ---- column threads: G <- dfinal ---------------------------------------------------------------------
+  if (is_col) {
+    float gc[HP];
     const float* __restrict__ df = a.dfinal ? a.dfinal + (bh * a.P) * a.N + n : nullptr;
 #pragma unroll
-    for (int p = 0; p < PP; ++p) G[p] = (df && p < a.P) ? df[(size_t)p * a.N] : 0.f;
-    const uint4* src = (const uint4*)(a.saved + ((bh * (nblk + 1) + nblk) * a.N + n) * PP);
-#pragma unroll
-    for (int c = 0; c < PP / 8; ++c) {
-      const uint4 v = src[c];
-      Snext[c * 4] = v.x; Snext[c * 4 + 1] = v.y; Snext[c * 4 + 2] = v.z; Snext[c * 4 + 3] = v.w;
-    }
+    for (int j = 0; j < HP; ++j) gc[j] = (df && half * HP + j < a.P) ? df[(size_t)(half * HP + j) * a.N] : 0.f;
+    tmem_st16(t_G, gc);
+    tmem_st8(t_G + 16, gc + 16);
+    tmem_st_wait();
   }
-  const int kcol = tid & 63;
-  const int npt = (QB * a.P + NT - 1) / NT;
-  float dDacc[XR];
+
+  // ---- I/O threads: flat element walk over the [64][P] tile (see the forward kernel) ---------------------
+  const int io_l0 = io_t / a.P, io_p0 = io_t % a.P, io_dl = NIO / a.P, io_dp = NIO % a.P;
+  auto io_next = [&](int& l, int& p) {
+    l += io_dl; p += io_dp;
+    if (p >= a.P) { p -= a.P; ++l; }
+  };
+  const float dscalar = (a.has_D && !a.D_has_hdim) ? __ldg(a.D + h) : 0.f;
+  float dDacc = 0.f;                                     // sum of dy * x over this thread's elements
+  // dy (and dz) of a chunk of elements: dy = dout * z sigmoid(z), dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
+  // (issm_chunk_scan.py:351-360); loads are unconditional with the row clamped into the block
+  auto load_dy = [&](int t_row0, int t_rows, int l, int p, bool write_dz, float* dyv, bf16* xv) {
+    bf16 gv[CH], zv[CH], yv[CH];
+    int lc = l, pc = p;
 #pragma unroll
-  for (int k = 0; k < XR; ++k) dDacc[k] = 0.f;
+    for (int k = 0; k < CH; ++k) {
+      const int64_t mr = trow(a, t_row0 + min(lc, t_rows - 1));
+      xv[k] = xp[mr * a.x_sl + pc];
+      gv[k] = gp[mr * a.g_sl + pc];
+      zv[k] = zp ? zp[mr * a.z_sl + pc] : __float2bfloat16_rn(0.f);
+      yv[k] = (zp && write_dz) ? yp[mr * a.o_sl + pc] : __float2bfloat16_rn(0.f);
+      io_next(lc, pc);
+    }
+    lc = l; pc = p;
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      float dy = __bfloat162float(gv[k]);
+      if (zp) {
+        const float z1 = __bfloat162float(zv[k]);
+        const float sg = 1.f / (1.f + ex2f(-z1 * LOG2E));
+        if (write_dz && lc < t_rows)
+          a.dz[(((size_t)b * a.L + trow(a, t_row0 + lc)) * a.H + h) * a.P + pc] =
+              __float2bfloat16_rn(dy * __bfloat162float(yv[k]) * sg * (1.f + z1 * (1.f - sg)));
+        dy *= z1 * sg;
+      }
+      dyv[k] = lc < t_rows ? __bfloat162float(__float2bfloat16_rn(dy)) : 0.f;     // as the MMAs see it
+      io_next(lc, pc);
+    }
+  };
+  // dx = accumulator tile + D dy for the rows of a finished block; coalesced over p
+  auto store_dx = [&](int t_row0, int t_rows) {
+    int l = io_l0, p = io_p0;
+#pragma unroll 1
+    for (int c = 0; c < XR / CH; ++c) {
+      float dyv[CH];
+      bf16 xv[CH];
+      if (a.has_D) load_dy(t_row0, t_rows, l, p, false, dyv, xv);
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        if (l < t_rows) {
+          float v = *(const float*)(smem + SM::kDxT + (l * PP + p) * 4);
+          if (a.has_D) v = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar, dyv[k], v);
+          a.dx[(((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + p] = __float2bfloat16_rn(v);
+        }
+        io_next(l, p);
+      }
+    }
+  };
+
+  // descriptor bases
+  const uint32_t sb = smem_u32(smem);
+  const uint64_t dK = desc_sw128(sb);
+  const uint64_t dMN = desc_sw128_mn(sb, QB * 128);
+  const uint64_t dIL = desc_interleave(sb, NT * 16, 128);
+
   float dAacc = 0.f, dbacc = 0.f;
   bool failed = false;
   uint32_t unsafe = 0;
+  int prev_rows = 0, prev_row0 = 0;
 
   for (int it = 0; it < nblk; ++it) {
     const int blk = nblk - 1 - it;
     const int row0 = blk * QB;
     const int rows = min(QB, a.L - row0);
     const uint32_t parity = it & 1;
+    float dtv[32];
+    float a0 = 0.f, alast = 0.f, cst = 0.f;
+    uint32_t cmask = 0;                                  // bit j: dt of row 32 half + j was clamped (no gradient)
 
-    // ---- issue the global loads of this block's small tiles and of the entering state -----------
-    bf16 xr[XR], gr[XR], zr[XR], yr[XR];
-#pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      xr[k] = gr[k] = zr[k] = yr[k] = __float2bfloat16_rn(0.f);
-      const int i = tid + k * NT;
-      if (k < npt && i < rows * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
-        const int64_t mr = trow(a, row0 + l);
-        xr[k] = xp[mr * a.x_sl + p];
-        gr[k] = gp[mr * a.g_sl + p];
-        if (zp) { zr[k] = zp[mr * a.z_sl + p]; yr[k] = yp[mr * a.o_sl + p]; }
+    if (is_io) {
+      // ---- dx rows of the previous block (its accumulator tile is complete once every column warp has
+      //      arrived on the named barrier), then the x / dy tiles, dz and dD partials of this block ---------
+      if (it > 0) {
+        named_barrier(9, NTH + NIO);
+        store_dx(prev_row0, prev_rows);
       }
-    }
-    uint32_t Scur[PP / 2];
-    {
-      const uint4* src = (const uint4*)(a.saved + ((bh * (nblk + 1) + blk) * a.N + n) * PP);
-#pragma unroll
-      for (int c = 0; c < PP / 8; ++c) {
-        const uint4 v = src[c];
-        Scur[c * 4] = v.x; Scur[c * 4 + 1] = v.y; Scur[c * 4 + 2] = v.z; Scur[c * 4 + 3] = v.w;
-      }
-    }
-
-    // ---- state bookkeeping that needs no decay: <S leaving the block, G>, and the S operand ----------
-    float cst = 0.f;
-#pragma unroll
-    for (int q = 0; q < PP / 2; ++q) {
-      cst = fmaf(__uint_as_float(Snext[q] << 16), G[2 * q], cst);
-      cst = fmaf(__uint_as_float(Snext[q] & 0xffff0000u), G[2 * q + 1], cst);
-    }
-#pragma unroll
-    for (int c = 0; c < PP / 8; ++c)
-      *(uint4*)(smem + SM::kSop + c * (NT * 16) + tid * 16) = make_uint4(Scur[c * 4], Scur[c * 4 + 1], Scur[c * 4 + 2], Scur[c * 4 + 3]);
-
-    if (kStageDt && !mbar_wait(barS, parity)) failed = true;
-    if (!mbar_wait(barT, parity)) failed = true;
-
-    // ---- one pass over the rows: dt transform, cumulative decay, this column of Cd and Bd ----------
-    // (C comes straight from global memory: L2-resident, shared by the heads of a sample)
-    const float alast = build_operands<NT, TDT, kStageDt, false>(
-        a, rows, row0, kcol, (const bf16*)(smem + SM::kSdt) + n, dtp + n, (const bf16*)(smem + SM::kSB) + n,
-        nullptr, Cp, smem + SM::kCd + (tid >> 6) * (QB * 128), smem + SM::kBd + (tid >> 6) * (QB * 128), A2, bias);
-    if (fabsf(alast) > 120.f) unsafe = 1;
-
-    // ---- g' = 2^(a_last) G: fp32 copy parked in TMEM for the accumulate MMA, bf16 copy as operand ----
-    {
-      const float eg = ex2f(alast);
-      float gs[PP];
-#pragma unroll
-      for (int p = 0; p < PP; ++p) gs[p] = G[p] * eg;
-      tmem_st16(t_Grow, gs);
-      tmem_st16(t_Grow + 16, gs + 16);
-      tmem_st16(t_Grow + 32, gs + 32);
-#pragma unroll
-      for (int c = 0; c < PP / 8; ++c)
-        *(uint4*)(smem + SM::kGop + sw128_chunk(tid, c)) =
-            make_uint4(pack_bf16(gs[c * 8], gs[c * 8 + 1]), pack_bf16(gs[c * 8 + 2], gs[c * 8 + 3]),
-                       pack_bf16(gs[c * 8 + 4], gs[c * 8 + 5]), pack_bf16(gs[c * 8 + 6], gs[c * 8 + 7]));
-      tmem_st_wait();
-    }
-
-    // ---- x and dy tiles, dz, dD partials -------------------------------------------------------------
-#pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      const int i = tid + k * NT;
-      if (k < npt && i < QB * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
-        const float xv = __bfloat162float(xr[k]);
-        float dy = __bfloat162float(gr[k]);
-        if (zp) {
-          const float zv = __bfloat162float(zr[k]);
-          const float sg = 1.f / (1.f + ex2f(-zv * LOG2E));
-          if (i < rows * a.P)
-            a.dz[(((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.P + p] =
-                __float2bfloat16_rn(dy * __bfloat162float(yr[k]) * sg * (1.f + zv * (1.f - sg)));
-          dy *= zv * sg;
-        }
-        const bf16 dyb = __float2bfloat16_rn(dy);
-        dDacc[k] = fmaf(__bfloat162float(dyb), xv, dDacc[k]);
-        *(bf16*)(smem + SM::kX + sw128_off(l, p)) = xr[k];
-        *(bf16*)(smem + SM::kDy + sw128_off(l, p)) = dyb;
-      }
-    }
-    fence_async_smem();
-    fence_before_sync();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // ---- MMA phase 1: dM = dy x^T, M = Cd Bd^T ---------------------------------------------------
-    if (tid == 0) {
-      fence_after_sync();
-      const uint32_t sb = smem_u32(smem);
-#pragma unroll
-      for (int kk = 0; kk < PP / 16; ++kk)
-        mma_bf16(t_dM, desc_sw128(sb + SM::kDy + kk * 32), desc_sw128(sb + SM::kX + kk * 32), idesc_bf16(64, 64), kk != 0);
-#pragma unroll
-      for (int at = 0; at < NT / 64; ++at)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint32_t ko = at * (QB * 128) + kk * 32;
-          mma_bf16(t_M, desc_sw128(sb + SM::kCd + ko), desc_sw128(sb + SM::kBd + ko), idesc_bf16(64, 64), (at | kk) != 0);
-        }
-      mma_commit(bar1);
-    }
-    if (!mbar_wait(bar1, parity)) failed = true;
-    fence_after_sync();
-
-    // ---- epilogue 1: causal masks, bf16 operands dMm[l][s], Mm[l][s] --------------------------------
-    if (warp < 4 && !failed) {
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        float mv[64];
-        const uint32_t t0 = (which ? t_M : t_dM) + lane_base;
-        tmem_ld16(t0, mv);
-        tmem_ld16(t0 + 16, mv + 16);
-        tmem_ld16(t0 + 32, mv + 32);
-        tmem_ld16(t0 + 48, mv + 48);
-        tmem_ld_wait();
-        if (lane < 16) {
-          const int l = warp * 16 + lane;
-          uint8_t* dst = smem + (which ? SM::kMm : SM::kDMm);
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              const int s = c * 8 + j;
-              pk[j >> 1] = pack_bf16(s <= l ? mv[s] : 0.f, s + 1 <= l ? mv[s + 1] : 0.f);
-            }
-            *(uint4*)(dst + sw128_chunk(l, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          }
-        }
-      }
-    }
-    fence_async_smem();
-    fence_before_sync();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // ---- MMA phase 2 ----------------------------------------------------------------------------------
-    if (tid == 0) {
-      fence_after_sync();
-      const uint32_t sb = smem_u32(smem);
-#pragma unroll
-      for (int sl = 0; sl < NT / 128; ++sl) {
-        const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
-          const uint64_t aCd = desc_sw128_mn(sb + SM::kCd + sl * (2 * QB * 128) + kk * 2048, QB * 128);
-          const uint64_t aBd = desc_sw128_mn(sb + SM::kBd + sl * (2 * QB * 128) + kk * 2048, QB * 128);
-          mma_bf16(dBD, aCd, desc_sw128_mn(sb + SM::kDMm + kk * 2048, QB * 128), idesc_bf16(128, 64, 1, 1), kk != 0);
-          mma_bf16(dCD, aBd, desc_sw128(sb + SM::kDMm + kk * 32), idesc_bf16(128, 64, 1, 0), kk != 0);
-          mma_bf16(dG, aCd, desc_sw128_mn(sb + SM::kDy + kk * 2048, QB * 128), idesc_bf16(128, PP, 1, 1), 1);
-        }
-#pragma unroll
-        for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
-          mma_bf16(dBD, desc_sw128(sb + SM::kGop + sl * (128 * 128) + kk * 32), desc_sw128(sb + SM::kX + kk * 32),
-                   idesc_bf16(128, 64), 1);
-          mma_bf16(dCD, desc_interleave(sb + SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), NT * 16, 128),
-                   desc_sw128(sb + SM::kDy + kk * 32), idesc_bf16(128, 64), 1);
-        }
-      }
-#pragma unroll
-      for (int at = 0; at < NT / 64; ++at)               // dx: K = states
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_bf16(t_dx, desc_sw128(sb + SM::kBd + at * (QB * 128) + kk * 32),
-                   desc_sw128_mn(sb + SM::kGop + (at * 4 + kk) * 2048, QB * 128), idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
-        mma_bf16(t_dx, desc_sw128_mn(sb + SM::kMm + kk * 2048, QB * 128), desc_sw128_mn(sb + SM::kDy + kk * 2048, QB * 128),
-                 idesc_bf16(64, PP, 1, 1), 1);
-      mma_commit(bar2);
-    }
-    if (!mbar_wait(bar2, parity)) failed = true;
-    fence_after_sync();
-
-    // ---- epilogue 2 ------------------------------------------------------------------------------------
-    if (!failed) {
-      // (a) the owner of state column n: dB_h, dC_h, ddt, in-block reverse cumsum of dacs
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
-      const uint8_t* cd_col = smem + SM::kCd + (tid >> 6) * (QB * 128);
-      const uint8_t* bd_col = smem + SM::kBd + (tid >> 6) * (QB * 128);
-      float total = 0.f;                                  // sum over the block of dacs = Cd CD - Bd BD
+      int l = io_l0, p = io_p0;
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        float bdv[16], cdv[16];
-        tmem_ld16(t_BDrow + ch * 16, bdv);
-        tmem_ld16(t_CDrow + ch * 16, cdv);
-        tmem_ld_wait();
+      for (int c = 0; c < XR / CH; ++c) {
+        float dyv[CH];
+        bf16 xv[CH];
+        load_dy(row0, rows, l, p, true, dyv, xv);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t off = (uint32_t)((ch * 16 + j) * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
-          total = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], total);
-          total = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], total);
-        }
-      }
-      float prefix = 0.f, ac = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        float bdv[16], cdv[16];
-        tmem_ld16(t_BDrow + ch * 16, bdv);
-        tmem_ld16(t_CDrow + ch * 16, cdv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int l = ch * 16 + j;
-          const bool valid = l < rows;
-          const int64_t mr = trow(a, row0 + min(l, rows - 1));
-          const float raw = kStageDt ? __bfloat162float(sdt[l * NT]) : ldf(dtp + mr * a.dt_sl + n);
-          bool clamped = false;
-          const float dtl = valid ? dt_transform(a, raw, bias, clamped) : 0.f;
-          ac = fmaf(dtl, A2, ac);
-          const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
-          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
-          const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
-                             __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
-          const float ddA = cst + total - prefix;          // sum of dacs over rows >= l, plus <S_next, G>
-          prefix += dacs;
-          float gd = fmaf(ddA, Anat, __bfloat162float(sB[l * NT]) * bd);
-          if (clamped) gd = 0.f;
-          else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
-          dAacc = fmaf(ddA, dtl, dAacc);
-          if (valid) {
-            dbacc += gd;
-            const size_t o = (((size_t)b * a.L + mr) * a.H + h) * a.N + n;
-            stf((TDT*)a.ddt + o, gd);
-            a.dBh[o] = __float2bfloat16_rn(dtl * bd);
-            a.dCh[o] = __float2bfloat16_rn(cd);
+        for (int k = 0; k < CH; ++k) {
+          if (l < QB) {
+            const bf16 xb = l < rows ? xv[k] : __float2bfloat16_rn(0.f);
+            dDacc = fmaf(dyv[k], __bfloat162float(xb), dDacc);
+            *(bf16*)(smem + SM::kX + sw128_off(l, p)) = xb;
+            *(bf16*)(smem + SM::kDy + sw128_off(l, p)) = __float2bfloat16_rn(dyv[k]);
           }
+          io_next(l, p);
         }
       }
-      // (b) new state gradient
+      fence_async_smem();
+    }
+
+    if (is_col) {
+      // ---- <S leaving the block, G> over this thread's state columns; S operand rows of the entering state ----
+      float cpart = 0.f;
       {
-        float gs[PP];
-        tmem_ld16(t_Grow, gs);
-        tmem_ld16(t_Grow + 16, gs + 16);
-        tmem_ld16(t_Grow + 32, gs + 32);
+        float gc[HP];
+        tmem_ld16(t_G, gc);
+        tmem_ld8(t_G + 16, gc + 16);
+        const uint4* sn = (const uint4*)(a.saved + ((bh * (nblk + 1) + blk + 1) * a.N + n) * PP + half * HP);
+        const uint4* sc = (const uint4*)(a.saved + ((bh * (nblk + 1) + blk) * a.N + n) * PP + half * HP);
+        uint4 snv[HP / 8], scv[HP / 8];
+#pragma unroll
+        for (int c = 0; c < HP / 8; ++c) { snv[c] = sn[c]; scv[c] = sc[c]; }
         tmem_ld_wait();
 #pragma unroll
-        for (int p = 0; p < PP; ++p) G[p] = gs[p];
-      }
+        for (int c = 0; c < HP / 8; ++c) {
+          const uint32_t w[4] = {snv[c].x, snv[c].y, snv[c].z, snv[c].w};
 #pragma unroll
-      for (int q = 0; q < PP / 2; ++q) Snext[q] = Scur[q];
-      // (c) dx rows -> shared memory
-      if (warp < 4) {
-        float dv[PP];
-        tmem_ld16(t_dx + lane_base, dv);
-        tmem_ld16(t_dx + lane_base + 16, dv + 16);
-        tmem_ld16(t_dx + lane_base + 32, dv + 32);
-        tmem_ld_wait();
-        if (lane < 16) {
-          float4* dst = (float4*)(smem + SM::kDxT + (warp * 16 + lane) * PP * 4);
-#pragma unroll
-          for (int c = 0; c < PP / 4; ++c) dst[c] = make_float4(dv[c * 4], dv[c * 4 + 1], dv[c * 4 + 2], dv[c * 4 + 3]);
+          for (int j = 0; j < 4; ++j) {
+            cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
+            cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
+          }
+          *(uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16) = scv[c];
         }
       }
+      if (kStageDt && !mbar_wait(barS, parity)) failed = true;
+
+      // ---- phase A: dt of this thread's 32 rows, clamp mask, summed log2-decay --------------------------
+      float asum = 0.f;
+      {
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const float raw = kStageDt ? __bfloat162float(sdt[l * NT])
+                                     : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
+          bool clamped = false;
+          const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
+          if (clamped && l < rows) cmask |= 1u << j;
+          dtv[j] = v;
+          asum = fmaf(v, A2, asum);
+        }
+      }
+      sXch[half * NT + n] = asum;
+      sXch[(2 + half) * NT + n] = cpart;
+      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+      a0 = sXch[n];
+      alast = a0 + sXch[NT + n];
+      cst = sXch[2 * NT + n] + sXch[3 * NT + n];
+      if (fabsf(alast) > 120.f) unsafe = 1;
+
+      if (!mbar_wait(barT, parity)) failed = true;
+
+      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a (C straight from global memory,
+      //      16 unconditional loads in flight) ---------------------------------------------------------------
+      {
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+        float acc = half ? a0 : 0.f;
+#pragma unroll
+        for (int j0 = 0; j0 < 32; j0 += 16) {
+          bf16 cl[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            cl[j] = Cp[(int64_t)trow(a, row0 + min(half * 32 + j0 + j, rows - 1)) * a.C_sl];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int l = half * 32 + j0 + j;
+            const bool valid = l < rows;
+            const int sl = flipB ? max(rows - 1 - l, 0) : l;
+            acc = fmaf(dtv[j0 + j], A2, acc);
+            const float cd = valid ? __bfloat162float(cl[j]) * ex2f(acc) : 0.f;
+            const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j0 + j] * ex2f(-acc) : 0.f;
+            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+          }
+        }
+      }
+      // ---- g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -----------
+      {
+        float gc[HP];
+        tmem_ld16(t_G, gc);
+        tmem_ld8(t_G + 16, gc + 16);
+        tmem_ld_wait();
+        const float eg = ex2f(alast);
+#pragma unroll
+        for (int j = 0; j < HP; ++j) gc[j] *= eg;
+        tmem_st16(t_G, gc);
+        tmem_st8(t_G + 16, gc + 16);
+#pragma unroll
+        for (int c = 0; c < HP / 8; ++c)
+          *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
+              make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
+                         pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
+        tmem_st_wait();
+      }
+      fence_async_smem();
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
-    if (warp == 1 && blk > 0) prefetch_dt(blk - 1);       // every thread is past its dt / B staging reads
-    if (warp == 2 && blk > 0) prefetch_B(blk - 1);
 
-    // ---- coalesced dx store: dx = tile + D dy --------------------------------------------------------
+    // ---- MMA phase 1: dM = dy x^T, M = Cd Bd^T (service warp) --------------------------------------------
+    if (is_svc) {
+      if (lane == 0) {
+        fence_after_sync();
 #pragma unroll
-    for (int k = 0; k < XR; ++k) {
-      const int i = tid + k * NT;
-      if (k < npt && i < rows * a.P) {
-        const int l = i / a.P, p = i - l * a.P;
-        float v = *(const float*)(smem + SM::kDxT + (l * PP + p) * 4);
-        if (a.has_D) v = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : __ldg(a.D + h),
-                              __bfloat162float(*(const bf16*)(smem + SM::kDy + sw128_off(l, p))), v);
-        a.dx[(((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.P + p] = __float2bfloat16_rn(v);
+        for (int kk = 0; kk < PP / 16; ++kk)
+          mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
+#pragma unroll
+        for (int at = 0; at < NT / 64; ++at)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
+                         idesc_bf16(64, 64), (at | kk) != 0);
+        mma_commit(bar1);
+      }
+      __syncwarp();
+      if (blk > 0) prefetch_dt(blk - 1);                   // every column thread is past phase A
+    }
+
+    if (is_col) {
+      if (!mbar_wait(bar1, parity)) failed = true;
+      fence_after_sync();
+      // ---- epilogue 1: causal masks, bf16 operands dMm[l][s] (first half of the warps) and Mm[l][s] --------
+      if (!failed) {
+        const int l = (warp & 3) * 16 + lane;
+        const uint32_t t0 = (half ? t_M : t_dM) + lane_base;
+        uint8_t* dst = smem + (half ? SM::kMm : SM::kDMm);
+        for (int c16 = (warp >> 2) % (NCG / 2 > 0 ? NCG / 2 : 1); c16 < 4; c16 += (NCG / 2 > 0 ? NCG / 2 : 1)) {
+          float mv[16];
+          tmem_ld16(t0 + c16 * 16, mv);
+          tmem_ld_wait();
+          if (lane < 16) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const int s = c16 * 16 + c * 8 + j;
+                pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
+              }
+              *(uint4*)(dst + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        }
+      }
+      fence_async_smem();
+    }
+    fence_before_sync();
+    if (__syncthreads_or(failed)) { failed = true; break; }
+
+    // ---- MMA phase 2 (service warp) -----------------------------------------------------------------------
+    if (is_svc) {
+      if (lane == 0) {
+        fence_after_sync();
+#pragma unroll
+        for (int sl = 0; sl < NT / 128; ++sl) {
+          const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
+            const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
+            mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
+            mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
+            mma_bf16_off(dG, dMN, oCd, dMN, SM::kDy + kk * 2048, idesc_bf16(128, PP, 1, 1), 1);
+          }
+#pragma unroll
+          for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
+            mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
+            mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
+          }
+        }
+#pragma unroll
+        for (int at = 0; at < NT / 64; ++at)               // dx: K = states
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
+                         idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
+          mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
+        mma_commit(bar2);
+      }
+      __syncwarp();
+      if (blk > 0) {                                       // B staging is free once every column thread has
+        named_barrier(10, NTH + 32);                       // finished its (row, state) epilogue
+        prefetch_B(blk - 1);
       }
     }
-    // the tile buffers are rewritten only after the next block's first barrier, but the dx tile aliases
-    // the masked-matrix operands that epilogue 1 of the next block writes: keep the readers ahead
-    __syncthreads();
+
+    if (is_col) {
+      if (!mbar_wait(bar2, parity)) failed = true;
+      fence_after_sync();
+      if (!failed) {
+        // ---- (a) the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse cumsum of dacs ------
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
+        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
+        float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          float bdv[16], cdv[16];
+          tmem_ld16(t_BD + ch * 16, bdv);
+          tmem_ld16(t_CD + ch * 16, cdv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t off = (uint32_t)((half * 32 + ch * 16 + j) * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+            part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
+            part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
+          }
+        }
+        sXch[half * NT + n] = part;
+        named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+        const float p0 = sXch[n];
+        const float total = p0 + sXch[NT + n];
+        float prefix = half ? p0 : 0.f;
+        float ac = half ? a0 : 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          float bdv[16], cdv[16];
+          tmem_ld16(t_BD + ch * 16, bdv);
+          tmem_ld16(t_CD + ch * 16, cdv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int jj = ch * 16 + j;
+            const int l = half * 32 + jj;
+            const bool valid = l < rows;
+            const float dtl = dtv[jj];
+            ac = fmaf(dtl, A2, ac);
+            const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
+            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+            const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
+                               __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
+            const float ddA = cst + total - prefix;          // sum of dacs over rows >= l, plus <S_next, G>
+            prefix += dacs;
+            const int sl = flipB ? max(rows - 1 - l, 0) : l;
+            float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * NT]) * bd);
+            if ((cmask >> jj) & 1u) gd = 0.f;
+            else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
+            dAacc = fmaf(ddA, dtl, dAacc);
+            if (valid) {
+              dbacc += gd;
+              const size_t o = (((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.N + n;
+              stf((TDT*)a.ddt + o, gd);
+              a.dBh[o] = __float2bfloat16_rn(dtl * bd);
+              a.dCh[o] = __float2bfloat16_rn(cd);
+            }
+          }
+        }
+        asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
+        // ---- (b) dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) -----------------
+        {
+          const int l = (warp & 3) * 16 + lane;
+          for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
+            float dv[16];
+            tmem_ld16(t_dx + lane_base + c16 * 16, dv);
+            tmem_ld_wait();
+            if (lane < 16) {
+              float4* dst = (float4*)(smem + SM::kDxT + (l * PP + c16 * 16) * 4);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) dst[c] = make_float4(dv[c * 4], dv[c * 4 + 1], dv[c * 4 + 2], dv[c * 4 + 3]);
+            }
+          }
+        }
+      } else {
+        asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
+      }
+      asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");          // dx tile complete
+    }
+    prev_rows = rows;
+    prev_row0 = row0;
+    fence_before_sync();
   }
 
+  // the I/O warps store the dx rows of the last processed block
+  if (is_io && !failed && nblk > 0) {
+    named_barrier(9, NTH + NIO);
+    store_dx(prev_row0, prev_rows);
+  }
+  __syncthreads();
   if (!failed) {
-    if (a.dinit) {
-      bf16* dp = a.dinit + (bh * a.P) * a.N + n;
+    if (is_col) {
+      if (a.dinit) {
+        float gc[HP];
+        tmem_ld16(t_G, gc);
+        tmem_ld8(t_G + 16, gc + 16);
+        tmem_ld_wait();
+        bf16* dp = a.dinit + (bh * a.P) * a.N + n;
 #pragma unroll
-      for (int p = 0; p < PP; ++p)
-        if (p < a.P) dp[(size_t)p * a.N] = __float2bfloat16_rn(G[p]);
+        for (int j = 0; j < HP; ++j)
+          if (half * HP + j < a.P) dp[(size_t)(half * HP + j) * a.N] = __float2bfloat16_rn(gc[j]);
+      }
+      // dA / ddt_bias partials of the two row halves, summed in a fixed order
+      sXch[half * NT + n] = dAacc;
+      sXch[(2 + half) * NT + n] = dbacc;
     }
-    a.dApart[bh * a.N + n] = dAacc;
-    a.dbpart[bh * a.N + n] = dbacc;
-    // dD partials: element k of thread t always has p = (t + k NT) % P; fixed-order sum per p
     float* red = (float*)(smem + SM::kRed);
-#pragma unroll
-    for (int k = 0; k < XR; ++k) red[k * NT + tid] = (k < npt) ? dDacc[k] : 0.f;
+    if (is_io) red[io_t] = dDacc;
     __syncthreads();
-    if (tid < a.P) {
-      float s = 0.f;
-      for (int i = 0; i < npt * NT; ++i)
-        if (i < QB * a.P && i % a.P == tid) s += red[(i / NT) * NT + (i % NT)];
-      a.dDpart[bh * PP + tid] = s;
+    if (is_col && half == 0) {
+      a.dApart[bh * a.N + n] = sXch[n] + sXch[NT + n];
+      a.dbpart[bh * a.N + n] = sXch[2 * NT + n] + sXch[3 * NT + n];
+    }
+    if (tid == 0) {                                       // scalar dD partial of this (batch, head)
+      float sacc = 0.f;
+      for (int i = 0; i < NIO; ++i) sacc += red[i];
+      a.dDpart[bh] = sacc;
     }
   }
   if (a.status) {
@@ -439,6 +558,26 @@ __global__ void __launch_bounds__(NT, 1) k_bwd_tensor(const TArgs a) {
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// dD[h, p] partials for a per-(head, head-dim) D: sum over the rows of one (batch, head) of dy * x, one
+// warp per head-dim index (the scan kernel only accumulates the per-head scalar)
+__global__ void k_dD_hdim(const TArgs a) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int p = warp; p < a.P; p += blockDim.x >> 5) {
+    float acc = 0.f;
+    for (int l = lane; l < a.L; l += 32) {
+      float dy = __bfloat162float(a.dout[b * a.g_sb + (int64_t)l * a.g_sl + h * a.g_sh + p]);
+      if (a.has_z) {
+        const float z1 = __bfloat162float(a.z[b * a.z_sb + (int64_t)l * a.z_sl + h * a.z_sh + p]);
+        dy *= z1 / (1.f + ex2f(-z1 * LOG2E));
+      }
+      acc = fmaf(__bfloat162float(__float2bfloat16_rn(dy)), __bfloat162float(a.x[b * a.x_sb + (int64_t)l * a.x_sl + h * a.x_sh + p]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) a.dDpart[((size_t)b * a.H + h) * PP + p] = acc;
+  }
 }
 
 // dB[b,l,g,n] = sum over the heads of group g of the bf16 per-head partials
@@ -529,7 +668,7 @@ static int launch_bwd(const TArgs& a, cudaStream_t s) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT>), dim3(1, a.H, a.b), NT, smem, s, a);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a);
   return ISSM_OK;
 }
 
@@ -561,8 +700,12 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   ISSM_LAUNCH(k_reduce_batch, (HN + 127) / 128, 128, 0, s, w.dApart, p.batch, HN, p.dA);
   if (p.has_dt_bias) ISSM_LAUNCH(k_reduce_batch, (HN + 127) / 128, 128, 0, s, w.dbpart, p.batch, HN, p.ddt_bias);
   if (p.has_D) {
-    const int cnt = p.D_has_hdim ? p.nheads * p.headdim : p.nheads;
-    ISSM_LAUNCH(k_reduce_dD, (cnt + 63) / 64, 64, 0, s, w.dDpart, p.batch, p.nheads, p.headdim, p.D_has_hdim, p.dD);
+    if (p.D_has_hdim) {
+      ISSM_LAUNCH(k_dD_hdim, dim3(p.nheads, p.batch), 256, 0, s, a);
+      ISSM_LAUNCH(k_reduce_dD, (p.nheads * p.headdim + 63) / 64, 64, 0, s, w.dDpart, p.batch, p.nheads, p.headdim, 1, p.dD);
+    } else {
+      ISSM_LAUNCH(k_reduce_batch, (p.nheads + 63) / 64, 64, 0, s, w.dDpart, p.batch, p.nheads, p.dD);
+    }
   }
   return ISSM_OK;
 }
