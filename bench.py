@@ -20,6 +20,8 @@ import time
 
 import torch
 
+torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False) if hasattr(torch.autograd.graph, 'set_warn_on_accumulate_grad_stream_mismatch') else None
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -118,19 +120,40 @@ def make_batch(w, batch, sample0, device=None, pin=False):
     return host, par, dfinal
 
 
+_SIDE = {}
+
+
 def layer_step(dev, par, dfinal, w, path):
-    """One bidirectional ISSM layer forward+backward through the public interface."""
+    """One bidirectional ISSM layer forward+backward through the public interface.  The two scan
+    directions are independent, so they are enqueued on two CUDA streams (autograd runs each scan's
+    backward on the stream of its forward): with few samples per GPU one direction alone does not
+    fill the 148 SMs (one CTA per (sample, head))."""
     from dest3d_b200 import ISSM_chunk_scan_combined
+    main = torch.cuda.current_stream()
+    key = torch.cuda.current_device()
+    if key not in _SIDE:
+        _SIDE[key] = (torch.cuda.Stream(), torch.cuda.Stream())
+    s1, s2 = _SIDE[key]
     leaves = {k: v.detach().requires_grad_() for k, v in dev.items() if k not in ("dout",)}
     P_ = {k: v.detach().requires_grad_() for k, v in par.items()}
     kw = dict(D=P_["D"], z=leaves["z"], dt_bias=P_["dt_bias"], initial_states=leaves["init"], dt_softplus=True,
               dt_limit=(1e-3, 1e-1), return_final_states=True, path=path)
-    yf, sf = ISSM_chunk_scan_combined(leaves["x_f"], leaves["dt"], P_["A"], leaves["B_f"], leaves["C_f"], w["Q"], **kw)
-    yb, sb = ISSM_chunk_scan_combined(leaves["x_b"], leaves["dt"], P_["A"], leaves["B_b"], leaves["C_b"], w["Q"],
-                                      reverse=True, **kw)
+    s1.wait_stream(main)
+    s2.wait_stream(main)
+    with torch.cuda.stream(s1):
+        yf, sf = ISSM_chunk_scan_combined(leaves["x_f"], leaves["dt"], P_["A"], leaves["B_f"], leaves["C_f"], w["Q"], **kw)
+    with torch.cuda.stream(s2):
+        yb, sb = ISSM_chunk_scan_combined(leaves["x_b"], leaves["dt"], P_["A"], leaves["B_b"], leaves["C_b"], w["Q"],
+                                          reverse=True, **kw)
+    main.wait_stream(s1)
+    main.wait_stream(s2)
+    for t in (yf, sf, yb, sb):
+        t.record_stream(main)
     out = (yf + yb) * 0.5                       # the reference's combine (models/dest_module.py:574)
     fin = (sf + sb) * 0.5
     torch.autograd.backward([out, fin], [dev["dout"], dfinal])
+    main.wait_stream(s1)
+    main.wait_stream(s2)
     return out, fin, {"dA": P_["A"].grad, "ddt_bias": P_["dt_bias"].grad, "dD": P_["D"].grad}
 
 
@@ -244,17 +267,19 @@ def kernel_roofline(dev, par, dfinal, w, batch, path):
     reps, tf, tb = 3, 0.0, 0.0
     for i in range(reps + 1):
         e[0].record()
-        out, out_x, fin = issm_fwd(dev["x_f"], dev["dt"], par["A"], dev["B_f"], dev["C_f"], w["Q"], **kw)
+        out, out_x, fin, saved = issm_fwd(dev["x_f"], dev["dt"], par["A"], dev["B_f"], dev["C_f"], w["Q"],
+                                          save_states=True, **kw)
         e[1].record()
         issm_bwd(dev["dout"], dev["x_f"], dev["dt"], par["A"], dev["B_f"], dev["C_f"], out_x, w["Q"],
-                 dfinal_states=dfinal, **kw)
+                 dfinal_states=dfinal, saved_states=saved, **kw)
         e[2].record()
         torch.cuda.synchronize()
         if i:
             tf += e[0].elapsed_time(e[1]) / reps
             tb += e[1].elapsed_time(e[2]) / reps
     fb, bb = algorithmic_bytes(batch, w["L"], w["H"], w["P"], w["N"], dirs=1)
-    which, t, nbytes = ("forward call (k_fwd_tensor)", tf, fb) if tf >= tb else ("backward call", tb, bb)
+    which, t, nbytes = (("forward call (k_fwd_tensor)", tf, fb) if tf >= tb else
+                        ("backward call (k_bwd_tensor + head/batch reductions)", tb, bb))
     ach = nbytes / (t * 1e-3) / 1e9
     return {"bound": "hbm", "kernel": which, "achieved": ach, "peak": hbm, "peak_source": src, "unit": "GB/s",
             "frac": ach / hbm, "traffic": None, "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": t,

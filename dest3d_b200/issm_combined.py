@@ -9,6 +9,7 @@ models/dest_module.py:567-573 does with four torch.flip calls), and `path` selec
 """
 import ctypes as ct
 import math
+import os
 
 import torch
 
@@ -110,6 +111,18 @@ def _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_s
     return p, keep
 
 
+def _check_status(device, what):
+    """With ISSM_B200_CHECK_STATUS=1 every call synchronises and raises on a device status bit (debug aid:
+    the status word is otherwise only read by `device_status`)."""
+    if os.environ.get("ISSM_B200_CHECK_STATUS") == "1":
+        v = device_status(device)
+        if v & 1:
+            raise RuntimeError(f"{what}: a bounded device-side wait expired (status {v})")
+        if v & 2:
+            raise RuntimeError(f"{what}: a 64-point block exceeded the decay range of the tensor-core path "
+                               f"(dt*|A| summed over the block > 83); rerun with path='simt'")
+
+
 def _workspace(p, pass_, device, keep):
     need = _lib.lib().issm_b200_workspace_bytes(ct.byref(p), pass_)
     ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=device)
@@ -141,6 +154,7 @@ def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_s
         rc = _lib.lib().issm_b200_fwd(ct.byref(p), _lib.stream_ptr(x.device))
     if rc:
         raise _lib.IssmError(rc, "issm_b200_fwd")
+    _check_status(x.device, "issm_b200_fwd")
     return (out, out_x, final, saved) if save_states else (out, out_x, final)
 
 
@@ -185,6 +199,7 @@ def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=No
         rc = _lib.lib().issm_b200_bwd(ct.byref(p), _lib.stream_ptr(dev))
     if rc:
         raise _lib.IssmError(rc, "issm_b200_bwd")
+    _check_status(dev, "issm_b200_bwd")
     return dx, ddt, dA, dB, dC, dD, dz, dbias, dinit
 
 

@@ -83,6 +83,22 @@ def test_parity_tensor(case):
     parity.compare(got, ref, torch.bfloat16, want_final=opts.get("return_final", True))
 
 
+def test_tensor_path_flags_out_of_range_blocks(monkeypatch):
+    """dt*|A| summed over a 64-point block beyond the factorisation range sets status bit 1; with
+    ISSM_B200_CHECK_STATUS=1 the call raises instead of returning unchecked values."""
+    from dest3d_b200 import ISSM_chunk_scan_combined
+    from dest3d_b200.issm_combined import device_status
+    inp, Q = _inputs((1, 128, 1, 36, 128, 1, 64), {}, dict(dt_scale=5.0), torch.bfloat16)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    device_status()
+    ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, dt_bias=c["dt_bias"], dt_softplus=True, path="tensor")
+    assert device_status() & 2
+    monkeypatch.setenv("ISSM_B200_CHECK_STATUS", "1")
+    with pytest.raises(RuntimeError, match="decay range"):
+        ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, dt_bias=c["dt_bias"], dt_softplus=True, path="tensor")
+    device_status()
+
+
 def test_tensor_backward_without_saved_states():
     """The C ABI backward recomputes the block-entry states when the caller kept none."""
     from dest3d_b200 import issm_bwd, issm_fwd
