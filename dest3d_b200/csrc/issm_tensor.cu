@@ -18,6 +18,8 @@
 // while the current block computes.
 #include "issm_tensor.cuh"
 
+#include <cstring>
+
 namespace issm {
 
 template <int NT>
@@ -44,7 +46,7 @@ struct FwdSmem {
 // every bulk prefetch.  The I/O warps load the x / z rows of the block, build the x operand tile and
 // store the previous block's output rows (D skip and gate applied) with coalesced accesses.
 template <int NT, typename TDT>
-__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;                           // column threads
@@ -92,16 +94,18 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
   // the block at staged row rows-1-l (see srow below).
   auto prefetch = [&](int blk) {
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
-    if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * (kStageDt ? 3 : 2));
+    const bool dt_tile = kStageDt && a.dt_tma;
+    const int64_t m0 = a.rev ? a.L - row0 - rows : row0;            // lowest memory row of the tile
+    if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * 2 + (kStageDt ? (uint32_t)(dt_tile ? QB : rows) * NT * 2 : 0u));
     __syncwarp();
+    if (dt_tile && lane == 2) tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh, b * a.L + (int)m0, barS);
     if (a.bc_contig) {
-      const int64_t m0 = a.rev ? a.L - row0 - rows : row0;          // lowest memory row of the tile
       if (lane == 0) bulk_g2s(smem + SM::kSB, Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2, barS);
       if (lane == 1) bulk_g2s(smem + SM::kSC, Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2, barS);
     }
     for (int l = lane; l < rows; l += 32) {
       const int64_t mr = trow(a, row0 + l);
-      if (kStageDt) bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + mr * a.dt_sl, NT * 2, barS);
+      if (kStageDt && !dt_tile) bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + mr * a.dt_sl, NT * 2, barS);
       if (!a.bc_contig) {
         bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + mr * a.B_sl, NT * 2, barS);
         bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
@@ -112,7 +116,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
 
   uint8_t* sop_col = smem + SM::kSop + (n >> 6) * SM::kAtomB;
   const int kcol = n & 63;
-  bf16* savep = a.saved ? a.saved + ((((size_t)b * a.H + h) * (nblk + 1)) * a.N + n) * PP + half * HP : nullptr;
+  // saved block-entry states: (b, H, nblk + 1, PP / 8, N, 8) bf16, i.e. per block the interleaved
+  // [head-dim chunk][state][8] layout the backward uses directly as an MMA operand
+  bf16* savep = a.saved ? a.saved + (((size_t)b * a.H + h) * (nblk + 1)) * a.N * PP + ((size_t)half * (HP / 8) * a.N + n) * 8 : nullptr;
   // bf16 operand copy and saved copy of this thread's HP state values
   auto publish_state = [&](const float* sc, int blk_index) {
     if (!a.no_output) {
@@ -120,10 +126,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
       for (int j = 0; j < HP; ++j) *(bf16*)(sop_col + sw128_off(half * HP + j, kcol)) = __float2bfloat16_rn(sc[j]);
     }
     if (savep) {
-      uint4* dst = (uint4*)(savep + (size_t)blk_index * a.N * PP);
+      bf16* dst = savep + (size_t)blk_index * a.N * PP;
 #pragma unroll
       for (int c = 0; c < HP / 8; ++c)
-        dst[c] = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
+        *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
                             pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
     }
   };
@@ -241,7 +247,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const float raw = kStageDt ? __bfloat162float(sdt[l * NT])
+          const int sl = (a.dt_tma && a.rev) ? max(rows - 1 - l, 0) : l;   // a TMA tile is staged in memory order
+          const float raw = kStageDt ? __bfloat162float(sdt[sl * NT])
                                      : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
           bool clamped;
           const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
@@ -439,24 +446,59 @@ TArgs make_targs(const issm_params& p) {
   a.status = p.status;
   a.saved = (bf16*)p.saved_states;
   a.bc_contig = (p.B_sl == p.dstate && p.C_sl == p.dstate);
+  a.dt_tma = 0;
   return a;
 }
 
+// ---- tensor map over dt ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) { (void)cudaGetLastError(); f = nullptr; }
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
+  memset(out, 0, sizeof(*out));
+  if (p.dt_dtype != ISSM_BF16) return false;
+  // rows (b, l) must form one regular array: batch stride = seqlen * row stride; 16-byte aligned rows
+  if (p.dt_sb != (int64_t)p.seqlen * p.dt_sl || (p.dt_sl & 7) || (p.dt_sh & 7) || ((uintptr_t)p.dt & 15)) return false;
+  const uint64_t width = (uint64_t)(p.nheads - 1) * p.dt_sh + p.dstate;
+  if (width > (uint64_t)p.dt_sl || (uint64_t)p.batch * p.seqlen > 0x7fffffffull) return false;
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t gdim[2] = {width, (cuuint64_t)p.batch * p.seqlen};
+  const cuuint64_t gstride[1] = {(cuuint64_t)p.dt_sl * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)p.dstate, (cuuint32_t)QB};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.dt), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int NT, typename TDT>
-static int launch_fwd(const TArgs& a, cudaStream_t s) {
+static int launch_fwd(TArgs a, const issm_params& p, cudaStream_t s) {
+  CUtensorMap dtmap;
+  a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
   const size_t smem = FwdSmem<NT>::kTotal + 1024;
   if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
   return ISSM_OK;
 }
 
 int tensor_fwd(const issm_params& p, cudaStream_t s) {
   const TArgs a = make_targs(p);
-  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, s) : launch_fwd<256, float>(a, s);
-  return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, s) : launch_fwd<128, float>(a, s);
+  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
+  return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);
 }
 
 // forward walk that only regenerates the block-entry states (for a backward without saved states)
@@ -465,8 +507,8 @@ int tensor_fwd_states_only(const issm_params& p, bf16* saved, cudaStream_t s) {
   a.saved = saved;
   a.no_output = 1;
   a.want_final = 0;
-  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, s) : launch_fwd<256, float>(a, s);
-  return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, s) : launch_fwd<128, float>(a, s);
+  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
+  return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);
 }
 
 }  // namespace issm

@@ -1,6 +1,8 @@
 // Declarations shared by the forward and backward kernels of the tcgen05 ISSM path.
 #pragma once
 
+#include <cuda.h>
+
 #include <type_traits>
 
 #include "issm_common.cuh"
@@ -18,6 +20,7 @@ constexpr float LN2 = 0.6931471805599453f;
 struct TArgs {
   int b, L, H, P, N, G, hpg, rev;
   int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
+  int dt_tma;       // dt is a regular 2-D array of rows: a 64-row tile is ONE tiled TMA load through a tensor map
   int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
   float dtmin, dtmax;
   const bf16* x; int64_t x_sb, x_sl, x_sh;
@@ -30,7 +33,7 @@ struct TArgs {
   bf16* out; int64_t o_sb, o_sl, o_sh;
   bf16* out_x;
   float* final_states;
-  bf16* saved;      // optional (b, H, nblk + 1, N, PP) bf16: state entering every 64-point block, and the final one
+  bf16* saved;      // optional (b, H, nblk + 1, PP / 8, N, 8) bf16: state entering every 64-point block, and the final one
   int* status;
   // backward
   const bf16* dout; int64_t g_sb, g_sl, g_sh;
@@ -105,6 +108,9 @@ __device__ __forceinline__ float build_operands(const TArgs& a, int rows, int ro
 }
 
 TArgs make_targs(const issm_params& p);
+// Tensor map over bf16 dt viewed as (batch*seqlen rows) x (row pitch) with a (dstate x 64 rows) box; false if dt
+// is not laid out as one regular 2-D array (then the kernels fall back to one bulk copy per row).
+bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out);
 int tensor_fwd_states_only(const issm_params& p, bf16* saved, cudaStream_t s);
 size_t tensor_bwd_workspace_bytes(const issm_params& p);
 

@@ -27,7 +27,8 @@ template <int NT>
 struct BwdSmem {
   static constexpr int kCd = 0;                         // [NT/64 atoms][64 l][128 B]
   static constexpr int kBd = kCd + NT * 128;
-  static constexpr int kGop = kBd + NT * 128;           // [NT n][128 B]: g' rows, p contiguous (SW128)
+  static constexpr int kGop = kBd + NT * 128;           // [NT n][128 B]: g' rows, p contiguous (SW128) ...
+  static constexpr int kSC = kGop;                      // ... time-shared with the staged C rows [64][NT] bf16
   static constexpr int kSop = kGop + NT * 128;          // [PP/8][NT n][16 B]: S rows (interleaved)
   static constexpr int kX = kSop + NT * (PP * 2);       // [64 l][128 B]
   static constexpr int kDy = kX + QB * 128;             // [64 l][128 B]
@@ -47,7 +48,7 @@ struct BwdSmem {
 // the operand pass and in the (row, state) epilogue, and columns [24 half, 24 half + 24) of TMEM lane n
 // of the state gradient G, which lives in TMEM for the whole walk.
 template <int NT, typename TDT>
-__global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = BwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;
@@ -62,7 +63,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
   uint64_t* bar2 = bar1 + 1;
   uint64_t* barS = bar1 + 2;     // dt staging
   uint64_t* barT = bar1 + 3;     // B staging
-  uint32_t* tmem_holder = (uint32_t*)(bar1 + 4);
+  uint64_t* barU = bar1 + 4;     // S operand (saved block-entry state)
+  uint64_t* barV = bar1 + 5;     // C staging
+  uint32_t* tmem_holder = (uint32_t*)(bar1 + 6);
   float* sXch = (float*)(smem + SM::kXch);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -74,7 +77,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
   const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
   const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
-  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg + n;
+  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg;
   const bf16* __restrict__ xp = a.x + b * a.x_sb + h * a.x_sh;
   const bf16* __restrict__ zp = a.has_z ? a.z + b * a.z_sb + h * a.z_sh : nullptr;
   const bf16* __restrict__ yp = a.has_z ? a.out_x + b * a.o_sb + h * a.o_sh : nullptr;
@@ -86,7 +89,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
   const size_t bh = (size_t)b * a.H + h;
 
   for (int i = tid; i < (SM::kSdt - SM::kGop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kGop))[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) { mbar_init(bar1, 1); mbar_init(bar2, 1); mbar_init(barS, 1); mbar_init(barT, 1); mbar_fence_init(); }
+  if (tid == 0) {
+    mbar_init(bar1, 1); mbar_init(bar2, 1); mbar_init(barS, 1); mbar_init(barT, 1); mbar_init(barU, 1); mbar_init(barV, 1);
+    mbar_fence_init();
+  }
   if (warp == 0) { tmem_alloc(tmem_holder, 512); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
@@ -105,6 +111,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
   auto prefetch_dt = [&](int blk) {
     if (!kStageDt) return;
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
+    if (a.dt_tma) {                                        // one tiled TMA load; the tile is staged in memory order
+      if (lane == 0) {
+        mbar_expect_tx(barS, (uint32_t)QB * NT * 2);
+        tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh, b * a.L + (a.rev ? a.L - row0 - rows : row0), barS);
+      }
+      return;
+    }
     if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2);
     __syncwarp();
     for (int l = lane; l < rows; l += 32)
@@ -122,7 +135,27 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
         bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + (int64_t)trow(a, row0 + l) * a.B_sl, NT * 2, barT);
     }
   };
-  if (is_svc) { prefetch_dt(nblk - 1); prefetch_B(nblk - 1); }
+  // C rows share their buffer with the g' operand: valid from here until the operand pass of the block ends
+  auto prefetch_C = [&](int blk) {
+    const int row0 = blk * QB, rows = min(QB, a.L - row0);
+    if (lane == 0) mbar_expect_tx(barV, (uint32_t)rows * NT * 2);
+    __syncwarp();
+    if (a.bc_contig) {
+      const int64_t m0 = a.rev ? a.L - row0 - rows : row0;
+      if (lane == 0) bulk_g2s(smem + SM::kSC, Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2, barV);
+    } else {
+      for (int l = lane; l < rows; l += 32)
+        bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + (int64_t)trow(a, row0 + l) * a.C_sl, NT * 2, barV);
+    }
+  };
+  // state entering block `blk` (or the final state, blk = nblk): one copy, already in operand layout
+  auto prefetch_S = [&](int blk) {
+    if (lane == 0) {
+      mbar_expect_tx(barU, (uint32_t)NT * PP * 2);
+      bulk_g2s(smem + SM::kSop, a.saved + (bh * (nblk + 1) + blk) * (size_t)a.N * PP, (uint32_t)NT * PP * 2, barU);
+    }
+  };
+  if (is_svc) { prefetch_dt(nblk - 1); prefetch_B(nblk - 1); prefetch_C(nblk - 1); prefetch_S(nblk); }
 
   // ---- column threads: G <- dfinal ---------------------------------------------------------------------
   if (is_col) {
@@ -241,17 +274,17 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
     }
 
     if (is_col) {
-      // ---- <S leaving the block, G> over this thread's state columns; S operand rows of the entering state ----
+      // ---- <S leaving the block, G> over this thread's state columns: the S operand tile still holds the
+      //      state entering the block processed before this one, i.e. the state leaving this block ------------
       float cpart = 0.f;
       {
         float gc[HP];
         tmem_ld16(t_G, gc);
         tmem_ld8(t_G + 16, gc + 16);
-        const uint4* sn = (const uint4*)(a.saved + ((bh * (nblk + 1) + blk + 1) * a.N + n) * PP + half * HP);
-        const uint4* sc = (const uint4*)(a.saved + ((bh * (nblk + 1) + blk) * a.N + n) * PP + half * HP);
-        uint4 snv[HP / 8], scv[HP / 8];
+        if (!mbar_wait(barU, parity)) failed = true;
+        uint4 snv[HP / 8];
 #pragma unroll
-        for (int c = 0; c < HP / 8; ++c) { snv[c] = sn[c]; scv[c] = sc[c]; }
+        for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < HP / 8; ++c) {
@@ -261,7 +294,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
             cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
             cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
           }
-          *(uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16) = scv[c];
         }
       }
       if (kStageDt && !mbar_wait(barS, parity)) failed = true;
@@ -273,7 +305,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const float raw = kStageDt ? __bfloat162float(sdt[l * NT])
+          const int sl = (a.dt_tma && a.rev) ? max(rows - 1 - l, 0) : l;
+          const float raw = kStageDt ? __bfloat162float(sdt[sl * NT])
                                      : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
           bool clamped = false;
           const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
@@ -292,33 +325,33 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
 
       if (!mbar_wait(barT, parity)) failed = true;
 
-      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a (C straight from global memory,
-      //      16 unconditional loads in flight) ---------------------------------------------------------------
+      if (!mbar_wait(barV, parity)) failed = true;
+      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
       {
         uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
         uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
         const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+        const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
         float acc = half ? a0 : 0.f;
 #pragma unroll
-        for (int j0 = 0; j0 < 32; j0 += 16) {
-          bf16 cl[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            cl[j] = Cp[(int64_t)trow(a, row0 + min(half * 32 + j0 + j, rows - 1)) * a.C_sl];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int l = half * 32 + j0 + j;
-            const bool valid = l < rows;
-            const int sl = flipB ? max(rows - 1 - l, 0) : l;
-            acc = fmaf(dtv[j0 + j], A2, acc);
-            const float cd = valid ? __bfloat162float(cl[j]) * ex2f(acc) : 0.f;
-            const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j0 + j] * ex2f(-acc) : 0.f;
-            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
-            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-          }
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const bool valid = l < rows;
+          const int sl = flipB ? max(rows - 1 - l, 0) : l;
+          acc = fmaf(dtv[j], A2, acc);
+          const float cd = valid ? __bfloat162float(sC[sl * NT]) * ex2f(acc) : 0.f;
+          const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j] * ex2f(-acc) : 0.f;
+          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
         }
       }
+      fence_async_smem();
+    }
+    fence_before_sync();
+    if (__syncthreads_or(failed)) { failed = true; break; }
+
+    if (is_col) {
       // ---- g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -----------
       {
         float gc[HP];
@@ -337,10 +370,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
                          pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
         tmem_st_wait();
       }
-      fence_async_smem();
     }
-    fence_before_sync();
-    if (__syncthreads_or(failed)) { failed = true; break; }
 
     // ---- MMA phase 1: dM = dy x^T, M = Cd Bd^T (service warp) --------------------------------------------
     if (is_svc) {
@@ -358,7 +388,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
         mma_commit(bar1);
       }
       __syncwarp();
-      if (blk > 0) prefetch_dt(blk - 1);                   // every column thread is past phase A
+      if (blk > 0) prefetch_dt(blk - 1);                   // every column thread is past phase A ...
+      prefetch_S(blk);                                     // ... and has read the previous content of the S tile
     }
 
     if (is_col) {
@@ -396,6 +427,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
     if (is_svc) {
       if (lane == 0) {
         fence_after_sync();
+        if (!mbar_wait(barU, parity ^ 1)) { if (a.status) atomicOr(a.status, 1); }   // S tile of this block has landed
 #pragma unroll
         for (int sl = 0; sl < NT / 128; ++sl) {
           const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
@@ -425,8 +457,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
       }
       __syncwarp();
       if (blk > 0) {                                       // B staging is free once every column thread has
-        named_barrier(10, NTH + 32);                       // finished its (row, state) epilogue
-        prefetch_B(blk - 1);
+        named_barrier(10, NTH + 32);                       // finished its (row, state) epilogue (the MMAs that
+        prefetch_B(blk - 1);                               // read the g' tile are complete by then, too)
+        prefetch_C(blk - 1);
       }
     }
 
@@ -440,14 +473,14 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
         const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
         float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          float bdv[16], cdv[16];
-          tmem_ld16(t_BD + ch * 16, bdv);
-          tmem_ld16(t_CD + ch * 16, cdv);
+        for (int ch = 0; ch < 4; ++ch) {
+          float bdv[8], cdv[8];
+          tmem_ld8(t_BD + ch * 8, bdv);
+          tmem_ld8(t_CD + ch * 8, cdv);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t off = (uint32_t)((half * 32 + ch * 16 + j) * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t off = (uint32_t)((half * 32 + ch * 8 + j) * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
             part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
             part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
           }
@@ -459,20 +492,20 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a) {
         float prefix = half ? p0 : 0.f;
         float ac = half ? a0 : 0.f;
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          float bdv[16], cdv[16];
-          tmem_ld16(t_BD + ch * 16, bdv);
-          tmem_ld16(t_CD + ch * 16, cdv);
+        for (int ch = 0; ch < 4; ++ch) {
+          float bdv[8], cdv[8];
+          tmem_ld8(t_BD + ch * 8, bdv);
+          tmem_ld8(t_CD + ch * 8, cdv);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int jj = ch * 16 + j;
+          for (int j = 0; j < 8; ++j) {
+            const int jj = ch * 8 + j;
             const int l = half * 32 + jj;
             const bool valid = l < rows;
             const float dtl = dtv[jj];
             ac = fmaf(dtl, A2, ac);
             const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
-            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
             const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
                                __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
             const float ddA = cst + total - prefix;          // sum of dacs over rows >= l, plus <S_next, G>
@@ -662,13 +695,15 @@ size_t tensor_bwd_workspace_bytes(const issm_params& p) {
 }
 
 template <int NT, typename TDT>
-static int launch_bwd(const TArgs& a, cudaStream_t s) {
+static int launch_bwd(TArgs a, const issm_params& p, cudaStream_t s) {
+  CUtensorMap dtmap;
+  a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
   const size_t smem = BwdSmem<NT>::kTotal + 1024;
   if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
   return ISSM_OK;
 }
 
@@ -689,8 +724,8 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   a.dx = (bf16*)p.dx; a.ddt = p.ddt; a.dz = (bf16*)p.dz; a.dinit = (bf16*)p.dinitial_states;
   a.dBh = w.dBh; a.dCh = w.dCh; a.dApart = w.dApart; a.dbpart = w.dbpart; a.dDpart = w.dDpart;
   int rc;
-  if (p.dstate == 256) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, s) : launch_bwd<256, float>(a, s);
-  else rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<128, bf16>(a, s) : launch_bwd<128, float>(a, s);
+  if (p.dstate == 256) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, p, s) : launch_bwd<256, float>(a, p, s);
+  else rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<128, bf16>(a, p, s) : launch_bwd<128, float>(a, p, s);
   if (rc) return rc;
   const int hpg = p.nheads / p.ngroups;
   const size_t tot = (size_t)p.batch * p.seqlen * p.ngroups * (p.dstate / 8);
