@@ -149,49 +149,51 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     tmem_st_wait();
   }
 
-  // I/O threads: tile element k of thread t is flat index t + k * NIO of the [64][P] tile
+  // I/O threads work on groups of 4 consecutive head-dim elements (8-byte accesses; headdim % 4 == 0):
+  // group k of thread t is flat index t + k * NIO of the [64][P / 4] grid; (row, group) advance by
+  // (NIO / (P/4), NIO % (P/4)), so there is no division in the loops.  All loads of a pass are
+  // unconditional (row clamped into the block) and in flight together.
   const float dscalar = (a.has_D && !a.D_has_hdim) ? __ldg(a.D + h) : 0.f;
-  // I/O threads: element k of thread t is flat index t + k * NIO of the [64][P] tile; (row, head-dim
-  // index) advance by (NIO / P, NIO % P) per element, so no division in the loops.  Elements are
-  // handled in chunks of CH: all loads of a chunk are unconditional (row clamped into the block) and in
-  // flight together; nothing is kept in registers across chunks.
-  constexpr int XR = (QB * PP + NIO - 1) / NIO;          // 32
-  constexpr int CH = 8;
-  const int io_l0 = io_t / a.P, io_p0 = io_t % a.P, io_dl = NIO / a.P, io_dp = NIO % a.P;
-  auto io_next = [&](int& l, int& p) {
-    l += io_dl; p += io_dp;
-    if (p >= a.P) { p -= a.P; ++l; }
+  constexpr int XG = (QB * (PP / 4) + NIO - 1) / NIO;    // groups per I/O thread (8)
+  const int ngrp = a.P / 4;
+  const int io_l0 = io_t / ngrp, io_g0 = io_t % ngrp, io_dl = NIO / ngrp, io_dg = NIO % ngrp;
+  auto io_next = [&](int& l, int& gq) {
+    l += io_dl; gq += io_dg;
+    if (gq >= ngrp) { gq -= ngrp; ++l; }
   };
-  // out = (y + D x) * silu(z) for the output rows of a finished block; coalesced over p
+  auto bf_lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+  auto bf_hi = [](uint32_t w) { return __uint_as_float(w & 0xffff0000u); };
+  // out = (y + D x) * silu(z) for the output rows of a finished block
   auto store_tile = [&](int t_row0, int t_rows) {
-    int l = io_l0, p = io_p0;
-#pragma unroll 1
-    for (int c = 0; c < XR / CH; ++c) {
-      bf16 xv[CH], zv[CH];
-      int lc = l, pc = p;
+    uint2 xv[XG], zv[XG];
+    int l = io_l0, gq = io_g0;
 #pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        const int64_t mr = trow(a, t_row0 + min(lc, t_rows - 1));
-        xv[k] = xp[mr * a.x_sl + pc];
-        zv[k] = a.has_z ? zp[mr * a.z_sl + pc] : __float2bfloat16_rn(0.f);
-        io_next(lc, pc);
-      }
+    for (int k = 0; k < XG; ++k) {
+      const int64_t mr = trow(a, t_row0 + min(l, t_rows - 1));
+      xv[k] = *(const uint2*)(xp + mr * a.x_sl + gq * 4);
+      zv[k] = a.has_z ? *(const uint2*)(zp + mr * a.z_sl + gq * 4) : make_uint2(0, 0);
+      io_next(l, gq);
+    }
+    l = io_l0; gq = io_g0;
 #pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        if (l < t_rows) {
-          float y = *(const float*)(smem + SM::kY + (l * PP + p) * 4);
-          const float dc = a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar;
-          y = fmaf(dc, __bfloat162float(xv[k]), y);
-          const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + p;
-          if (a.has_z) {
-            a.out_x[o] = __float2bfloat16_rn(y);
-            const float z1 = __bfloat162float(zv[k]);
-            y *= z1 / (1.f + ex2f(-z1 * LOG2E));
-          }
-          a.out[o] = __float2bfloat16_rn(y);
+    for (int k = 0; k < XG; ++k) {
+      if (l < t_rows) {
+        const float4 yv = *(const float4*)(smem + SM::kY + (l * PP + gq * 4) * 4);
+        float y[4] = {yv.x, yv.y, yv.z, yv.w};
+        const float xf[4] = {bf_lo(xv[k].x), bf_hi(xv[k].x), bf_lo(xv[k].y), bf_hi(xv[k].y)};
+        const float zf[4] = {bf_lo(zv[k].x), bf_hi(zv[k].x), bf_lo(zv[k].y), bf_hi(zv[k].y)};
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          y[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, xf[q], y[q]);
+        const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + gq * 4;
+        if (a.has_z) {
+          *(uint2*)(a.out_x + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) y[q] *= zf[q] / (1.f + ex2f(-zf[q] * LOG2E));
         }
-        io_next(l, p);
+        *(uint2*)(a.out + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
       }
+      io_next(l, gq);
     }
   };
 
@@ -210,29 +212,21 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     const uint32_t parity = blk & 1;
     float alast = 0.f;
     if (is_io) {
-      // ---- output rows of the previous block (its accumulator tile is complete once every column warp
-      //      has arrived on the named barrier), then the x rows of this block ------------------------------
-      if (blk > 0 && !a.no_output) {
-        named_barrier(9, NTH + NIO);
-        store_tile(prev_row0, prev_rows);
+      // ---- x rows of this block -> x operand tile [l][p] (swizzled rows); the tile is free once the last
+      //      MMA of the previous block has completed ---------------------------------------------------------
+      if (blk > 0 && !a.no_output && !mbar_wait(barB, parity ^ 1)) failed = true;
+      uint2 xv[XG];
+      int l = io_l0, gq = io_g0;
+#pragma unroll
+      for (int k = 0; k < XG; ++k) {
+        xv[k] = *(const uint2*)(xp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.x_sl + gq * 4);
+        io_next(l, gq);
       }
-      {
-        int l = io_l0, p = io_p0;
-#pragma unroll 1
-        for (int c = 0; c < XR / CH; ++c) {
-          bf16 xv[CH];
-          int lc = l, pc = p;
+      l = io_l0; gq = io_g0;
 #pragma unroll
-          for (int k = 0; k < CH; ++k) {
-            xv[k] = xp[(int64_t)trow(a, row0 + min(lc, rows - 1)) * a.x_sl + pc];
-            io_next(lc, pc);
-          }
-#pragma unroll
-          for (int k = 0; k < CH; ++k) {
-            if (l < QB) *(bf16*)(smem + SM::kX + sw128_off(l, p)) = l < rows ? xv[k] : __float2bfloat16_rn(0.f);
-            io_next(l, p);
-          }
-        }
+      for (int k = 0; k < XG; ++k) {
+        if (l < QB) *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = l < rows ? xv[k] : make_uint2(0, 0);
+        io_next(l, gq);
       }
       fence_async_smem();
     }
@@ -311,6 +305,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
       __syncwarp();
       if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
     }
+    // ---- output rows of the previous block: its accumulator tile was completed before this barrier and is
+    //      not rewritten until after the next one -----------------------------------------------------------------
+    if (is_io && blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
 
     if (is_col) {
       if (!mbar_wait(barA, parity)) failed = true;
@@ -390,7 +387,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
           }
         }
       }
-      if (blk + 1 < nblk) asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");   // output tile complete
     }
     fence_before_sync();
   }
@@ -411,7 +407,11 @@ static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 bool tensor_path_supported(const issm_params& p) {
   if (p.io_dtype != ISSM_BF16) return false;
-  if (p.headdim > PP) return false;
+  // the tile-I/O warps move 4 head-dim elements (8 bytes) at a time; the backward's dx tile holds 40 columns
+  if (p.headdim > 40 || (p.headdim & 3)) return false;
+  if ((p.x_sb | p.x_sl | p.x_sh | p.out_sb | p.out_sl | p.out_sh | p.dout_sb | p.dout_sl | p.dout_sh) & 3) return false;
+  if (p.has_z && ((p.z_sb | p.z_sl | p.z_sh) & 3)) return false;
+  if (((uintptr_t)p.x | (uintptr_t)p.z | (uintptr_t)p.out | (uintptr_t)p.out_x | (uintptr_t)p.dout | (uintptr_t)p.dx | (uintptr_t)p.dz) & 7) return false;
   if (p.dstate != 128 && p.dstate != 256) return false;
   // bulk (TMA) row copies need 16-byte aligned rows of B, C and (bf16) dt
   if (p.B && (!aligned16(p.B) || !aligned16(p.C))) return false;

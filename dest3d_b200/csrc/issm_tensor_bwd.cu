@@ -34,12 +34,13 @@ struct BwdSmem {
   static constexpr int kDy = kX + QB * 128;             // [64 l][128 B]
   static constexpr int kDMm = kDy + QB * 128;           // [64 l][128 B], s contiguous
   static constexpr int kMm = kDMm + QB * 128;           // [64 l][128 B]
-  static constexpr int kDxT = kDMm;                     // [64][PP] float, aliases dMm + Mm after the MMAs
   static constexpr int kSdt = kMm + QB * 128;           // staging [64][NT] bf16
   static constexpr int kSB = kSdt + QB * NT * 2;
   static constexpr int kXch = kSB + QB * NT * 2;        // [4][NT] float: per-half exchange (sum dt*A, <S,G>, sum dacs)
   static constexpr int kRed = kSdt;                     // dD reduction scratch (after the walk)
-  static constexpr int kBars = kXch + 4 * NT * 4;
+  static constexpr int kDxT = kXch + 4 * NT * 4;        // [64][DXS] bf16: dx accumulator rows on their way to global memory
+  static constexpr int DXS = 40;                        // row stride of that tile (headdim <= 40 on this path)
+  static constexpr int kBars = kDxT + QB * DXS * 2;
   static constexpr int kTotal = kBars + 64;
 };
 
@@ -54,7 +55,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   constexpr int NTH = 2 * NT;
   constexpr int NIO = 96;
   constexpr int XR = (QB * PP + NIO - 1) / NIO;         // 32 tile elements per I/O thread
-  constexpr int CH = 8;
   constexpr int HP = PP / 2;
   constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
@@ -168,61 +168,58 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
     tmem_st_wait();
   }
 
-  // ---- I/O threads: flat element walk over the [64][P] tile (see the forward kernel) ---------------------
-  const int io_l0 = io_t / a.P, io_p0 = io_t % a.P, io_dl = NIO / a.P, io_dp = NIO % a.P;
-  auto io_next = [&](int& l, int& p) {
-    l += io_dl; p += io_dp;
-    if (p >= a.P) { p -= a.P; ++l; }
+  // ---- I/O threads: groups of 4 consecutive head-dim elements, 8-byte accesses (see the forward kernel) -----
+  constexpr int XG = (QB * (PP / 4) + NIO - 1) / NIO;    // groups per I/O thread (8)
+  const int ngrp = a.P / 4;
+  const int io_l0 = io_t / ngrp, io_g0 = io_t % ngrp, io_dl = NIO / ngrp, io_dg = NIO % ngrp;
+  auto io_next = [&](int& l, int& gq) {
+    l += io_dl; gq += io_dg;
+    if (gq >= ngrp) { gq -= ngrp; ++l; }
   };
+  auto bf_lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+  auto bf_hi = [](uint32_t w) { return __uint_as_float(w & 0xffff0000u); };
   const float dscalar = (a.has_D && !a.D_has_hdim) ? __ldg(a.D + h) : 0.f;
   float dDacc = 0.f;                                     // sum of dy * x over this thread's elements
-  // dy (and dz) of a chunk of elements: dy = dout * z sigmoid(z), dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
-  // (issm_chunk_scan.py:351-360); loads are unconditional with the row clamped into the block
-  auto load_dy = [&](int t_row0, int t_rows, int l, int p, bool write_dz, float* dyv, bf16* xv) {
-    bf16 gv[CH], zv[CH], yv[CH];
-    int lc = l, pc = p;
+  // dy = dout * z sigmoid(z) as the MMAs see it (rounded to bf16), for one group of 4
+  auto gate_dy = [&](uint2 gv, uint2 zv, float* dy) {
+    dy[0] = bf_lo(gv.x); dy[1] = bf_hi(gv.x); dy[2] = bf_lo(gv.y); dy[3] = bf_hi(gv.y);
+    if (zp) {
+      const float zf[4] = {bf_lo(zv.x), bf_hi(zv.x), bf_lo(zv.y), bf_hi(zv.y)};
 #pragma unroll
-    for (int k = 0; k < CH; ++k) {
-      const int64_t mr = trow(a, t_row0 + min(lc, t_rows - 1));
-      xv[k] = xp[mr * a.x_sl + pc];
-      gv[k] = gp[mr * a.g_sl + pc];
-      zv[k] = zp ? zp[mr * a.z_sl + pc] : __float2bfloat16_rn(0.f);
-      yv[k] = (zp && write_dz) ? yp[mr * a.o_sl + pc] : __float2bfloat16_rn(0.f);
-      io_next(lc, pc);
+      for (int q = 0; q < 4; ++q) dy[q] *= zf[q] / (1.f + ex2f(-zf[q] * LOG2E));
     }
-    lc = l; pc = p;
 #pragma unroll
-    for (int k = 0; k < CH; ++k) {
-      float dy = __bfloat162float(gv[k]);
-      if (zp) {
-        const float z1 = __bfloat162float(zv[k]);
-        const float sg = 1.f / (1.f + ex2f(-z1 * LOG2E));
-        if (write_dz && lc < t_rows)
-          a.dz[(((size_t)b * a.L + trow(a, t_row0 + lc)) * a.H + h) * a.P + pc] =
-              __float2bfloat16_rn(dy * __bfloat162float(yv[k]) * sg * (1.f + z1 * (1.f - sg)));
-        dy *= z1 * sg;
-      }
-      dyv[k] = lc < t_rows ? __bfloat162float(__float2bfloat16_rn(dy)) : 0.f;     // as the MMAs see it
-      io_next(lc, pc);
-    }
+    for (int q = 0; q < 4; ++q) dy[q] = __bfloat162float(__float2bfloat16_rn(dy[q]));
   };
-  // dx = accumulator tile + D dy for the rows of a finished block; coalesced over p
+  // dx = accumulator tile + D dy for the rows of a finished block
   auto store_dx = [&](int t_row0, int t_rows) {
-    int l = io_l0, p = io_p0;
-#pragma unroll 1
-    for (int c = 0; c < XR / CH; ++c) {
-      float dyv[CH];
-      bf16 xv[CH];
-      if (a.has_D) load_dy(t_row0, t_rows, l, p, false, dyv, xv);
+    uint2 gv[XG], zv[XG];
+    int l = io_l0, gq = io_g0;
+    if (a.has_D) {
 #pragma unroll
-      for (int k = 0; k < CH; ++k) {
-        if (l < t_rows) {
-          float v = *(const float*)(smem + SM::kDxT + (l * PP + p) * 4);
-          if (a.has_D) v = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + p) : dscalar, dyv[k], v);
-          a.dx[(((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + p] = __float2bfloat16_rn(v);
-        }
-        io_next(l, p);
+      for (int k = 0; k < XG; ++k) {
+        const int64_t mr = trow(a, t_row0 + min(l, t_rows - 1));
+        gv[k] = *(const uint2*)(gp + mr * a.g_sl + gq * 4);
+        zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gq * 4) : make_uint2(0, 0);
+        io_next(l, gq);
       }
+    }
+    l = io_l0; gq = io_g0;
+#pragma unroll
+    for (int k = 0; k < XG; ++k) {
+      if (l < t_rows) {
+        const uint2 tv = *(const uint2*)(smem + SM::kDxT + (l * SM::DXS + gq * 4) * 2);
+        float v[4] = {bf_lo(tv.x), bf_hi(tv.x), bf_lo(tv.y), bf_hi(tv.y)};
+        if (a.has_D) {
+          float dy[4];
+          gate_dy(gv[k], zv[k], dy);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, dy[q], v[q]);
+        }
+        *(uint2*)(a.dx + (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4) =
+            make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+      }
+      io_next(l, gq);
     }
   };
 
@@ -247,27 +244,55 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
     uint32_t cmask = 0;                                  // bit j: dt of row 32 half + j was clamped (no gradient)
 
     if (is_io) {
-      // ---- dx rows of the previous block (its accumulator tile is complete once every column warp has
-      //      arrived on the named barrier), then the x / dy tiles, dz and dD partials of this block ---------
-      if (it > 0) {
-        named_barrier(9, NTH + NIO);
-        store_dx(prev_row0, prev_rows);
-      }
-      int l = io_l0, p = io_p0;
-#pragma unroll 1
-      for (int c = 0; c < XR / CH; ++c) {
-        float dyv[CH];
-        bf16 xv[CH];
-        load_dy(row0, rows, l, p, true, dyv, xv);
+      // ---- x / dy tiles, dz and dD partials of this block; the tiles are free once the MMAs of the
+      //      previous block have completed.  dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
+      //      (issm_chunk_scan.py:351-360) ------------------------------------------------------------------------
+      if (it > 0 && !mbar_wait(bar2, parity ^ 1)) failed = true;
 #pragma unroll
-        for (int k = 0; k < CH; ++k) {
+      for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 4 loads per group in flight
+        uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2], yv[XG / 2];
+        int l = io_l0, gq = io_g0;
+        for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
+        int lc = l, gc = gq;
+#pragma unroll
+        for (int k = 0; k < XG / 2; ++k) {
+          const int64_t mr = trow(a, row0 + min(lc, rows - 1));
+          xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
+          gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
+          zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
+          yv[k] = zp ? *(const uint2*)(yp + mr * a.o_sl + gc * 4) : make_uint2(0, 0);
+          io_next(lc, gc);
+        }
+#pragma unroll
+        for (int k = 0; k < XG / 2; ++k) {
           if (l < QB) {
-            const bf16 xb = l < rows ? xv[k] : __float2bfloat16_rn(0.f);
-            dDacc = fmaf(dyv[k], __bfloat162float(xb), dDacc);
-            *(bf16*)(smem + SM::kX + sw128_off(l, p)) = xb;
-            *(bf16*)(smem + SM::kDy + sw128_off(l, p)) = __float2bfloat16_rn(dyv[k]);
+            const bool valid = l < rows;
+            float dy[4];
+            gate_dy(gv[k], zv[k], dy);
+            if (zp && valid) {
+              const float go[4] = {bf_lo(gv[k].x), bf_hi(gv[k].x), bf_lo(gv[k].y), bf_hi(gv[k].y)};
+              const float zf[4] = {bf_lo(zv[k].x), bf_hi(zv[k].x), bf_lo(zv[k].y), bf_hi(zv[k].y)};
+              const float yf[4] = {bf_lo(yv[k].x), bf_hi(yv[k].x), bf_lo(yv[k].y), bf_hi(yv[k].y)};
+              float dzv[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float sg = 1.f / (1.f + ex2f(-zf[q] * LOG2E));
+                dzv[q] = go[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
+              }
+              *(uint2*)(a.dz + (((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.P + gq * 4) =
+                  make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
+            }
+            const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
+            const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (!valid) dy[q] = 0.f;
+              dDacc = fmaf(dy[q], xf[q], dDacc);
+            }
+            *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = xs;
+            *(uint2*)(smem + SM::kDy + sw128_off(l, gq * 4)) = make_uint2(pack_bf16(dy[0], dy[1]), pack_bf16(dy[2], dy[3]));
           }
-          io_next(l, p);
+          io_next(l, gq);
         }
       }
       fence_async_smem();
@@ -391,6 +416,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       if (blk > 0) prefetch_dt(blk - 1);                   // every column thread is past phase A ...
       prefetch_S(blk);                                     // ... and has read the previous content of the S tile
     }
+    // ---- dx rows of the previous block: its tile was completed before this barrier and is rewritten only
+    //      after the next one --------------------------------------------------------------------------------------
+    if (is_io && it > 0) store_dx(prev_row0, prev_rows);
 
     if (is_col) {
       if (!mbar_wait(bar1, parity)) failed = true;
@@ -533,16 +561,17 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
             tmem_ld16(t_dx + lane_base + c16 * 16, dv);
             tmem_ld_wait();
             if (lane < 16) {
-              float4* dst = (float4*)(smem + SM::kDxT + (l * PP + c16 * 16) * 4);
 #pragma unroll
-              for (int c = 0; c < 4; ++c) dst[c] = make_float4(dv[c * 4], dv[c * 4 + 1], dv[c * 4 + 2], dv[c * 4 + 3]);
+              for (int c = 0; c < 4; ++c)
+                if (c16 * 16 + c * 4 < SM::DXS)
+                  *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
+                      make_uint2(pack_bf16(dv[c * 4], dv[c * 4 + 1]), pack_bf16(dv[c * 4 + 2], dv[c * 4 + 3]));
             }
           }
         }
       } else {
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
       }
-      asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");          // dx tile complete
     }
     prev_rows = rows;
     prev_row0 = row0;
@@ -550,10 +579,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   }
 
   // the I/O warps store the dx rows of the last processed block
-  if (is_io && !failed && nblk > 0) {
-    named_barrier(9, NTH + NIO);
-    store_dx(prev_row0, prev_rows);
-  }
+  __syncthreads();
+  if (is_io && !failed && nblk > 0) store_dx(prev_row0, prev_rows);
   __syncthreads();
   if (!failed) {
     if (is_col) {
