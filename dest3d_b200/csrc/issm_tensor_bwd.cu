@@ -239,9 +239,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
     const int row0 = blk * QB;
     const int rows = min(QB, a.L - row0);
     const uint32_t parity = it & 1;
-    float dtv[32];
     float a0 = 0.f, alast = 0.f, cst = 0.f;
-    uint32_t cmask = 0;                                  // bit j: dt of row 32 half + j was clamped (no gradient)
 
     if (is_io) {
       // ---- x / dy tiles, dz and dD partials of this block; the tiles are free once the MMAs of the
@@ -323,7 +321,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       }
       if (kStageDt && !mbar_wait(barS, parity)) failed = true;
 
-      // ---- phase A: dt of this thread's 32 rows, clamp mask, summed log2-decay --------------------------
+      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
+      //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
+      float dtv[32];
       float asum = 0.f;
       {
         const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
@@ -335,7 +335,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
                                      : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
           bool clamped = false;
           const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
-          if (clamped && l < rows) cmask |= 1u << j;
           dtv[j] = v;
           asum = fmaf(v, A2, asum);
         }
@@ -413,12 +412,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         mma_commit(bar1);
       }
       __syncwarp();
-      if (blk > 0) prefetch_dt(blk - 1);                   // every column thread is past phase A ...
-      prefetch_S(blk);                                     // ... and has read the previous content of the S tile
+      prefetch_S(blk);                                     // every column thread has read the previous content of the S tile
     }
-    // ---- dx rows of the previous block: its tile was completed before this barrier and is rewritten only
-    //      after the next one --------------------------------------------------------------------------------------
-    if (is_io && it > 0) store_dx(prev_row0, prev_rows);
 
     if (is_col) {
       if (!mbar_wait(bar1, parity)) failed = true;
@@ -450,6 +445,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
+
+    // ---- dx rows of the previous block (I/O warps), overlapping the second MMA phase and the (row, state)
+    //      epilogue; the column warps wait on named barrier 9 before they rewrite the dx tile ---------------------
+    if (is_io) {
+      if (it > 0) store_dx(prev_row0, prev_rows);
+      asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
+    }
 
     // ---- MMA phase 2 (service warp) -----------------------------------------------------------------------
     if (is_svc) {
@@ -488,6 +490,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         named_barrier(10, NTH + 32);                       // finished its (row, state) epilogue (the MMAs that
         prefetch_B(blk - 1);                               // read the g' tile are complete by then, too)
         prefetch_C(blk - 1);
+        prefetch_dt(blk - 1);
       }
     }
 
@@ -497,8 +500,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       if (!failed) {
         // ---- (a) the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse cumsum of dacs ------
         const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
         const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
         const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
+        const bool flipT = a.dt_tma && a.rev;
         float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -527,10 +532,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int jj = ch * 8 + j;
-            const int l = half * 32 + jj;
+            const int l = half * 32 + ch * 8 + j;
             const bool valid = l < rows;
-            const float dtl = dtv[jj];
+            const int st = flipT ? max(rows - 1 - l, 0) : l;
+            const float raw = kStageDt ? __bfloat162float(sdt[st * NT])
+                                       : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
+            bool clamped = false;
+            const float dtl = valid ? dt_transform(a, raw, bias, clamped) : 0.f;
             ac = fmaf(dtl, A2, ac);
             const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
             const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
@@ -540,7 +548,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
             prefix += dacs;
             const int sl = flipB ? max(rows - 1 - l, 0) : l;
             float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * NT]) * bd);
-            if ((cmask >> jj) & 1u) gd = 0.f;
+            if (clamped) gd = 0.f;
             else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
             dAacc = fmaf(ddA, dtl, dAacc);
             if (valid) {
@@ -554,6 +562,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         }
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
         // ---- (b) dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) -----------------
+        named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
         {
           const int l = (warp & 3) * 16 + lane;
           for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
@@ -571,6 +580,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         }
       } else {
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
+        named_barrier(9, NTH + NIO);
       }
     }
     prev_rows = rows;
