@@ -51,7 +51,9 @@ __device__ __forceinline__ float softplus_fast(float v) {
   return v <= 20.f ? lg2f(1.f + ex2f(v * LOG2E)) * LN2 : v;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));   // one instruction: {hi, lo} -> packed pair
+  return r;
 }
 
 

@@ -54,7 +54,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;
   constexpr int NIO = 96;
-  constexpr int XR = (QB * PP + NIO - 1) / NIO;         // 32 tile elements per I/O thread
   constexpr int HP = PP / 2;
   constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
@@ -321,24 +320,35 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       }
       if (kStageDt && !mbar_wait(barS, parity)) failed = true;
 
+      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
+      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
+      const bool flipT = a.dt_tma && a.rev;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+      const int dstep = flipT ? -NT : NT;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+      const int bstep = flipB ? -NT : NT;
+
       // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
       //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
       float dtv[32];
       float asum = 0.f;
-      {
-        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
+      auto phaseA = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const int sl = (a.dt_tma && a.rev) ? max(rows - 1 - l, 0) : l;
-          const float raw = kStageDt ? __bfloat162float(sdt[sl * NT])
-                                     : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
+          float raw;
+          if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
+          else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
           bool clamped = false;
-          const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
+          float v = dt_transform(a, raw, bias, clamped);
+          if (!kFull && l >= rows) v = 0.f;
           dtv[j] = v;
           asum = fmaf(v, A2, asum);
         }
-      }
+      };
+      if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
       sXch[half * NT + n] = asum;
       sXch[(2 + half) * NT + n] = cpart;
       named_barrier(1 + (warp & (NT / 32 - 1)), 64);
@@ -348,28 +358,28 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       if (fabsf(alast) > 120.f) unsafe = 1;
 
       if (!mbar_wait(barT, parity)) failed = true;
-
       if (!mbar_wait(barV, parity)) failed = true;
       // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
-      {
-        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
-        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-        const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
+      auto phaseB = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
         float acc = half ? a0 : 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const bool valid = l < rows;
-          const int sl = flipB ? max(rows - 1 - l, 0) : l;
+          const int sl = kFull ? l : min(l, rows - 1);
           acc = fmaf(dtv[j], A2, acc);
-          const float cd = valid ? __bfloat162float(sC[sl * NT]) * ex2f(acc) : 0.f;
-          const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j] * ex2f(-acc) : 0.f;
-          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
+          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
+          if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
+          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
           *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
           *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
         }
-      }
+      };
+      if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
       fence_async_smem();
     }
     fence_before_sync();
@@ -499,11 +509,14 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       fence_after_sync();
       if (!failed) {
         // ---- (a) the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse cumsum of dacs ------
-        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
-        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
-        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128);
         const bool flipT = a.dt_tma && a.rev;
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+        const int dstep = flipT ? -NT : NT;
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+        const int bstep = flipB ? -NT : NT;
+        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
         float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -513,7 +526,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const uint32_t off = (uint32_t)((half * 32 + ch * 8 + j) * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
+            const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
             part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
             part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
           }
@@ -522,44 +535,51 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         named_barrier(1 + (warp & (NT / 32 - 1)), 64);
         const float p0 = sXch[n];
         const float total = p0 + sXch[NT + n];
-        float prefix = half ? p0 : 0.f;
-        float ac = half ? a0 : 0.f;
+        // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
+        const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
+        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        auto epi = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          float prefix = half ? p0 : 0.f;
+          float ac = half ? a0 : 0.f;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float bdv[8], cdv[8];
-          tmem_ld8(t_BD + ch * 8, bdv);
-          tmem_ld8(t_CD + ch * 8, cdv);
-          tmem_ld_wait();
+          for (int ch = 0; ch < 4; ++ch) {
+            float bdv[8], cdv[8];
+            tmem_ld8(t_BD + ch * 8, bdv);
+            tmem_ld8(t_CD + ch * 8, cdv);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int l = half * 32 + ch * 8 + j;
-            const bool valid = l < rows;
-            const int st = flipT ? max(rows - 1 - l, 0) : l;
-            const float raw = kStageDt ? __bfloat162float(sdt[st * NT])
-                                       : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
-            bool clamped = false;
-            const float dtl = valid ? dt_transform(a, raw, bias, clamped) : 0.f;
-            ac = fmaf(dtl, A2, ac);
-            const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
-            const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
-            const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
-                               __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
-            const float ddA = cst + total - prefix;          // sum of dacs over rows >= l, plus <S_next, G>
-            prefix += dacs;
-            const int sl = flipB ? max(rows - 1 - l, 0) : l;
-            float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * NT]) * bd);
-            if (clamped) gd = 0.f;
-            else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
-            dAacc = fmaf(ddA, dtl, dAacc);
-            if (valid) {
-              dbacc += gd;
-              const size_t o = (((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.N + n;
-              stf((TDT*)a.ddt + o, gd);
-              a.dBh[o] = __float2bfloat16_rn(dtl * bd);
-              a.dCh[o] = __float2bfloat16_rn(cd);
+            for (int j = 0; j < 8; ++j) {
+              const int l = half * 32 + ch * 8 + j;
+              const int sl = kFull ? l : min(l, rows - 1);
+              float raw;
+              if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+              else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
+              bool clamped = false;
+              float dtl = dt_transform(a, raw, bias, clamped);
+              if (!kFull && l >= rows) dtl = 0.f;
+              ac = fmaf(dtl, A2, ac);
+              const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
+              const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+              const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
+                                 __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
+              const float ddA = cst + total - prefix;        // sum of dacs over rows >= l, plus <S_next, G>
+              prefix += dacs;
+              float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * bstep]) * bd);
+              if (clamped) gd = 0.f;
+              else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
+              dAacc = fmaf(ddA, dtl, dAacc);
+              if (kFull || l < rows) {
+                dbacc += gd;
+                const int64_t o = o0 + l * ostep;
+                stf((TDT*)a.ddt + o, gd);
+                a.dBh[o] = __float2bfloat16_rn(dtl * bd);
+                a.dCh[o] = __float2bfloat16_rn(cd);
+              }
             }
           }
-        }
+        };
+        if (rows == QB) epi(std::true_type{}); else epi(std::false_type{});
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
         // ---- (b) dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) -----------------
         named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
