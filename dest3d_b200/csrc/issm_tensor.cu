@@ -233,23 +233,35 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     if (is_col) {
       if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
 
+      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
+      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
+      const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+      const int dstep = flipT ? -NT : NT;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+      const int bstep = flipB ? -NT : NT;
+
       // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
       float dtv[32];
       float asum = 0.f;
-      {
-        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n;
+      auto phaseA = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const int sl = (a.dt_tma && a.rev) ? max(rows - 1 - l, 0) : l;   // a TMA tile is staged in memory order
-          const float raw = kStageDt ? __bfloat162float(sdt[sl * NT])
-                                     : ldf(dtp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.dt_sl + n);
+          const int sl = kFull ? l : min(l, rows - 1);
+          float raw;
+          if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+          else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
           bool clamped;
-          const float v = l < rows ? dt_transform(a, raw, bias, clamped) : 0.f;
+          float v = dt_transform(a, raw, bias, clamped);
+          if (!kFull && l >= rows) v = 0.f;
           dtv[j] = v;
           asum = fmaf(v, A2, asum);
         }
-      }
+      };
+      if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
       sAsum[half * NT + n] = asum;
       named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
       const float a0 = sAsum[n];
@@ -257,26 +269,26 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
       if (fabsf(alast) > 120.f) unsafe = 1;
 
       // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
-      {
-        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB;
-        const bf16* sB = (const bf16*)(smem + SM::kSB) + n;
-        const bf16* sC = (const bf16*)(smem + SM::kSC) + n;
-        const bool flip = a.bc_contig && a.rev;            // staged B / C rows are in memory order
+      auto phaseB = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
         float acc = half ? a0 : 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int l = half * 32 + j;
-          const bool valid = l < rows;
-          const int sl = flip ? max(rows - 1 - l, 0) : l;
+          const int sl = kFull ? l : min(l, rows - 1);
           acc = fmaf(dtv[j], A2, acc);
-          const float cd = valid ? __bfloat162float(sC[sl * NT]) * ex2f(acc) : 0.f;
-          const float bd = valid ? __bfloat162float(sB[sl * NT]) * dtv[j] * ex2f(-acc) : 0.f;
-          const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ (j & 7)) << 4) | ((kcol & 7) << 1)));
+          float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
+          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
+          if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
+          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
           *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
           *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
         }
-      }
+      };
+      if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
       fence_async_smem();
     }
     fence_before_sync();
