@@ -256,6 +256,11 @@ def run_mine(args):
         dist.destroy_process_group()
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on the small profiling case c3s
+# (batch 16, L = 4096), from the ncu captures summarised in profiles/; traffic grows in proportion to batch x L
+NCU_C3S_TRAFFIC = {"fwd": 413.6e6 + 250.2e6, "bwd": 700.4e6 + 859.7e6}
+
+
 def kernel_roofline(dev, par, dfinal, w, batch, path):
     """Time the forward call and the backward call of one direction separately (CUDA events on
     the current stream); report the roofline of the slower one's main kernel."""
@@ -281,8 +286,11 @@ def kernel_roofline(dev, par, dfinal, w, batch, path):
     which, t, nbytes = (("forward call (k_fwd_tensor)", tf, fb) if tf >= tb else
                         ("backward call (k_bwd_tensor + head/batch reductions)", tb, bb))
     ach = nbytes / (t * 1e-3) / 1e9
+    traffic = None
+    if (w["H"], w["P"], w["N"]) == (8, 36, 256):
+        traffic = NCU_C3S_TRAFFIC["fwd" if tf >= tb else "bwd"] * (batch * w["L"]) / (16 * 4096)
     return {"bound": "hbm", "kernel": which, "achieved": ach, "peak": hbm, "peak_source": src, "unit": "GB/s",
-            "frac": ach / hbm, "traffic": None, "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": t,
+            "frac": ach / hbm, "traffic": traffic, "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": t,
             "fwd_ms_one_direction": tf, "bwd_ms_one_direction": tb,
             "fwd_frac": fb / (tf * 1e-3) / 1e9 / hbm, "bwd_frac": bb / (tb * 1e-3) / 1e9 / hbm}
 
