@@ -13,7 +13,9 @@
 // chunk state, state passing, C.A.B^T, chunk scan with D skip and silu(z) gate) with a 64-row
 // chunk and the state carried on chip instead of through HBM.  The decay inside the contraction is
 // factored through the block-start reference, so every factor stays in range as long as the span of
-// |a| over a 64-point block is below 120 (log2 units); a violated block sets bit 1 of the status word.
+// |a| over a 64-point block is below 120 (log2 units); a block that violates this for some column is
+// redone in 2, 4, ... 64 row windows with one reference each (exact for any decay: with single-row
+// windows only the decay itself is floored, at 2^-100), and bit 2 of the status word records that it happened.
 // dt (bf16), B and C rows of the next block are prefetched into shared memory by bulk (TMA) copies
 // while the current block computes.
 #include "issm_tensor.cuh"
@@ -39,14 +41,125 @@ struct FwdSmem {
   static constexpr int kTotal = kBars + 64;
 };
 
+// bf16 operand copy (row of the state operand tile) and saved copy of one thread's PP / 2 state values
+__device__ __forceinline__ void publish_state_cols(const TArgs& a, const float* sc, uint8_t* sop_col, int kcol, int half,
+                                                   bf16* savep, int blk_index, bool save) {
+  constexpr int HP = PP / 2;
+  if (!a.no_output) {
+#pragma unroll
+    for (int j = 0; j < HP; ++j) *(bf16*)(sop_col + sw128_off(half * HP + j, kcol)) = __float2bfloat16_rn(sc[j]);
+  }
+  if (savep && save) {
+    bf16* dst = savep + (size_t)blk_index * a.N * PP;
+#pragma unroll
+    for (int c = 0; c < HP / 8; ++c)
+      *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
+                          pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
+  }
+}
+
+template <typename TDT>
+struct WinCtx {
+  uint8_t* smem;
+  uint64_t* barA;
+  const TDT* dtp;
+  bf16* savep;
+  uint8_t* sop_col;
+  float* sAsum;
+  float* final_col;            // this thread's column of final_states when this is the last block and they are wanted
+  int n, half, rows, row0, blk, ws, npass;
+  float A2, bias;
+  uint32_t t_S, phA;
+  bool failed;
+};
+
+// The windowed passes of one block as the column threads run them (the service warp issues the MMAs of
+// every pass between named barriers 11 and 12): rebuild Cd / Bd for the window, wait for the MMAs, rescale the
+// state by the window's decay and republish it.
+template <int NT, typename TDT>
+__device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c) {
+  using SM = FwdSmem<NT>;
+  constexpr bool kStageDt = sizeof(TDT) == 2;
+  constexpr int NTH = 2 * NT, HP = PP / 2;
+  uint8_t* smem = c.smem;
+  const int n = c.n, half = c.half, rows = c.rows, kcol = n & 63;
+  const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
+  const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+  const int dstep = flipT ? -NT : NT;
+  const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+  const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+  const int bstep = flipB ? -NT : NT;
+  uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+  uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
+  const int kc = kcol >> 3;
+  for (int w = 0; w < c.npass; ++w) {
+    const int w0 = w * c.ws;
+    const bool mine = (w0 >> 5) == half;           // ws <= 32: a window lies inside one half
+    float acc = 0.f;
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
+      const int l = half * 32 + j;
+      float cd = 0.f, bd = 0.f;
+      if (mine && l >= w0 && l < w0 + c.ws && l < rows) {
+        float raw;
+        if (kStageDt) raw = __bfloat162float(sdt[l * dstep]);
+        else raw = ldf(c.dtp + (int64_t)trow(a, c.row0 + l) * a.dt_sl + n);
+        bool clamped;
+        const float v = dt_transform(a, raw, c.bias, clamped);
+        acc = fmaf(v, c.A2, acc);
+        const float ac = fminf(fmaxf(acc, -100.f), 100.f);   // only binds for single-row windows
+        cd = __bfloat162float(sC[l * bstep]) * ex2f(ac);
+        bd = __bfloat162float(sB[l * bstep]) * v * ex2f(-ac);
+      }
+      const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+      *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+      *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+    }
+    if (mine) c.sAsum[n] = fminf(fmaxf(acc, -100.f), 100.f);
+    fence_async_smem();
+    fence_before_sync();
+    named_barrier(11, NTH + 32);
+    if (!mbar_wait(c.barA, c.phA)) c.failed = true;
+    c.phA ^= 1;
+    fence_after_sync();
+    {                                              // state after the window = 2^(window decay) * accumulator
+      float sc[HP];
+      tmem_ld16(c.t_S, sc);
+      tmem_ld8(c.t_S + 16, sc + 16);
+      tmem_ld_wait();
+      const float el = ex2f(c.sAsum[n]);
+#pragma unroll
+      for (int j = 0; j < HP; ++j) sc[j] *= el;
+      tmem_st16(c.t_S, sc);
+      tmem_st8(c.t_S + 16, sc + 16);
+      const bool last = w == c.npass - 1;
+      publish_state_cols(a, sc, c.sop_col, kcol, half, c.savep, c.blk + 1, last);
+      if (last && c.final_col) {
+#pragma unroll
+        for (int j = 0; j < HP; ++j)
+          if (half * HP + j < a.P) c.final_col[(size_t)(half * HP + j) * a.N] = sc[j];
+      }
+      tmem_st_wait();
+    }
+    fence_async_smem();
+    fence_before_sync();
+    named_barrier(12, NTH + 32);
+  }
+}
+
 // Thread layout: 2*NT column threads, one service warp, three tile-I/O warps (registers are allocated in
 // groups of four warps, so the service warp brings three more along).  Column thread (n = tid % NT,
 // half = tid / NT) owns rows [32 half, 32 half + 32) of state column n in the operand pass and columns
 // [24 half, 24 half + 24) of TMEM lane n of the running state.  The service warp issues every MMA and
 // every bulk prefetch.  The I/O warps load the x / z rows of the block, build the x operand tile and
 // store the previous block's output rows (D skip and gate applied) with coalesced accesses.
-template <int NT, typename TDT>
-__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, const __grid_constant__ CUtensorMap dtmap) {
+//
+// Two instantiations walk the streams.  kWin = false is the fast one: it only notices a block outside the range
+// of the single-reference factorisation and marks its (batch, head) stream in a.redo.  kWin = true is launched
+// right behind it, returns at once for unmarked streams and redoes the marked ones from the start with the
+// windowed passes described at fwd_windowed_passes (keeping that code out of the fast kernel is worth 15 %).
+template <int NT, typename TDT, bool kWin>
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;                           // column threads
@@ -59,6 +172,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
   uint64_t* barB = barA + 1;
   uint64_t* barS = barA + 2;
   uint32_t* tmem_holder = (uint32_t*)(barA + 3);
+  uint32_t* sFlag = tmem_holder + 1;                     // (block index + 1) * 8 + log2(windows) of a block that needs windowed passes
   float* sAsum = (float*)(smem + SM::kAsum);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -67,6 +181,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
   const bool is_io = tid >= NTH + 32;
   const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
+  if (kWin && !a.redo[b * a.H + h]) return;              // the fast kernel finished this stream
   const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
   const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
@@ -79,7 +194,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
   for (int i = tid; i < (SM::kSdt - SM::kBd) / 16; i += blockDim.x) ((uint4*)(smem + SM::kBd))[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); }
+  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); *sFlag = 0; }
   if (warp == 0) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
@@ -119,19 +234,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
   // saved block-entry states: (b, H, nblk + 1, PP / 8, N, 8) bf16, i.e. per block the interleaved
   // [head-dim chunk][state][8] layout the backward uses directly as an MMA operand
   bf16* savep = a.saved ? a.saved + (((size_t)b * a.H + h) * (nblk + 1)) * a.N * PP + ((size_t)half * (HP / 8) * a.N + n) * 8 : nullptr;
-  // bf16 operand copy and saved copy of this thread's HP state values
-  auto publish_state = [&](const float* sc, int blk_index) {
-    if (!a.no_output) {
-#pragma unroll
-      for (int j = 0; j < HP; ++j) *(bf16*)(sop_col + sw128_off(half * HP + j, kcol)) = __float2bfloat16_rn(sc[j]);
-    }
-    if (savep) {
-      bf16* dst = savep + (size_t)blk_index * a.N * PP;
-#pragma unroll
-      for (int c = 0; c < HP / 8; ++c)
-        *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
-                            pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
-    }
+  auto publish_state = [&](const float* sc, int blk_index, bool save) {
+    publish_state_cols(a, sc, sop_col, kcol, half, savep, blk_index, save);
   };
   if (is_col) {                                          // initial state -> TMEM, operand, saved[0]
     float sc[HP];
@@ -145,7 +249,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     }
     tmem_st16(t_S, sc);
     tmem_st8(t_S + 16, sc + 16);
-    publish_state(sc, 0);
+    publish_state(sc, 0, true);
     tmem_st_wait();
   }
 
@@ -203,8 +307,27 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
   const uint64_t dMNb = desc_sw128_mn(sb, SM::kAtomB);         // Bd as [states x rows] operand: 64-state groups kAtomB apart
   const uint64_t dMNx = desc_sw128_mn(sb, QB * 128);           // x tile as [head-dim x rows] operand
 
+  // every MMA of one pass over a block: [M | Y] = Cd [Bd ; S]^T (one 64 x 112 MMA per K step), S += Bd^T x
+  auto issue_mmas = [&](bool accumulate) {
+    if (!a.no_output) {
+#pragma unroll
+      for (int at = 0; at < NT / 64; ++at)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * SM::kAtomB + kk * 32,
+                       idesc_bf16(64, QB + PP), accumulate || (at | kk) != 0);
+    }
+#pragma unroll
+    for (int sl = 0; sl < NT / 128; ++sl)
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        mma_bf16_off(tmem + 128 + sl * PP, dMNb, SM::kBd + sl * (2 * SM::kAtomB) + kk * 2048, dMNx, SM::kX + kk * 2048,
+                     idesc_bf16(128, PP, 1, 1), 1);
+    mma_commit(barA);
+  };
+
   bool failed = false;
-  uint32_t unsafe = 0;
+  uint32_t windowed = 0, unsafe = 0, phA = 0;
   int prev_rows = 0, prev_row0 = 0;
   for (int blk = 0; blk < nblk; ++blk) {
     const int row0 = blk * QB;
@@ -266,7 +389,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
       named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
       const float a0 = sAsum[n];
       alast = a0 + sAsum[NT + n];
-      if (fabsf(alast) > 120.f) unsafe = 1;
+      // Range of the factorisation: 2^(+-a) must stay finite in bf16.  A column whose decay over the block
+      // (or over its first half) exceeds 2^120 asks for the block to be redone in 2^k row windows, each with
+      // its own reference: the smallest k for which this thread's windows stay within 2^100.
+      if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
+        if (kWin) atomicMax(sFlag, (uint32_t)(blk + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
+        else unsafe = 1;
+      }
 
       // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
       auto phaseB = [&](auto full) {
@@ -294,27 +423,34 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- MMAs: [M | Y] = Cd [Bd ; S]^T (one 64 x 112 MMA per K step), S += Bd^T x (service warp) ------
+    // A block some column flagged is redone in windows of ws = 64 >> kw rows (the operands built above are
+    // dropped): per window the column threads rebuild Cd / Bd relative to the window start with every row outside
+    // the window zero, the MMAs accumulate [M | Y] over the windows (M becomes block diagonal, rows of later
+    // windows see earlier ones through the state) and the state is rescaled by the window's decay.
+    const uint32_t flag = kWin ? *sFlag : 0u;
+    const int kw = (kWin && (flag >> 3) == (uint32_t)(blk + 1)) ? (int)(flag & 7) : 0;
+    const int ws = QB >> kw;
+    const int npass = kw ? (rows + ws - 1) / ws : 1;
+
+    // ---- MMAs (service warp) -----------------------------------------------------------------------------
     if (is_svc) {
-      if (lane == 0) {
-        fence_after_sync();
-        if (!a.no_output) {
-#pragma unroll
-          for (int at = 0; at < NT / 64; ++at)
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * SM::kAtomB + kk * 32,
-                           idesc_bf16(64, QB + PP), (at | kk) != 0);
+      if (!kWin || kw == 0) {
+        if (lane == 0) {
+          fence_after_sync();
+          issue_mmas(false);
         }
-#pragma unroll
-        for (int sl = 0; sl < NT / 128; ++sl)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_bf16_off(tmem + 128 + sl * PP, dMNb, SM::kBd + sl * (2 * SM::kAtomB) + kk * 2048, dMNx, SM::kX + kk * 2048,
-                         idesc_bf16(128, PP, 1, 1), 1);
-        mma_commit(barA);
+        __syncwarp();
+      } else {
+        for (int w = 0; w < npass; ++w) {
+          named_barrier(11, NTH + 32);                   // window operands are in place
+          if (lane == 0) {
+            fence_after_sync();
+            issue_mmas(w != 0);
+          }
+          __syncwarp();
+          named_barrier(12, NTH + 32);                   // state rescaled and republished
+        }
       }
-      __syncwarp();
       if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
     }
     // ---- output rows of the previous block: its accumulator tile was completed before this barrier and is
@@ -322,8 +458,21 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     if (is_io && blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
 
     if (is_col) {
-      if (!mbar_wait(barA, parity)) failed = true;
-      fence_after_sync();
+      if (!kWin || kw == 0) {
+        if (!mbar_wait(barA, phA)) failed = true;
+        phA ^= 1;
+        fence_after_sync();
+      } else {
+        windowed = 1;
+        WinCtx<TDT> c;
+        c.smem = smem; c.barA = barA; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
+        c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n : nullptr;
+        c.n = n; c.half = half; c.rows = rows; c.row0 = row0; c.blk = blk; c.ws = ws; c.npass = npass;
+        c.A2 = A2; c.bias = bias; c.t_S = t_S; c.phA = phA; c.failed = failed;
+        fwd_windowed_passes<NT, TDT>(a, c);
+        phA = c.phA; failed = c.failed;
+        fence_after_sync();
+      }
 
       // ---- epilogue 1a: masked M -> bf16 operand (every warp takes 16-column groups of its 16 rows) ----
       if (!a.no_output && !failed) {
@@ -347,7 +496,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
         }
       }
       // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
-      if (!failed) {
+      if (!failed && kw == 0) {
         float sc[HP];
         tmem_ld16(t_S, sc);
         tmem_ld8(t_S + 16, sc + 16);
@@ -357,7 +506,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
         for (int j = 0; j < HP; ++j) sc[j] *= el;
         tmem_st16(t_S, sc);
         tmem_st8(t_S + 16, sc + 16);
-        publish_state(sc, blk + 1);
+        publish_state(sc, blk + 1, true);
         if (blk == nblk - 1 && a.want_final) {
           float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
 #pragma unroll
@@ -403,11 +552,12 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const TArgs a, c
     fence_before_sync();
   }
 
-  __syncthreads();
+  const int any_unsafe = __syncthreads_or(unsafe);
   if (is_io && !failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
+  if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
-    if (unsafe) atomicOr(a.status, 2);
+    if (windowed && tid == 0) atomicOr(a.status, 4);       // informational: some block ran windowed
   }
   fence_before_sync();
   __syncthreads();
@@ -436,7 +586,8 @@ bool tensor_path_supported(const issm_params& p) {
 }
 
 size_t tensor_workspace_bytes(const issm_params& p, int pass) {
-  return pass == 0 ? 0 : tensor_bwd_workspace_bytes(p);
+  // forward: one mark per (batch, head) stream
+  return pass == 0 ? align_up((size_t)p.batch * p.nheads * sizeof(int), 256) : tensor_bwd_workspace_bytes(p);
 }
 
 TArgs make_targs(const issm_params& p) {
@@ -499,24 +650,28 @@ static int launch_fwd(TArgs a, const issm_params& p, cudaStream_t s) {
   CUtensorMap dtmap;
   a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
   const size_t smem = FwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+  if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
   return ISSM_OK;
 }
 
 int tensor_fwd(const issm_params& p, cudaStream_t s) {
-  const TArgs a = make_targs(p);
+  TArgs a = make_targs(p);
+  a.redo = (int*)p.workspace;
   if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
   return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);
 }
 
 // forward walk that only regenerates the block-entry states (for a backward without saved states)
-int tensor_fwd_states_only(const issm_params& p, bf16* saved, cudaStream_t s) {
+int tensor_fwd_states_only(const issm_params& p, bf16* saved, int* redo, cudaStream_t s) {
   TArgs a = make_targs(p);
   a.saved = saved;
+  a.redo = redo;
   a.no_output = 1;
   a.want_final = 0;
   if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);

@@ -20,6 +20,8 @@ constexpr float LN2 = 0.6931471805599453f;
 struct TArgs {
   int b, L, H, P, N, G, hpg, rev;
   int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
+  bf16* wscr;       // backward, windowed kernel: (batch, nheads, 63, state) bf16 window-entry states of the block in progress
+  int* redo;        // (batch, nheads) marks: stream holds a block outside the fast kernel's range, redo it windowed
   int dt_tma;       // dt is a regular 2-D array of rows: a 64-row tile is ONE tiled TMA load through a tensor map
   int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
   float dtmin, dtmax;
@@ -109,11 +111,39 @@ __device__ __forceinline__ float build_operands(const TArgs& a, int rows, int ro
   return acc;
 }
 
+// ---- blocks outside the range of the single-reference factorisation (rare; kept out of line) -------------------
+// Smallest k in 1..6 such that, with the block cut into 2^k windows of 64 >> k rows, the summed log2-decay
+// of every window of this thread's 32 rows stays within 2^100 (k = 6, single rows, always qualifies: there
+// the decay itself is floored).  sdt: this thread's column of the staged dt tile (unused for float dt).
+template <typename TDT>
+__device__ __noinline__ int window_need(const TArgs& a, const bf16* sdt, int dstep, const TDT* __restrict__ dtp, int row0,
+                                        int rows, int half, int n, float A2, float bias) {
+  int need = 6;
+  for (int k = 5; k >= 1; --k) {
+    const int wsz = QB >> k;
+    float run = 0.f, mx = 0.f;
+    for (int j = 0; j < 32; ++j) {
+      const int l = half * 32 + j;
+      if (l >= rows) break;
+      float raw;
+      if (sizeof(TDT) == 2) raw = __bfloat162float(sdt[l * dstep]);
+      else raw = ldf(dtp + (int64_t)trow(a, row0 + l) * a.dt_sl + n);
+      bool clamped;
+      const float v = dt_transform(a, raw, bias, clamped);
+      if (j % wsz == 0) run = 0.f;
+      run = fmaf(v, A2, run);
+      mx = fmaxf(mx, fabsf(run));
+    }
+    if (mx <= 100.f) need = k;
+  }
+  return need;
+}
+
 TArgs make_targs(const issm_params& p);
 // Tensor map over bf16 dt viewed as (batch*seqlen rows) x (row pitch) with a (dstate x 64 rows) box; false if dt
 // is not laid out as one regular 2-D array (then the kernels fall back to one bulk copy per row).
 bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out);
-int tensor_fwd_states_only(const issm_params& p, bf16* saved, cudaStream_t s);
+int tensor_fwd_states_only(const issm_params& p, bf16* saved, int* redo, cudaStream_t s);
 size_t tensor_bwd_workspace_bytes(const issm_params& p);
 
 }  // namespace issm

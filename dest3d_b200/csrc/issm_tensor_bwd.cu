@@ -41,15 +41,23 @@ struct BwdSmem {
   static constexpr int kDxT = kXch + 4 * NT * 4;        // [64][DXS] bf16: dx accumulator rows on their way to global memory
   static constexpr int DXS = 40;                        // row stride of that tile (headdim <= 40 on this path)
   static constexpr int kBars = kDxT + QB * DXS * 2;
-  static constexpr int kTotal = kBars + 64;
+  static constexpr int kTotal = kBars + 128;             // 8 mbarriers, TMEM holder, window flag
 };
 
 // Thread layout (as in the forward): 2*NT column threads, one service warp, three tile-I/O warps.
 // Column thread (n = tid % NT, half = tid / NT) owns rows [32 half, 32 half + 32) of state column n in
 // the operand pass and in the (row, state) epilogue, and columns [24 half, 24 half + 24) of TMEM lane n
 // of the state gradient G, which lives in TMEM for the whole walk.
-template <int NT, typename TDT>
-__global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, const __grid_constant__ CUtensorMap dtmap) {
+//
+// As in the forward there are two instantiations: kWin = false is the fast kernel, which only marks a stream
+// holding a block outside the range of the single-reference factorisation in a.redo; kWin = true is launched
+// right behind it, returns at once for unmarked streams and redoes marked ones from the start.  In that kernel a
+// flagged block is cut into 2^k row windows (see window_need) that are processed last to first, each as a
+// pass of the ordinary block code restricted to the window's rows, with its own reference, the state entering the
+// window as the S operand and the rescaled G as g'.  The window-entry states come from a short forward walk over
+// the block's windows (S += Bd^T x on the tensor cores, rescale, bf16 copy to a.wscr) run first.
+template <int NT, typename TDT, bool kWin>
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = BwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;
@@ -64,7 +72,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   uint64_t* barT = bar1 + 3;     // B staging
   uint64_t* barU = bar1 + 4;     // S operand (saved block-entry state)
   uint64_t* barV = bar1 + 5;     // C staging
-  uint32_t* tmem_holder = (uint32_t*)(bar1 + 6);
+  uint64_t* barW = bar1 + 6;     // MMAs of the window-entry-state walk (windowed blocks only)
+  uint64_t* barX = bar1 + 7;     // windowed kernel: last MMA of a block (bar2 completes once per window there)
+  uint32_t* tmem_holder = (uint32_t*)(bar1 + 8);
+  uint32_t* sFlag = tmem_holder + 1;                     // (iteration + 1) * 8 + log2(windows) of a block that needs windows
   float* sXch = (float*)(smem + SM::kXch);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -73,6 +84,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   const bool is_io = tid >= NTH + 32;
   const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
+  if (kWin && !a.redo[b * a.H + h]) return;              // the fast kernel finished this stream
   const int n = tid % NT, half = (tid / NT) & 1;
   const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
   const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
@@ -90,7 +102,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   for (int i = tid; i < (SM::kSdt - SM::kGop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kGop))[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
     mbar_init(bar1, 1); mbar_init(bar2, 1); mbar_init(barS, 1); mbar_init(barT, 1); mbar_init(barU, 1); mbar_init(barV, 1);
+    mbar_init(barW, 1); mbar_init(barX, 1);
     mbar_fence_init();
+    *sFlag = 0;
   }
   if (warp == 0) { tmem_alloc(tmem_holder, 512); tmem_relinquish(); }
   fence_before_sync();
@@ -230,7 +244,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
 
   float dAacc = 0.f, dbacc = 0.f;
   bool failed = false;
-  uint32_t unsafe = 0;
+  uint32_t unsafe = 0, windowed = 0;
+  uint32_t c1 = 0, c2 = 0, cw = 0;                       // completions so far of bar1 / bar2 / barW (windowed kernel)
   int prev_rows = 0, prev_row0 = 0;
 
   for (int it = 0; it < nblk; ++it) {
@@ -240,11 +255,271 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
     const uint32_t parity = it & 1;
     float a0 = 0.f, alast = 0.f, cst = 0.f;
 
+    // ---- column threads: operand pass restricted to rows [w0, w1) of the block.  `first` is the ordinary pass over
+    //      the whole block (staged C, range check, waits for the staged tiles); later passes (windowed kernel only)
+    //      rebuild the operands for one window: C comes from global memory because the g' operand has taken the place
+    //      of the staged C rows, and the exponent is kept within +-100 (this only binds for single-row windows).
+    //      Sets a0 (sum of dt*A over the first half's rows), alast (over all rows) and cst (sum of both cpart). -------
+    auto phaseAB = [&](int w0, int w1, bool first, float cpart) {
+      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
+      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
+      const bool flipT = a.dt_tma && a.rev;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+      const int dstep = flipT ? -NT : NT;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+      const int bstep = flipB ? -NT : NT;
+
+      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
+      //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
+      float dtv[32];
+      float asum = 0.f;
+      auto phaseA = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          float raw;
+          if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
+          else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
+          bool clamped = false;
+          float v = dt_transform(a, raw, bias, clamped);
+          if (!kFull && (l < w0 || l >= w1)) v = 0.f;
+          dtv[j] = v;
+          asum = fmaf(v, A2, asum);
+        }
+      };
+      if (first && rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
+      sXch[half * NT + n] = asum;
+      sXch[(2 + half) * NT + n] = cpart;
+      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+      a0 = sXch[n];
+      alast = a0 + sXch[NT + n];
+      cst = sXch[2 * NT + n] + sXch[3 * NT + n];
+      if (first) {
+        // range of the factorisation: 2^(+-a) must stay finite in bf16 (see the forward kernel)
+        if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
+          if (kWin) atomicMax(sFlag, (uint32_t)(it + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
+          else unsafe = 1;
+        }
+        if (!mbar_wait(barT, parity)) failed = true;
+        if (!mbar_wait(barV, parity)) failed = true;
+      }
+      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
+      auto phaseB = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
+        float acc = half ? a0 : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const int sl = kFull ? l : min(l, rows - 1);
+          acc = fmaf(dtv[j], A2, acc);
+          const float e = (kWin && !first) ? fminf(fmaxf(acc, -100.f), 100.f) : acc;
+          float cv;
+          if (kWin && !first) cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + sl) * a.C_sl + n]);
+          else cv = __bfloat162float(sC[sl * bstep]);
+          float cd = cv * ex2f(e);
+          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-e);
+          if (!kFull && (l < w0 || l >= w1)) { cd = 0.f; bd = 0.f; }
+          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+        }
+      };
+      if (first && rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
+      fence_async_smem();
+    };
+
+    // ---- column threads: g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -------
+    auto gprime = [&]() {
+      float gc[HP];
+      tmem_ld16(t_G, gc);
+      tmem_ld8(t_G + 16, gc + 16);
+      tmem_ld_wait();
+      const float eg = ex2f(alast);
+#pragma unroll
+      for (int j = 0; j < HP; ++j) gc[j] *= eg;
+      tmem_st16(t_G, gc);
+      tmem_st8(t_G + 16, gc + 16);
+#pragma unroll
+      for (int c = 0; c < HP / 8; ++c)
+        *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
+            make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
+                       pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
+      tmem_st_wait();
+    };
+
+    // ---- column threads, epilogue 1: causal masks, bf16 operands dMm[l][s] (first half of the warps) and Mm[l][s] ----
+    auto epilogue1 = [&]() {
+      const int l = (warp & 3) * 16 + lane;
+      const uint32_t t0 = (half ? t_M : t_dM) + lane_base;
+      uint8_t* dst = smem + (half ? SM::kMm : SM::kDMm);
+      for (int c16 = (warp >> 2) % (NCG / 2 > 0 ? NCG / 2 : 1); c16 < 4; c16 += (NCG / 2 > 0 ? NCG / 2 : 1)) {
+        float mv[16];
+        tmem_ld16(t0 + c16 * 16, mv);
+        tmem_ld_wait();
+        if (lane < 16) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              const int s = c16 * 16 + c * 8 + j;
+              pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
+            }
+            *(uint4*)(dst + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+      }
+    };
+
+    // ---- column threads, epilogue (a): the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse
+    //      cumsum of dacs, for the rows [w0, w1) of the block ------------------------------------------------------
+    auto epilogue_a = [&](int w0, int w1, bool first) {
+      const bool flipT = a.dt_tma && a.rev;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+      const int dstep = flipT ? -NT : NT;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+      const int bstep = flipB ? -NT : NT;
+      const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+      const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+      const int kc = kcol >> 3;
+      float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        float bdv[8], cdv[8];
+        tmem_ld8(t_BD + ch * 8, bdv);
+        tmem_ld8(t_CD + ch * 8, cdv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+          part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
+          part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
+        }
+      }
+      sXch[half * NT + n] = part;
+      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+      const float p0 = sXch[n];
+      const float total = p0 + sXch[NT + n];
+      // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
+      const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
+      const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+      auto epi = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+        float prefix = half ? p0 : 0.f;
+        float ac = half ? a0 : 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float bdv[8], cdv[8];
+          tmem_ld8(t_BD + ch * 8, bdv);
+          tmem_ld8(t_CD + ch * 8, cdv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int l = half * 32 + ch * 8 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            const bool in = kFull || (l >= w0 && l < w1);
+            float raw;
+            if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+            else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
+            bool clamped = false;
+            float dtl = dt_transform(a, raw, bias, clamped);
+            if (!in) dtl = 0.f;
+            ac = fmaf(dtl, A2, ac);
+            const float e = (kWin && !first) ? fminf(fmaxf(ac, -100.f), 100.f) : ac;
+            const float bd = ex2f(-e) * bdv[j], cd = ex2f(e) * cdv[j];
+            const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+            const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
+                               __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
+            const float ddA = cst + total - prefix;        // sum of dacs over rows >= l, plus <S_next, G>
+            prefix += dacs;
+            float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * bstep]) * bd);
+            if (clamped) gd = 0.f;
+            else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
+            if (in) {
+              dAacc = fmaf(ddA, dtl, dAacc);
+              dbacc += gd;
+              const int64_t o = o0 + l * ostep;
+              stf((TDT*)a.ddt + o, gd);
+              a.dBh[o] = __float2bfloat16_rn(dtl * bd);
+              a.dCh[o] = __float2bfloat16_rn(cd);
+            }
+          }
+        }
+      };
+      if (first && rows == QB) epi(std::true_type{}); else epi(std::false_type{});
+    };
+
+    // ---- column threads, epilogue (b): dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) ----
+    auto epilogue_b = [&](int w0, int w1, bool first) {
+      const int l = (warp & 3) * 16 + lane;
+      for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
+        float dv[16];
+        tmem_ld16(t_dx + lane_base + c16 * 16, dv);
+        tmem_ld_wait();
+        if (lane < 16 && (first || (l >= w0 && l < w1))) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (c16 * 16 + c * 4 < SM::DXS)
+              *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
+                  make_uint2(pack_bf16(dv[c * 4], dv[c * 4 + 1]), pack_bf16(dv[c * 4 + 2], dv[c * 4 + 3]));
+        }
+      }
+    };
+
+    // ---- service warp (one lane): MMA phase 1: dM = dy x^T, M = Cd Bd^T ---------------------------------------
+    auto issue_phase1 = [&]() {
+#pragma unroll
+      for (int kk = 0; kk < PP / 16; ++kk)
+        mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
+#pragma unroll
+      for (int at = 0; at < NT / 64; ++at)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
+                       idesc_bf16(64, 64), (at | kk) != 0);
+      mma_commit(bar1);
+    };
+    // ---- service warp (one lane): MMA phase 2: BD^T, CD^T, G, dx ---------------------------------------------
+    auto issue_phase2 = [&](bool last) {
+#pragma unroll
+      for (int sl = 0; sl < NT / 128; ++sl) {
+        const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
+          const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
+          mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
+          mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
+          mma_bf16_off(dG, dMN, oCd, dMN, SM::kDy + kk * 2048, idesc_bf16(128, PP, 1, 1), 1);
+        }
+#pragma unroll
+        for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
+          mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
+          mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
+        }
+      }
+#pragma unroll
+      for (int at = 0; at < NT / 64; ++at)               // dx: K = states
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
+                       idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
+        mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
+      mma_commit(bar2);
+      if (kWin && last) mma_commit(barX);
+    };
+
     if (is_io) {
       // ---- x / dy tiles, dz and dD partials of this block; the tiles are free once the MMAs of the
       //      previous block have completed.  dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
       //      (issm_chunk_scan.py:351-360) ------------------------------------------------------------------------
-      if (it > 0 && !mbar_wait(bar2, parity ^ 1)) failed = true;
+      if (it > 0 && !mbar_wait(kWin ? barX : bar2, parity ^ 1)) failed = true;
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 4 loads per group in flight
         uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2], yv[XG / 2];
@@ -319,139 +594,36 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
         }
       }
       if (kStageDt && !mbar_wait(barS, parity)) failed = true;
-
-      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
-      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-      const bool flipT = a.dt_tma && a.rev;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
-      const int dstep = flipT ? -NT : NT;
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
-      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
-      const int bstep = flipB ? -NT : NT;
-
-      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
-      //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
-      float dtv[32];
-      float asum = 0.f;
-      auto phaseA = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          float raw;
-          if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
-          else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
-          bool clamped = false;
-          float v = dt_transform(a, raw, bias, clamped);
-          if (!kFull && l >= rows) v = 0.f;
-          dtv[j] = v;
-          asum = fmaf(v, A2, asum);
-        }
-      };
-      if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
-      sXch[half * NT + n] = asum;
-      sXch[(2 + half) * NT + n] = cpart;
-      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
-      a0 = sXch[n];
-      alast = a0 + sXch[NT + n];
-      cst = sXch[2 * NT + n] + sXch[3 * NT + n];
-      if (fabsf(alast) > 120.f) unsafe = 1;
-
-      if (!mbar_wait(barT, parity)) failed = true;
-      if (!mbar_wait(barV, parity)) failed = true;
-      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
-      auto phaseB = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        const int kc = kcol >> 3;
-        float acc = half ? a0 : 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          const int sl = kFull ? l : min(l, rows - 1);
-          acc = fmaf(dtv[j], A2, acc);
-          float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
-          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
-          if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
-          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
-          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-        }
-      };
-      if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
-      fence_async_smem();
+      phaseAB(0, rows, true, cpart);
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    if (is_col) {
-      // ---- g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -----------
-      {
-        float gc[HP];
-        tmem_ld16(t_G, gc);
-        tmem_ld8(t_G + 16, gc + 16);
-        tmem_ld_wait();
-        const float eg = ex2f(alast);
-#pragma unroll
-        for (int j = 0; j < HP; ++j) gc[j] *= eg;
-        tmem_st16(t_G, gc);
-        tmem_st8(t_G + 16, gc + 16);
-#pragma unroll
-        for (int c = 0; c < HP / 8; ++c)
-          *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
-              make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
-                         pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
-        tmem_st_wait();
-      }
+    // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
+    int kw = 0;
+    if (kWin) {
+      const uint32_t flag = *sFlag;
+      if ((flag >> 3) == (uint32_t)(it + 1)) kw = (int)(flag & 7);
     }
+    const int ws = QB >> kw;
+    const int npass = kw ? (rows + ws - 1) / ws : 1;
 
-    // ---- MMA phase 1: dM = dy x^T, M = Cd Bd^T (service warp) --------------------------------------------
-    if (is_svc) {
-      if (lane == 0) {
-        fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < PP / 16; ++kk)
-          mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
-#pragma unroll
-        for (int at = 0; at < NT / 64; ++at)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
-                         idesc_bf16(64, 64), (at | kk) != 0);
-        mma_commit(bar1);
-      }
-      __syncwarp();
-      prefetch_S(blk);                                     // every column thread has read the previous content of the S tile
-    }
-
-    if (is_col) {
-      if (!mbar_wait(bar1, parity)) failed = true;
-      fence_after_sync();
-      // ---- epilogue 1: causal masks, bf16 operands dMm[l][s] (first half of the warps) and Mm[l][s] --------
-      if (!failed) {
-        const int l = (warp & 3) * 16 + lane;
-        const uint32_t t0 = (half ? t_M : t_dM) + lane_base;
-        uint8_t* dst = smem + (half ? SM::kMm : SM::kDMm);
-        for (int c16 = (warp >> 2) % (NCG / 2 > 0 ? NCG / 2 : 1); c16 < 4; c16 += (NCG / 2 > 0 ? NCG / 2 : 1)) {
-          float mv[16];
-          tmem_ld16(t0 + c16 * 16, mv);
-          tmem_ld_wait();
-          if (lane < 16) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              uint32_t pk[4];
-#pragma unroll
-              for (int j = 0; j < 8; j += 2) {
-                const int s = c16 * 16 + c * 8 + j;
-                pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
-              }
-              *(uint4*)(dst + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-          }
+    if (kw == 0) {
+      if (is_col) gprime();
+      if (is_svc) {
+        if (lane == 0) {
+          fence_after_sync();
+          issue_phase1();
         }
+        __syncwarp();
+        prefetch_S(blk);                                   // every column thread has read the previous content of the S tile
       }
-      fence_async_smem();
+      if (is_col) {
+        if (!mbar_wait(bar1, kWin ? (c1 & 1) : parity)) failed = true;
+        fence_after_sync();
+        if (!failed) epilogue1();
+        fence_async_smem();
+      }
     }
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
@@ -463,153 +635,172 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
       asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
     }
 
-    // ---- MMA phase 2 (service warp) -----------------------------------------------------------------------
-    if (is_svc) {
-      if (lane == 0) {
+    if (kw == 0) {
+      if (is_svc) {
+        if (lane == 0) {
+          fence_after_sync();
+          if (!mbar_wait(barU, parity ^ 1)) { if (a.status) atomicOr(a.status, 1); }   // S tile of this block has landed
+          issue_phase2(true);
+        }
+        __syncwarp();
+        if (blk > 0) {                                     // B staging is free once every column thread has
+          named_barrier(10, NTH + 32);                     // finished its (row, state) epilogue (the MMAs that
+          prefetch_B(blk - 1);                             // read the g' tile are complete by then, too)
+          prefetch_C(blk - 1);
+          prefetch_dt(blk - 1);
+        }
+      }
+      if (is_col) {
+        if (!mbar_wait(bar2, kWin ? (c2 & 1) : parity)) failed = true;
         fence_after_sync();
-        if (!mbar_wait(barU, parity ^ 1)) { if (a.status) atomicOr(a.status, 1); }   // S tile of this block has landed
-#pragma unroll
-        for (int sl = 0; sl < NT / 128; ++sl) {
-          const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
-            const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
-            mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
-            mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
-            mma_bf16_off(dG, dMN, oCd, dMN, SM::kDy + kk * 2048, idesc_bf16(128, PP, 1, 1), 1);
-          }
-#pragma unroll
-          for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
-            mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
-            mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
-          }
+        if (!failed) {
+          epilogue_a(0, rows, true);
+          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
+          named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
+          epilogue_b(0, rows, true);
+        } else {
+          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
+          named_barrier(9, NTH + NIO);
         }
-#pragma unroll
-        for (int at = 0; at < NT / 64; ++at)               // dx: K = states
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
-                         idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
-          mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
-        mma_commit(bar2);
       }
-      __syncwarp();
-      if (blk > 0) {                                       // B staging is free once every column thread has
-        named_barrier(10, NTH + 32);                       // finished its (row, state) epilogue (the MMAs that
-        prefetch_B(blk - 1);                               // read the g' tile are complete by then, too)
-        prefetch_C(blk - 1);
-        prefetch_dt(blk - 1);
-      }
-    }
-
-    if (is_col) {
-      if (!mbar_wait(bar2, parity)) failed = true;
-      fence_after_sync();
-      if (!failed) {
-        // ---- (a) the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse cumsum of dacs ------
-        const bool flipT = a.dt_tma && a.rev;
-        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
-        const int dstep = flipT ? -NT : NT;
-        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
-        const int bstep = flipB ? -NT : NT;
-        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        const int kc = kcol >> 3;
-        float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
+    } else if (kWin) {
+      // ================= windowed block (column threads and service warp; named barriers 11 / 12 / 13) =================
+      const size_t sblk = (size_t)a.N * PP;                // elements of one saved state
+      if (is_svc) {
+        for (int w = 0; w + 1 < npass; ++w) {              // walk producing the window-entry states
+          named_barrier(11, NTH + 32);
+          if (lane == 0) {
+            fence_after_sync();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float bdv[8], cdv[8];
-          tmem_ld8(t_BD + ch * 8, bdv);
-          tmem_ld8(t_CD + ch * 8, cdv);
-          tmem_ld_wait();
+            for (int sl = 0; sl < NT / 128; ++sl)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
-            part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
-            part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
+              for (int kk = 0; kk < 4; ++kk)
+                mma_bf16_off(tmem + 128 + sl * 64, dMN, SM::kBd + sl * (2 * QB * 128) + kk * 2048, dMN, SM::kX + kk * 2048,
+                             idesc_bf16(128, PP, 1, 1), 1);
+            mma_commit(barW);
           }
+          __syncwarp();
+          named_barrier(12, NTH + 32);
         }
-        sXch[half * NT + n] = part;
-        named_barrier(1 + (warp & (NT / 32 - 1)), 64);
-        const float p0 = sXch[n];
-        const float total = p0 + sXch[NT + n];
-        // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
-        const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
-        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
-        auto epi = [&](auto full) {
-          constexpr bool kFull = decltype(full)::value;
-          float prefix = half ? p0 : 0.f;
-          float ac = half ? a0 : 0.f;
+        for (int w = npass - 1; w >= 0; --w) {
+          named_barrier(11, NTH + 32);
+          if (lane == 0) { fence_after_sync(); issue_phase1(); }
+          __syncwarp();
+          named_barrier(12, NTH + 32);
+          if (lane == 0) { fence_after_sync(); issue_phase2(w == 0); }
+          __syncwarp();
+          named_barrier(13, NTH + 32);
+        }
+        prefetch_S(blk);                                   // leaves the S tile as the next iteration expects it
+        if (blk > 0) {
+          named_barrier(10, NTH + 32);
+          prefetch_B(blk - 1);
+          prefetch_C(blk - 1);
+          prefetch_dt(blk - 1);
+        }
+      }
+      if (is_col) {
+        windowed = 1;
+        named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
+        const float cst_block = cst;
+        const size_t mine = ((size_t)half * (HP / 8) * a.N + n) * 8;          // this thread's chunks inside a state
+        const bf16* sv0 = a.saved + (bh * (nblk + 1) + blk) * sblk + mine;    // state entering the block
+        bf16* wsc = a.wscr + bh * 63 * sblk + mine;                           // slot j: state entering window j + 1
+        const uint32_t t_W = tmem + lane_base + 128 + slab * 64 + half * HP;  // accumulator of the walk
+        auto unpack = [&](const bf16* src, float* sc) {
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float bdv[8], cdv[8];
-            tmem_ld8(t_BD + ch * 8, bdv);
-            tmem_ld8(t_CD + ch * 8, cdv);
-            tmem_ld_wait();
+          for (int c = 0; c < HP / 8; ++c) {
+            const uint4 v = *(const uint4*)(src + (size_t)c * a.N * 8);
+            const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int l = half * 32 + ch * 8 + j;
-              const int sl = kFull ? l : min(l, rows - 1);
-              float raw;
-              if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
-              else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
-              bool clamped = false;
-              float dtl = dt_transform(a, raw, bias, clamped);
-              if (!kFull && l >= rows) dtl = 0.f;
-              ac = fmaf(dtl, A2, ac);
-              const float bd = ex2f(-ac) * bdv[j], cd = ex2f(ac) * cdv[j];
-              const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
-              const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
-                                 __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
-              const float ddA = cst + total - prefix;        // sum of dacs over rows >= l, plus <S_next, G>
-              prefix += dacs;
-              float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * bstep]) * bd);
-              if (clamped) gd = 0.f;
-              else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
-              dAacc = fmaf(ddA, dtl, dAacc);
-              if (kFull || l < rows) {
-                dbacc += gd;
-                const int64_t o = o0 + l * ostep;
-                stf((TDT*)a.ddt + o, gd);
-                a.dBh[o] = __float2bfloat16_rn(dtl * bd);
-                a.dCh[o] = __float2bfloat16_rn(cd);
-              }
+            for (int j = 0; j < 4; ++j) {
+              sc[c * 8 + 2 * j] = __uint_as_float(wd[j] << 16);
+              sc[c * 8 + 2 * j + 1] = __uint_as_float(wd[j] & 0xffff0000u);
             }
           }
         };
-        if (rows == QB) epi(std::true_type{}); else epi(std::false_type{});
-        asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
-        // ---- (b) dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) -----------------
-        named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
         {
-          const int l = (warp & 3) * 16 + lane;
-          for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
-            float dv[16];
-            tmem_ld16(t_dx + lane_base + c16 * 16, dv);
+          float sc[HP];
+          unpack(sv0, sc);
+          tmem_st16(t_W, sc);
+          tmem_st8(t_W + 16, sc + 16);
+          tmem_st_wait();
+          for (int w = 0; w + 1 < npass; ++w) {
+            phaseAB(w * ws, min(rows, w * ws + ws), false, 0.f);
+            fence_before_sync();
+            named_barrier(11, NTH + 32);
+            if (!mbar_wait(barW, cw & 1)) failed = true;
+            ++cw;
+            fence_after_sync();
+            tmem_ld16(t_W, sc);
+            tmem_ld8(t_W + 16, sc + 16);
             tmem_ld_wait();
-            if (lane < 16) {
+            const float el = ex2f(fminf(fmaxf(alast, -100.f), 100.f));
 #pragma unroll
-              for (int c = 0; c < 4; ++c)
-                if (c16 * 16 + c * 4 < SM::DXS)
-                  *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
-                      make_uint2(pack_bf16(dv[c * 4], dv[c * 4 + 1]), pack_bf16(dv[c * 4 + 2], dv[c * 4 + 3]));
-            }
+            for (int j = 0; j < HP; ++j) sc[j] *= el;
+            tmem_st16(t_W, sc);
+            tmem_st8(t_W + 16, sc + 16);
+            bf16* dst = wsc + (size_t)w * sblk;
+#pragma unroll
+            for (int c = 0; c < HP / 8; ++c)
+              *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
+                                  pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
+            tmem_st_wait();
+            fence_before_sync();
+            named_barrier(12, NTH + 32);
           }
         }
-      } else {
+        for (int w = npass - 1, k = 0; w >= 0; --w, ++k) {
+          const int w0 = w * ws, w1 = min(rows, w0 + ws);
+          // <state leaving the window, G>: the last window leaves the block (computed above); the others read the walk's copy
+          float cpart = half ? 0.f : cst_block;
+          if (w < npass - 1) {
+            float gc[HP], sn[HP];
+            tmem_ld16(t_G, gc);
+            tmem_ld8(t_G + 16, gc + 16);
+            unpack(wsc + (size_t)w * sblk, sn);
+            tmem_ld_wait();
+            cpart = 0.f;
+#pragma unroll
+            for (int j = 0; j < HP; ++j) cpart = fmaf(sn[j], gc[j], cpart);
+          }
+          {                                                // S operand tile <- state entering the window
+            const bf16* src = w ? wsc + (size_t)(w - 1) * sblk : sv0;
+#pragma unroll
+            for (int c = 0; c < HP / 8; ++c)
+              *(uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16) = *(const uint4*)(src + (size_t)c * a.N * 8);
+          }
+          phaseAB(w0, w1, false, cpart);
+          alast = fminf(fmaxf(alast, -100.f), 100.f);
+          gprime();
+          fence_async_smem();
+          fence_before_sync();
+          named_barrier(11, NTH + 32);
+          if (!mbar_wait(bar1, (c1 + k) & 1)) failed = true;
+          fence_after_sync();
+          epilogue1();
+          fence_async_smem();
+          fence_before_sync();
+          named_barrier(12, NTH + 32);
+          if (!mbar_wait(bar2, (c2 + k) & 1)) failed = true;
+          fence_after_sync();
+          epilogue_a(w0, w1, false);
+          epilogue_b(w0, w1, false);
+          fence_before_sync();
+          named_barrier(13, NTH + 32);
+        }
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
-        named_barrier(9, NTH + NIO);
       }
     }
+    if (kWin) { c1 += npass; c2 += npass; }
     prev_rows = rows;
     prev_row0 = row0;
     fence_before_sync();
   }
 
   // the I/O warps store the dx rows of the last processed block
-  __syncthreads();
+  const int any_unsafe = __syncthreads_or(unsafe);
+  if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
   if (is_io && !failed && nblk > 0) store_dx(prev_row0, prev_rows);
   __syncthreads();
   if (!failed) {
@@ -643,7 +834,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const TArgs a, c
   }
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
-    if (unsafe) atomicOr(a.status, 2);
+    if (windowed && tid == 0) atomicOr(a.status, 4);       // informational: some block ran windowed
   }
   fence_before_sync();
   __syncthreads();
@@ -724,8 +915,9 @@ __global__ void k_reduce_dD(const float* __restrict__ part, int batch, int H, in
 
 // ---------------------------------------------------------------------------------------------
 struct BwdWs {
-  bf16 *dBh, *dCh, *saved;
+  bf16 *dBh, *dCh, *saved, *wscr;
   float *dApart, *dbpart, *dDpart;
+  int *redo_fwd, *redo_bwd;
 };
 
 static BwdWs carve_bwd(const issm_params& p, size_t* total) {
@@ -738,6 +930,9 @@ static BwdWs carve_bwd(const issm_params& p, size_t* total) {
   w.dApart = c.take<float>(b * H * N);
   w.dbpart = c.take<float>(b * H * N);
   w.dDpart = c.take<float>(b * H * PP);
+  w.redo_fwd = c.take<int>(b * H);
+  w.redo_bwd = c.take<int>(b * H);
+  w.wscr = c.take<bf16>(b * H * 63 * N * PP);             // window-entry states of one block per stream (windowed kernel)
   w.saved = p.saved_states ? nullptr : c.take<bf16>(b * H * (nblk + 1) * N * PP);
   *total = c.off;
   return w;
@@ -756,11 +951,13 @@ static int launch_bwd(TArgs a, const issm_params& p, cudaStream_t s) {
   CUtensorMap dtmap;
   a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
   const size_t smem = BwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+  if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return ISSM_ERR_CUDA;
   }
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
   return ISSM_OK;
 }
 
@@ -770,7 +967,7 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   bf16* saved = (bf16*)p.saved_states;
   if (!saved) {                                           // recompute the block-entry states (reference: issm_combined.py:136-144)
     saved = w.saved;
-    int rc = tensor_fwd_states_only(p, saved, s);
+    int rc = tensor_fwd_states_only(p, saved, w.redo_fwd, s);
     if (rc) return rc;
   }
   TArgs a = make_targs(p);
@@ -780,6 +977,7 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   a.dfinal = p.has_dfinal ? p.dfinal_states : nullptr;
   a.dx = (bf16*)p.dx; a.ddt = p.ddt; a.dz = (bf16*)p.dz; a.dinit = (bf16*)p.dinitial_states;
   a.dBh = w.dBh; a.dCh = w.dCh; a.dApart = w.dApart; a.dbpart = w.dbpart; a.dDpart = w.dDpart;
+  a.redo = w.redo_bwd; a.wscr = w.wscr;
   int rc;
   if (p.dstate == 256) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, p, s) : launch_bwd<256, float>(a, p, s);
   else rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<128, bf16>(a, p, s) : launch_bwd<128, float>(a, p, s);

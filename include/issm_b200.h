@@ -96,9 +96,14 @@ typedef struct issm_params {
   void* dinitial_states;        /* optional */
 
   void* workspace; size_t workspace_bytes;
-  int32_t* status;              /* optional device word, written only on a device-side error */
-  /* Optional, tensor path only: (batch, nheads, ceil(seqlen/64) + 1, dstate, 48) bf16.  The forward
-   * stores the state entering every 64-point block (and the final state) here; a backward given
+  /* Optional device word the kernels OR bits into (never cleared by the library):
+   *   bit 0 (1): a bounded device-side wait expired; the affected call's results are invalid.
+   *   bit 2 (4): informational; some 64-point block of a (batch, head) stream exceeded the decay range of the
+   *              tensor-core factorisation and that stream was redone by the windowed kernels (results exact). */
+  int32_t* status;
+  /* Optional, tensor path only: batch * nheads * (ceil(seqlen/64) + 1) * dstate * 48 bf16 elements, laid out
+   * (batch, nheads, block, 6, dstate, 8): head-dim chunk, state, 8 head-dim values (padded to 48).  The
+   * forward stores the state entering every 64-point block (and the final state) here; a backward given
    * the same buffer skips recomputing them (the reference recomputes: issm_combined.py:136-144). */
   void* saved_states;
 } issm_params;

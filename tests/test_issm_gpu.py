@@ -79,33 +79,54 @@ def test_parity_tensor(case):
     ref = parity.oracle_run(inp, Q, opts)
     device_status()
     got = parity.cuda_run(inp, Q, opts, path="tensor")
-    assert device_status() == 0, "tensor path raised a device status bit"
+    assert device_status() == 0, "tensor path raised a device status bit (bounded benchmark-range inputs need no windows)"
     parity.compare(got, ref, torch.bfloat16, want_final=opts.get("return_final", True))
 
 
-def test_tensor_path_flags_out_of_range_blocks(monkeypatch):
-    """dt*|A| summed over a 64-point block beyond the factorisation range sets status bit 1; with
-    ISSM_B200_CHECK_STATUS=1 the call raises instead of returning unchecked values."""
-    from dest3d_b200 import ISSM_chunk_scan_combined
+# dt = softplus(scale * raw + offset) with |A| up to 16: the summed decay of a 64-point block leaves the range
+# of the single-reference factorisation (2^120), so the windowed kernels redo those streams
+WINDOWED_CASES = [
+    ("w_moderate_n128", (1, 192, 1, 36, 128, 1, 64), 1.0, 2.0, dict(dt_softplus=True)),
+    ("w_moderate_n256", (2, 200, 2, 36, 256, 1, 64), 1.0, 2.0, dict(dt_softplus=True)),
+    ("w_reverse_tail", (1, 333, 2, 36, 256, 1, 64), 1.0, 1.5, dict(dt_softplus=True, reverse=True)),
+    # dt up to ~20, dt*|A| up to ~300 per step: every window is a single row.  As for the float32 kernels on the same
+    # regime (unbounded_dt above), rounding is amplified by the large step sizes: 10x the nominal tolerance
+    ("w_single_row_windows", (1, 150, 2, 32, 256, 1, 64), 5.0, 4.0, dict(dt_softplus=True, loosen=10.0)),
+    ("w_float_dt", (1, 160, 2, 36, 256, 1, 64), 1.0, 2.0, dict(dt_softplus=True, f32dt=True)),
+    ("w_no_z_no_init", (1, 130, 2, 36, 128, 1, 64), 1.0, 2.0, dict(dt_softplus=True, use_z=False, use_initial_states=False)),
+]
+
+
+@pytest.mark.parametrize("case", WINDOWED_CASES, ids=[c[0] for c in WINDOWED_CASES])
+def test_parity_tensor_out_of_range_blocks(case):
+    """Unbounded dt (the detector's call has dt_limit = (0, inf)): blocks whose decay exceeds the range of the
+    tensor-core factorisation are redone in row windows, forward and backward, and still match the oracle;
+    status bit 2 (informational) shows that the windowed kernels really ran."""
     from dest3d_b200.issm_combined import device_status
-    inp, Q = _inputs((1, 128, 1, 36, 128, 1, 64), {}, dict(dt_scale=5.0), torch.bfloat16)
-    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    _, shape, scale, offset, opts = case
+    b, L, H, P, N, G, Q = shape
+    inp = O.make_inputs(b, L, H, P, N, G=G, seed=7, dtype=torch.bfloat16)
+    dt = inp["dt"].float() * scale + offset
+    inp["dt"] = dt if opts.get("f32dt") else dt.to(torch.bfloat16)
+    ref = parity.oracle_run(inp, Q, opts)
     device_status()
-    ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, dt_bias=c["dt_bias"], dt_softplus=True, path="tensor")
-    assert device_status() & 2
-    monkeypatch.setenv("ISSM_B200_CHECK_STATUS", "1")
-    with pytest.raises(RuntimeError, match="decay range"):
-        ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, dt_bias=c["dt_bias"], dt_softplus=True, path="tensor")
-    device_status()
+    got = parity.cuda_run(inp, Q, opts, path="tensor")
+    st = device_status()
+    assert st & 4, "the windowed kernels did not run: the case does not leave the fast kernels' range"
+    assert not st & 1
+    parity.compare(got, ref, torch.bfloat16, loosen=opts.get("loosen", 1.0))
 
 
-def test_tensor_backward_without_saved_states():
-    """The C ABI backward recomputes the block-entry states when the caller kept none."""
+@pytest.mark.parametrize("dt_offset", [0.0, 6.0], ids=["in_range", "windowed"])
+def test_tensor_backward_without_saved_states(dt_offset):
+    """The C ABI backward recomputes the block-entry states when the caller kept none (also for streams that
+    need the windowed kernels: dt_offset pushes softplus(dt) to ~2)."""
     from dest3d_b200 import issm_bwd, issm_fwd
     inp, Q = _inputs((1, 200, 2, 36, 256, 1, 64), {}, BENCH_OPTS, torch.bfloat16)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    c["dt"] = (c["dt"].float() + dt_offset).to(torch.bfloat16)
     kw = dict(D=c["D"], z=c["z"], dt_bias=c["dt_bias"], initial_states=c["initial_states"], dt_softplus=True,
-              dt_limit=(1e-3, 1e-1), path="tensor")
+              dt_limit=(1e-3, 1e-1) if dt_offset == 0.0 else (0.0, float("inf")), path="tensor")
     out, out_x, fin, saved = issm_fwd(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, save_states=True, **kw)
     assert saved is not None
     g1 = issm_bwd(c["dout"], c["x"], c["dt"], c["A"], c["B"], c["C"], out_x, Q, dfinal_states=c["dfinal"], saved_states=saved, **kw)
