@@ -267,25 +267,30 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   };
   auto bf_lo = [](uint32_t w) { return __uint_as_float(w << 16); };
   auto bf_hi = [](uint32_t w) { return __uint_as_float(w & 0xffff0000u); };
-  // out = (y + D x) * silu(z) for the output rows of a finished block
-  auto store_tile = [&](int t_row0, int t_rows) {
-    uint2 xv[XG], zv[XG];
-    int l = io_l0, gq = io_g0;
+  // out = (y + D x) * silu(z) for the output rows of a finished block.  The [64][P / 4] groups of the tile are
+  // dealt out one per thread: groups 0..511 to the column threads (which do them while the MMAs of the next
+  // block run and they would otherwise wait), the rest to the I/O threads.  R groups per call, loads first.
+  auto store_groups = [&](auto rtag, int t_row0, int t_rows, int g0, int gstride) {
+    constexpr int R = decltype(rtag)::value;
+    uint2 xv[R], zv[R];
+    int ls[R], gs[R];
 #pragma unroll
-    for (int k = 0; k < XG; ++k) {
-      const int64_t mr = trow(a, t_row0 + min(l, t_rows - 1));
-      xv[k] = *(const uint2*)(xp + mr * a.x_sl + gq * 4);
-      zv[k] = a.has_z ? *(const uint2*)(zp + mr * a.z_sl + gq * 4) : make_uint2(0, 0);
-      io_next(l, gq);
+    for (int r = 0; r < R; ++r) {
+      const int gi = g0 + r * gstride;
+      ls[r] = gi / ngrp;
+      gs[r] = gi - ls[r] * ngrp;
+      const int64_t mr = trow(a, t_row0 + min(ls[r], t_rows - 1));
+      xv[r] = *(const uint2*)(xp + mr * a.x_sl + gs[r] * 4);
+      zv[r] = a.has_z ? *(const uint2*)(zp + mr * a.z_sl + gs[r] * 4) : make_uint2(0, 0);
     }
-    l = io_l0; gq = io_g0;
 #pragma unroll
-    for (int k = 0; k < XG; ++k) {
+    for (int r = 0; r < R; ++r) {
+      const int l = ls[r], gq = gs[r];
       if (l < t_rows) {
         const float4 yv = *(const float4*)(smem + SM::kY + (l * PP + gq * 4) * 4);
         float y[4] = {yv.x, yv.y, yv.z, yv.w};
-        const float xf[4] = {bf_lo(xv[k].x), bf_hi(xv[k].x), bf_lo(xv[k].y), bf_hi(xv[k].y)};
-        const float zf[4] = {bf_lo(zv[k].x), bf_hi(zv[k].x), bf_lo(zv[k].y), bf_hi(zv[k].y)};
+        const float xf[4] = {bf_lo(xv[r].x), bf_hi(xv[r].x), bf_lo(xv[r].y), bf_hi(xv[r].y)};
+        const float zf[4] = {bf_lo(zv[r].x), bf_hi(zv[r].x), bf_lo(zv[r].y), bf_hi(zv[r].y)};
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           y[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, xf[q], y[q]);
@@ -297,8 +302,12 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         }
         *(uint2*)(a.out + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
       }
-      io_next(l, gq);
     }
+  };
+  constexpr int kColGroups = 512;                        // groups of a tile handled by the column threads
+  auto store_tile = [&](int t_row0, int t_rows) {
+    if (is_col) store_groups(std::integral_constant<int, kColGroups / NTH>{}, t_row0, t_rows, tid, NTH);
+    else if (is_io) store_groups(std::integral_constant<int, 2>{}, t_row0, t_rows, kColGroups + io_t, NIO);
   };
 
   // descriptor bases (start address = shared-memory base; per-MMA byte offsets are added at issue)
@@ -455,7 +464,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
     }
     // ---- output rows of the previous block: its accumulator tile was completed before this barrier and is
     //      not rewritten until after the next one -----------------------------------------------------------------
-    if (is_io && blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
+    if (blk > 0 && !a.no_output) store_tile(prev_row0, prev_rows);
 
     if (is_col) {
       if (!kWin || kw == 0) {
@@ -553,7 +562,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   }
 
   const int any_unsafe = __syncthreads_or(unsafe);
-  if (is_io && !failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
+  if (!failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
   if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
