@@ -287,8 +287,8 @@ def kernel_roofline(dev, par, dfinal, w, batch, path):
     kw = dict(D=par["D"], z=dev["z"], dt_bias=par["dt_bias"], initial_states=dev["init"], dt_softplus=True,
               dt_limit=(1e-3, 1e-1), path=path)
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    reps, tf, tb = 3, 0.0, 0.0
-    for i in range(reps + 1):
+    warm, reps, tfs, tbs = 2, 5, [], []
+    for i in range(warm + reps):
         e[0].record()
         out, out_x, fin, saved = issm_fwd(dev["x_f"], dev["dt"], par["A"], dev["B_f"], dev["C_f"], w["Q"],
                                           save_states=True, **kw)
@@ -297,9 +297,11 @@ def kernel_roofline(dev, par, dfinal, w, batch, path):
                  dfinal_states=dfinal, saved_states=saved, **kw)
         e[2].record()
         torch.cuda.synchronize()
-        if i:
-            tf += e[0].elapsed_time(e[1]) / reps
-            tb += e[1].elapsed_time(e[2]) / reps
+        if i >= warm:
+            tfs.append(e[0].elapsed_time(e[1]))
+            tbs.append(e[1].elapsed_time(e[2]))
+    # median of the repetitions: a call that has to grow the caching allocator's pool is not a kernel time
+    tf, tb = sorted(tfs)[reps // 2], sorted(tbs)[reps // 2]
     fb, bb = algorithmic_bytes(batch, w["L"], w["H"], w["P"], w["N"], dirs=1)
     which, t, nbytes = (("forward call (k_fwd_tensor)", tf, fb) if tf >= tb else
                         ("backward call (k_bwd_tensor + head/batch reductions)", tb, bb))
@@ -309,7 +311,7 @@ def kernel_roofline(dev, par, dfinal, w, batch, path):
         traffic = NCU_C3S_TRAFFIC["fwd" if tf >= tb else "bwd"] * (batch * w["L"]) / (16 * 4096)
     return {"bound": "hbm", "kernel": which, "achieved": ach, "peak": hbm, "peak_source": src, "unit": "GB/s",
             "frac": ach / hbm, "traffic": traffic, "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": t,
-            "fwd_ms_one_direction": tf, "bwd_ms_one_direction": tb,
+            "fwd_ms_one_direction": tf, "bwd_ms_one_direction": tb, "fwd_ms_reps": [round(t, 3) for t in tfs], "bwd_ms_reps": [round(t, 3) for t in tbs],
             "fwd_frac": fb / (tf * 1e-3) / 1e9 / hbm, "bwd_frac": bb / (tb * 1e-3) / 1e9 / hbm}
 
 

@@ -61,7 +61,7 @@ __device__ __forceinline__ void publish_state_cols(const TArgs& a, const float* 
 template <typename TDT>
 struct WinCtx {
   uint8_t* smem;
-  uint64_t* barA;
+  uint64_t *barA, *barA2;
   const TDT* dtp;
   bf16* savep;
   uint8_t* sop_col;
@@ -120,6 +120,7 @@ __device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c)
     fence_before_sync();
     named_barrier(11, NTH + 32);
     if (!mbar_wait(c.barA, c.phA)) c.failed = true;
+    if (!mbar_wait(c.barA2, c.phA)) c.failed = true;
     c.phA ^= 1;
     fence_after_sync();
     {                                              // state after the window = 2^(window decay) * accumulator
@@ -171,7 +172,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   uint64_t* barA = (uint64_t*)(smem + SM::kBars);
   uint64_t* barB = barA + 1;
   uint64_t* barS = barA + 2;
-  uint32_t* tmem_holder = (uint32_t*)(barA + 3);
+  uint64_t* barA2 = barA + 3;                            // state-update MMAs (barA: the [M | Y] MMAs issued before them)
+  uint32_t* tmem_holder = (uint32_t*)(barA + 4);
   uint32_t* sFlag = tmem_holder + 1;                     // (block index + 1) * 8 + log2(windows) of a block that needs windowed passes
   float* sAsum = (float*)(smem + SM::kAsum);
 
@@ -194,7 +196,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
   for (int i = tid; i < (SM::kSdt - SM::kBd) / 16; i += blockDim.x) ((uint4*)(smem + SM::kBd))[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_fence_init(); *sFlag = 0; }
+  if (tid == 0) { mbar_init(barA, 1); mbar_init(barB, 1); mbar_init(barS, 1); mbar_init(barA2, 1); mbar_fence_init(); *sFlag = 0; }
   if (warp == 0) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
@@ -326,13 +328,14 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
           mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * SM::kAtomB + kk * 32,
                        idesc_bf16(64, QB + PP), accumulate || (at | kk) != 0);
     }
+    mma_commit(barA);
 #pragma unroll
     for (int sl = 0; sl < NT / 128; ++sl)
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
         mma_bf16_off(tmem + 128 + sl * PP, dMNb, SM::kBd + sl * (2 * SM::kAtomB) + kk * 2048, dMNx, SM::kX + kk * 2048,
                      idesc_bf16(128, PP, 1, 1), 1);
-    mma_commit(barA);
+    mma_commit(barA2);
   };
 
   bool failed = false;
@@ -474,7 +477,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       } else {
         windowed = 1;
         WinCtx<TDT> c;
-        c.smem = smem; c.barA = barA; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
+        c.smem = smem; c.barA = barA; c.barA2 = barA2; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
         c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n : nullptr;
         c.n = n; c.half = half; c.rows = rows; c.row0 = row0; c.blk = blk; c.ws = ws; c.npass = npass;
         c.A2 = A2; c.bias = bias; c.t_S = t_S; c.phA = phA; c.failed = failed;
@@ -505,6 +508,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         }
       }
       // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
+      if (kw == 0) {
+        if (!mbar_wait(barA2, phA ^ 1)) failed = true;     // phA was flipped after the barA wait of this block
+        fence_after_sync();
+      }
       if (!failed && kw == 0) {
         float sc[HP];
         tmem_ld16(t_S, sc);

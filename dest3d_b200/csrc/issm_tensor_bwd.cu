@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   uint64_t* barV = bar1 + 5;     // C staging
   uint64_t* barW = bar1 + 6;     // MMAs of the window-entry-state walk (windowed blocks only)
   uint64_t* barX = bar1 + 7;     // windowed kernel: last MMA of a block (bar2 completes once per window there)
-  uint32_t* tmem_holder = (uint32_t*)(bar1 + 8);
+  uint64_t* bar2b = bar1 + 8;    // second half of MMA phase 2 (G, dx); bar2 covers BD^T / CD^T, which the epilogue needs first
+  uint32_t* tmem_holder = (uint32_t*)(bar1 + 9);
   uint32_t* sFlag = tmem_holder + 1;                     // (iteration + 1) * 8 + log2(windows) of a block that needs windows
   float* sXch = (float*)(smem + SM::kXch);
 
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   for (int i = tid; i < (SM::kSdt - SM::kGop) / 16; i += blockDim.x) ((uint4*)(smem + SM::kGop))[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
     mbar_init(bar1, 1); mbar_init(bar2, 1); mbar_init(barS, 1); mbar_init(barT, 1); mbar_init(barU, 1); mbar_init(barV, 1);
-    mbar_init(barW, 1); mbar_init(barX, 1);
+    mbar_init(barW, 1); mbar_init(barX, 1); mbar_init(bar2b, 1);
     mbar_fence_init();
     *sFlag = 0;
   }
@@ -204,36 +205,57 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
 #pragma unroll
     for (int q = 0; q < 4; ++q) dy[q] = __bfloat162float(__float2bfloat16_rn(dy[q]));
   };
-  // dx = accumulator tile + D dy for the rows of a finished block
-  auto store_dx = [&](int t_row0, int t_rows) {
-    uint2 gv[XG], zv[XG];
-    int l = io_l0, gq = io_g0;
-    if (a.has_D) {
+  // Rows of a finished block: dx = accumulator tile + D dy and dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
+  // (issm_chunk_scan.py:351-360).  The [64][P / 4] groups of the tile are dealt out one per thread: groups 0..511
+  // to the column threads, which do them while the second MMA phase of the next block runs and they would
+  // otherwise wait, the rest to the I/O threads.  R groups per call, loads first.
+  auto finish_groups = [&](auto rtag, int t_row0, int t_rows, int g0, int gstride) {
+    constexpr int R = decltype(rtag)::value;
+    uint2 gv[R], zv[R], yv[R];
+    int ls[R], gs[R];
 #pragma unroll
-      for (int k = 0; k < XG; ++k) {
-        const int64_t mr = trow(a, t_row0 + min(l, t_rows - 1));
-        gv[k] = *(const uint2*)(gp + mr * a.g_sl + gq * 4);
-        zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gq * 4) : make_uint2(0, 0);
-        io_next(l, gq);
-      }
+    for (int r = 0; r < R; ++r) {
+      const int gi = g0 + r * gstride;
+      ls[r] = gi / ngrp;
+      gs[r] = gi - ls[r] * ngrp;
+      const int64_t mr = trow(a, t_row0 + min(ls[r], t_rows - 1));
+      gv[r] = *(const uint2*)(gp + mr * a.g_sl + gs[r] * 4);
+      zv[r] = zp ? *(const uint2*)(zp + mr * a.z_sl + gs[r] * 4) : make_uint2(0, 0);
+      yv[r] = zp ? *(const uint2*)(yp + mr * a.o_sl + gs[r] * 4) : make_uint2(0, 0);
     }
-    l = io_l0; gq = io_g0;
 #pragma unroll
-    for (int k = 0; k < XG; ++k) {
+    for (int r = 0; r < R; ++r) {
+      const int l = ls[r], gq = gs[r];
       if (l < t_rows) {
         const uint2 tv = *(const uint2*)(smem + SM::kDxT + (l * SM::DXS + gq * 4) * 2);
         float v[4] = {bf_lo(tv.x), bf_hi(tv.x), bf_lo(tv.y), bf_hi(tv.y)};
-        if (a.has_D) {
-          float dy[4];
-          gate_dy(gv[k], zv[k], dy);
+        float dy[4] = {bf_lo(gv[r].x), bf_hi(gv[r].x), bf_lo(gv[r].y), bf_hi(gv[r].y)};
+        const size_t o = (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4;
+        if (zp) {
+          const float zf[4] = {bf_lo(zv[r].x), bf_hi(zv[r].x), bf_lo(zv[r].y), bf_hi(zv[r].y)};
+          const float yf[4] = {bf_lo(yv[r].x), bf_hi(yv[r].x), bf_lo(yv[r].y), bf_hi(yv[r].y)};
+          float dzv[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, dy[q], v[q]);
+          for (int q = 0; q < 4; ++q) {
+            const float sg = 1.f / (1.f + ex2f(-zf[q] * LOG2E));
+            dzv[q] = dy[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
+            dy[q] *= zf[q] * sg;
+          }
+          *(uint2*)(a.dz + o) = make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
         }
-        *(uint2*)(a.dx + (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4) =
-            make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+        if (a.has_D) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, __bfloat162float(__float2bfloat16_rn(dy[q])), v[q]);
+        }
+        *(uint2*)(a.dx + o) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
       }
-      io_next(l, gq);
     }
+  };
+  constexpr int kColGroups = 512;                        // groups of a tile handled by the column threads
+  auto finish_rows = [&](int t_row0, int t_rows) {
+    if (is_col) finish_groups(std::integral_constant<int, kColGroups / NTH>{}, t_row0, t_rows, tid, NTH);
+    else if (is_io) finish_groups(std::integral_constant<int, 2>{}, t_row0, t_rows, kColGroups + io_t, NIO);
   };
 
   // descriptor bases
@@ -484,17 +506,16 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
                        idesc_bf16(64, 64), (at | kk) != 0);
       mma_commit(bar1);
     };
-    // ---- service warp (one lane): MMA phase 2: BD^T, CD^T, G, dx ---------------------------------------------
+    // ---- service warp (one lane): MMA phase 2: BD^T, CD^T (what the (row, state) epilogue waits for), then G, dx ----
     auto issue_phase2 = [&](bool last) {
 #pragma unroll
       for (int sl = 0; sl < NT / 128; ++sl) {
-        const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64, dG = tmem + 384 + sl * PP;
+        const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
           const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
           mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
           mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
-          mma_bf16_off(dG, dMN, oCd, dMN, SM::kDy + kk * 2048, idesc_bf16(128, PP, 1, 1), 1);
         }
 #pragma unroll
         for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
@@ -502,6 +523,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
         }
       }
+      mma_commit(bar2);
+#pragma unroll
+      for (int sl = 0; sl < NT / 128; ++sl)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                   // G += Cd^T dy
+          mma_bf16_off(tmem + 384 + sl * PP, dMN, SM::kCd + sl * (2 * QB * 128) + kk * 2048, dMN, SM::kDy + kk * 2048,
+                       idesc_bf16(128, PP, 1, 1), 1);
 #pragma unroll
       for (int at = 0; at < NT / 64; ++at)               // dx: K = states
 #pragma unroll
@@ -511,18 +539,17 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
         mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
-      mma_commit(bar2);
+      mma_commit(bar2b);
       if (kWin && last) mma_commit(barX);
     };
 
     if (is_io) {
-      // ---- x / dy tiles, dz and dD partials of this block; the tiles are free once the MMAs of the
-      //      previous block have completed.  dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
-      //      (issm_chunk_scan.py:351-360) ------------------------------------------------------------------------
-      if (it > 0 && !mbar_wait(kWin ? barX : bar2, parity ^ 1)) failed = true;
+      // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
+      //      previous block have completed -------------------------------------------------------------------------
+      if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 4 loads per group in flight
-        uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2], yv[XG / 2];
+      for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
+        uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
         int l = io_l0, gq = io_g0;
         for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
         int lc = l, gc = gq;
@@ -532,7 +559,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
           gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
           zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
-          yv[k] = zp ? *(const uint2*)(yp + mr * a.o_sl + gc * 4) : make_uint2(0, 0);
           io_next(lc, gc);
         }
 #pragma unroll
@@ -541,19 +567,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
             const bool valid = l < rows;
             float dy[4];
             gate_dy(gv[k], zv[k], dy);
-            if (zp && valid) {
-              const float go[4] = {bf_lo(gv[k].x), bf_hi(gv[k].x), bf_lo(gv[k].y), bf_hi(gv[k].y)};
-              const float zf[4] = {bf_lo(zv[k].x), bf_hi(zv[k].x), bf_lo(zv[k].y), bf_hi(zv[k].y)};
-              const float yf[4] = {bf_lo(yv[k].x), bf_hi(yv[k].x), bf_lo(yv[k].y), bf_hi(yv[k].y)};
-              float dzv[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float sg = 1.f / (1.f + ex2f(-zf[q] * LOG2E));
-                dzv[q] = go[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
-              }
-              *(uint2*)(a.dz + (((size_t)b * a.L + trow(a, row0 + l)) * a.H + h) * a.P + gq * 4) =
-                  make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
-            }
             const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
             const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
 #pragma unroll
@@ -628,12 +641,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
     fence_before_sync();
     if (__syncthreads_or(failed)) { failed = true; break; }
 
-    // ---- dx rows of the previous block (I/O warps), overlapping the second MMA phase and the (row, state)
-    //      epilogue; the column warps wait on named barrier 9 before they rewrite the dx tile ---------------------
-    if (is_io) {
-      if (it > 0) store_dx(prev_row0, prev_rows);
-      asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
-    }
+    // ---- dx / dz rows of the previous block, while the second MMA phase is issued; named barrier 9 keeps the dx
+    //      tile from being rewritten before every thread has read its part -------------------------------------------
+    if (it > 0) finish_rows(prev_row0, prev_rows);
+    if (is_io) asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
 
     if (kw == 0) {
       if (is_svc) {
@@ -644,10 +655,12 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         }
         __syncwarp();
         if (blk > 0) {                                     // B staging is free once every column thread has
-          named_barrier(10, NTH + 32);                     // finished its (row, state) epilogue (the MMAs that
-          prefetch_B(blk - 1);                             // read the g' tile are complete by then, too)
-          prefetch_C(blk - 1);
+          named_barrier(10, NTH + 32);                     // finished its (row, state) epilogue; the C rows take the
+          prefetch_B(blk - 1);                             // place of the g' tile, which the dx MMAs read
           prefetch_dt(blk - 1);
+          if (lane == 0 && !mbar_wait(bar2b, kWin ? (c2 & 1) : parity)) { if (a.status) atomicOr(a.status, 1); }
+          __syncwarp();
+          prefetch_C(blk - 1);
         }
       }
       if (is_col) {
@@ -657,6 +670,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           epilogue_a(0, rows, true);
           asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
           named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
+          if (!mbar_wait(bar2b, kWin ? (c2 & 1) : parity)) failed = true;
+          fence_after_sync();
           epilogue_b(0, rows, true);
         } else {
           asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
@@ -785,6 +800,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           if (!mbar_wait(bar2, (c2 + k) & 1)) failed = true;
           fence_after_sync();
           epilogue_a(w0, w1, false);
+          if (!mbar_wait(bar2b, (c2 + k) & 1)) failed = true;
+          fence_after_sync();
           epilogue_b(w0, w1, false);
           fence_before_sync();
           named_barrier(13, NTH + 32);
@@ -801,7 +818,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   // the I/O warps store the dx rows of the last processed block
   const int any_unsafe = __syncthreads_or(unsafe);
   if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
-  if (is_io && !failed && nblk > 0) store_dx(prev_row0, prev_rows);
+  if (!failed && nblk > 0) finish_rows(prev_row0, prev_rows);
   __syncthreads();
   if (!failed) {
     if (is_col) {
