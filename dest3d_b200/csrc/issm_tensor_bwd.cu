@@ -267,363 +267,132 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   float dAacc = 0.f, dbacc = 0.f;
   bool failed = false;
   uint32_t unsafe = 0, windowed = 0;
-  uint32_t c1 = 0, c2 = 0, cw = 0;                       // completions so far of bar1 / bar2 / barW (windowed kernel)
-  int prev_rows = 0, prev_row0 = 0;
 
-  for (int it = 0; it < nblk; ++it) {
-    const int blk = nblk - 1 - it;
-    const int row0 = blk * QB;
-    const int rows = min(QB, a.L - row0);
-    const uint32_t parity = it & 1;
-    float a0 = 0.f, alast = 0.f, cst = 0.f;
-
-    // ---- column threads: operand pass restricted to rows [w0, w1) of the block.  `first` is the ordinary pass over
-    //      the whole block (staged C, range check, waits for the staged tiles); later passes (windowed kernel only)
-    //      rebuild the operands for one window: C comes from global memory because the g' operand has taken the place
-    //      of the staged C rows, and the exponent is kept within +-100 (this only binds for single-row windows).
-    //      Sets a0 (sum of dt*A over the first half's rows), alast (over all rows) and cst (sum of both cpart). -------
-    auto phaseAB = [&](int w0, int w1, bool first, float cpart) {
-      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
-      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-      const bool flipT = a.dt_tma && a.rev;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
-      const int dstep = flipT ? -NT : NT;
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
-      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
-      const int bstep = flipB ? -NT : NT;
-
-      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
-      //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
-      float dtv[32];
-      float asum = 0.f;
-      auto phaseA = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          float raw;
-          if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
-          else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
-          bool clamped = false;
-          float v = dt_transform(a, raw, bias, clamped);
-          if (!kFull && (l < w0 || l >= w1)) v = 0.f;
-          dtv[j] = v;
-          asum = fmaf(v, A2, asum);
-        }
-      };
-      if (first && rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
-      sXch[half * NT + n] = asum;
-      sXch[(2 + half) * NT + n] = cpart;
-      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
-      a0 = sXch[n];
-      alast = a0 + sXch[NT + n];
-      cst = sXch[2 * NT + n] + sXch[3 * NT + n];
-      if (first) {
-        // range of the factorisation: 2^(+-a) must stay finite in bf16 (see the forward kernel)
-        if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
-          if (kWin) atomicMax(sFlag, (uint32_t)(it + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
-          else unsafe = 1;
-        }
-        if (!mbar_wait(barT, parity)) failed = true;
-        if (!mbar_wait(barV, parity)) failed = true;
-      }
-      // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
-      auto phaseB = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        const int kc = kcol >> 3;
-        float acc = half ? a0 : 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          const int sl = kFull ? l : min(l, rows - 1);
-          acc = fmaf(dtv[j], A2, acc);
-          const float e = (kWin && !first) ? fminf(fmaxf(acc, -100.f), 100.f) : acc;
-          float cv;
-          if (kWin && !first) cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + sl) * a.C_sl + n]);
-          else cv = __bfloat162float(sC[sl * bstep]);
-          float cd = cv * ex2f(e);
-          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-e);
-          if (!kFull && (l < w0 || l >= w1)) { cd = 0.f; bd = 0.f; }
-          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
-          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-        }
-      };
-      if (first && rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
-      fence_async_smem();
-    };
-
-    // ---- column threads: g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -------
-    auto gprime = [&]() {
-      float gc[HP];
-      tmem_ld16(t_G, gc);
-      tmem_ld8(t_G + 16, gc + 16);
-      tmem_ld_wait();
-      const float eg = ex2f(alast);
-#pragma unroll
-      for (int j = 0; j < HP; ++j) gc[j] *= eg;
-      tmem_st16(t_G, gc);
-      tmem_st8(t_G + 16, gc + 16);
-#pragma unroll
-      for (int c = 0; c < HP / 8; ++c)
-        *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
-            make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
-                       pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
-      tmem_st_wait();
-    };
-
-    // ---- column threads, epilogue 1: causal masks, bf16 operands dMm[l][s] (first half of the warps) and Mm[l][s] ----
-    auto epilogue1 = [&]() {
-      const int l = (warp & 3) * 16 + lane;
-      const uint32_t t0 = (half ? t_M : t_dM) + lane_base;
-      uint8_t* dst = smem + (half ? SM::kMm : SM::kDMm);
-      for (int c16 = (warp >> 2) % (NCG / 2 > 0 ? NCG / 2 : 1); c16 < 4; c16 += (NCG / 2 > 0 ? NCG / 2 : 1)) {
-        float mv[16];
-        tmem_ld16(t0 + c16 * 16, mv);
-        tmem_ld_wait();
-        if (lane < 16) {
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              const int s = c16 * 16 + c * 8 + j;
-              pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
+  // The three roles run their own loop over the blocks (so that the registers of one role's state are not held
+  // through the code of the others); they meet at the two block-wide barriers of every iteration.
+  if (is_io) {
+    // ================================================ tile-I/O warps ================================================
+    for (int it = 0; it < nblk; ++it) {
+      const int blk = nblk - 1 - it;
+      const int row0 = blk * QB;
+      const int rows = min(QB, a.L - row0);
+      const uint32_t parity = it & 1;
+        // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
+        //      previous block have completed -------------------------------------------------------------------------
+        if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
+  #pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
+          uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
+          int l = io_l0, gq = io_g0;
+          for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
+          int lc = l, gc = gq;
+  #pragma unroll
+          for (int k = 0; k < XG / 2; ++k) {
+            const int64_t mr = trow(a, row0 + min(lc, rows - 1));
+            xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
+            gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
+            zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
+            io_next(lc, gc);
+          }
+  #pragma unroll
+          for (int k = 0; k < XG / 2; ++k) {
+            if (l < QB) {
+              const bool valid = l < rows;
+              float dy[4];
+              gate_dy(gv[k], zv[k], dy);
+              const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
+              const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
+  #pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (!valid) dy[q] = 0.f;
+                dDacc = fmaf(dy[q], xf[q], dDacc);
+              }
+              *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = xs;
+              *(uint2*)(smem + SM::kDy + sw128_off(l, gq * 4)) = make_uint2(pack_bf16(dy[0], dy[1]), pack_bf16(dy[2], dy[3]));
             }
-            *(uint4*)(dst + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            io_next(l, gq);
           }
         }
-      }
-    };
-
-    // ---- column threads, epilogue (a): the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse
-    //      cumsum of dacs, for the rows [w0, w1) of the block ------------------------------------------------------
-    auto epilogue_a = [&](int w0, int w1, bool first) {
-      const bool flipT = a.dt_tma && a.rev;
-      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
-      const int dstep = flipT ? -NT : NT;
-      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
-      const int bstep = flipB ? -NT : NT;
-      const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-      const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-      const int kc = kcol >> 3;
-      float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        float bdv[8], cdv[8];
-        tmem_ld8(t_BD + ch * 8, bdv);
-        tmem_ld8(t_CD + ch * 8, cdv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
-          part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
-          part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
-        }
-      }
-      sXch[half * NT + n] = part;
-      named_barrier(1 + (warp & (NT / 32 - 1)), 64);
-      const float p0 = sXch[n];
-      const float total = p0 + sXch[NT + n];
-      // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
-      const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
-      const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
-      auto epi = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-        float prefix = half ? p0 : 0.f;
-        float ac = half ? a0 : 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float bdv[8], cdv[8];
-          tmem_ld8(t_BD + ch * 8, bdv);
-          tmem_ld8(t_CD + ch * 8, cdv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int l = half * 32 + ch * 8 + j;
-            const int sl = kFull ? l : min(l, rows - 1);
-            const bool in = kFull || (l >= w0 && l < w1);
-            float raw;
-            if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
-            else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
-            bool clamped = false;
-            float dtl = dt_transform(a, raw, bias, clamped);
-            if (!in) dtl = 0.f;
-            ac = fmaf(dtl, A2, ac);
-            const float e = (kWin && !first) ? fminf(fmaxf(ac, -100.f), 100.f) : ac;
-            const float bd = ex2f(-e) * bdv[j], cd = ex2f(e) * cdv[j];
-            const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
-            const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
-                               __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
-            const float ddA = cst + total - prefix;        // sum of dacs over rows >= l, plus <S_next, G>
-            prefix += dacs;
-            float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * bstep]) * bd);
-            if (clamped) gd = 0.f;
-            else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
-            if (in) {
-              dAacc = fmaf(ddA, dtl, dAacc);
-              dbacc += gd;
-              const int64_t o = o0 + l * ostep;
-              stf((TDT*)a.ddt + o, gd);
-              a.dBh[o] = __float2bfloat16_rn(dtl * bd);
-              a.dCh[o] = __float2bfloat16_rn(cd);
-            }
-          }
-        }
+        fence_async_smem();
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      // dx / dz rows of the previous block beyond the column threads' share; named barrier 9 keeps the dx tile
+      // from being rewritten before every thread has read its part
+      if (it > 0) finish_groups(std::integral_constant<int, 2>{}, row0 + QB, min(QB, a.L - row0 - QB), kColGroups + io_t, NIO);
+      asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
+      fence_before_sync();
+    }
+  } else if (is_svc) {
+    // ================================================= service warp =================================================
+    uint32_t c2 = 0;                                     // completions so far of bar2 / bar2b (windowed kernel)
+    for (int it = 0; it < nblk; ++it) {
+      const int blk = nblk - 1 - it;
+      const int row0 = blk * QB;
+      const int rows = min(QB, a.L - row0);
+      const uint32_t parity = it & 1;
+      // ---- service warp (one lane): MMA phase 1: dM = dy x^T, M = Cd Bd^T ---------------------------------------
+      auto issue_phase1 = [&]() {
+  #pragma unroll
+        for (int kk = 0; kk < PP / 16; ++kk)
+          mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
+  #pragma unroll
+        for (int at = 0; at < NT / 64; ++at)
+  #pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
+                         idesc_bf16(64, 64), (at | kk) != 0);
+        mma_commit(bar1);
       };
-      if (first && rows == QB) epi(std::true_type{}); else epi(std::false_type{});
-    };
-
-    // ---- column threads, epilogue (b): dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) ----
-    auto epilogue_b = [&](int w0, int w1, bool first) {
-      const int l = (warp & 3) * 16 + lane;
-      for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
-        float dv[16];
-        tmem_ld16(t_dx + lane_base + c16 * 16, dv);
-        tmem_ld_wait();
-        if (lane < 16 && (first || (l >= w0 && l < w1))) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (c16 * 16 + c * 4 < SM::DXS)
-              *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
-                  make_uint2(pack_bf16(dv[c * 4], dv[c * 4 + 1]), pack_bf16(dv[c * 4 + 2], dv[c * 4 + 3]));
-        }
-      }
-    };
-
-    // ---- service warp (one lane): MMA phase 1: dM = dy x^T, M = Cd Bd^T ---------------------------------------
-    auto issue_phase1 = [&]() {
-#pragma unroll
-      for (int kk = 0; kk < PP / 16; ++kk)
-        mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
-#pragma unroll
-      for (int at = 0; at < NT / 64; ++at)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
-                       idesc_bf16(64, 64), (at | kk) != 0);
-      mma_commit(bar1);
-    };
-    // ---- service warp (one lane): MMA phase 2: BD^T, CD^T (what the (row, state) epilogue waits for), then G, dx ----
-    auto issue_phase2 = [&](bool last) {
-#pragma unroll
-      for (int sl = 0; sl < NT / 128; ++sl) {
-        const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
-          const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
-          mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
-          mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
-          mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
-          mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
-        }
-      }
-      mma_commit(bar2);
-#pragma unroll
-      for (int sl = 0; sl < NT / 128; ++sl)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)                   // G += Cd^T dy
-          mma_bf16_off(tmem + 384 + sl * PP, dMN, SM::kCd + sl * (2 * QB * 128) + kk * 2048, dMN, SM::kDy + kk * 2048,
-                       idesc_bf16(128, PP, 1, 1), 1);
-#pragma unroll
-      for (int at = 0; at < NT / 64; ++at)               // dx: K = states
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
-                       idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
-        mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
-      mma_commit(bar2b);
-      if (kWin && last) mma_commit(barX);
-    };
-
-    if (is_io) {
-      // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
-      //      previous block have completed -------------------------------------------------------------------------
-      if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
-        uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
-        int l = io_l0, gq = io_g0;
-        for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
-        int lc = l, gc = gq;
-#pragma unroll
-        for (int k = 0; k < XG / 2; ++k) {
-          const int64_t mr = trow(a, row0 + min(lc, rows - 1));
-          xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
-          gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
-          zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
-          io_next(lc, gc);
-        }
-#pragma unroll
-        for (int k = 0; k < XG / 2; ++k) {
-          if (l < QB) {
-            const bool valid = l < rows;
-            float dy[4];
-            gate_dy(gv[k], zv[k], dy);
-            const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
-            const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (!valid) dy[q] = 0.f;
-              dDacc = fmaf(dy[q], xf[q], dDacc);
-            }
-            *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = xs;
-            *(uint2*)(smem + SM::kDy + sw128_off(l, gq * 4)) = make_uint2(pack_bf16(dy[0], dy[1]), pack_bf16(dy[2], dy[3]));
+      // ---- service warp (one lane): MMA phase 2: BD^T, CD^T (what the (row, state) epilogue waits for), then G, dx ----
+      auto issue_phase2 = [&](bool last) {
+  #pragma unroll
+        for (int sl = 0; sl < NT / 128; ++sl) {
+          const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64;
+  #pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
+            const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
+            mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
+            mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
           }
-          io_next(l, gq);
-        }
-      }
-      fence_async_smem();
-    }
-
-    if (is_col) {
-      // ---- <S leaving the block, G> over this thread's state columns: the S operand tile still holds the
-      //      state entering the block processed before this one, i.e. the state leaving this block ------------
-      float cpart = 0.f;
-      {
-        float gc[HP];
-        tmem_ld16(t_G, gc);
-        tmem_ld8(t_G + 16, gc + 16);
-        if (!mbar_wait(barU, parity)) failed = true;
-        uint4 snv[HP / 8];
-#pragma unroll
-        for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < HP / 8; ++c) {
-          const uint32_t w[4] = {snv[c].x, snv[c].y, snv[c].z, snv[c].w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
-            cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
+  #pragma unroll
+          for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
+            mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
+            mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
           }
         }
+        mma_commit(bar2);
+  #pragma unroll
+        for (int sl = 0; sl < NT / 128; ++sl)
+  #pragma unroll
+          for (int kk = 0; kk < 4; ++kk)                   // G += Cd^T dy
+            mma_bf16_off(tmem + 384 + sl * PP, dMN, SM::kCd + sl * (2 * QB * 128) + kk * 2048, dMN, SM::kDy + kk * 2048,
+                         idesc_bf16(128, PP, 1, 1), 1);
+  #pragma unroll
+        for (int at = 0; at < NT / 64; ++at)               // dx: K = states
+  #pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
+                         idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
+  #pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
+          mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
+        mma_commit(bar2b);
+        if (kWin && last) mma_commit(barX);
+      };
+
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
+      int kw = 0;
+      if (kWin) {
+        const uint32_t flag = *sFlag;
+        if ((flag >> 3) == (uint32_t)(it + 1)) kw = (int)(flag & 7);
       }
-      if (kStageDt && !mbar_wait(barS, parity)) failed = true;
-      phaseAB(0, rows, true, cpart);
-    }
-    fence_before_sync();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
-    int kw = 0;
-    if (kWin) {
-      const uint32_t flag = *sFlag;
-      if ((flag >> 3) == (uint32_t)(it + 1)) kw = (int)(flag & 7);
-    }
-    const int ws = QB >> kw;
-    const int npass = kw ? (rows + ws - 1) / ws : 1;
-
-    if (kw == 0) {
-      if (is_col) gprime();
-      if (is_svc) {
+      const int ws = QB >> kw;
+      const int npass = kw ? (rows + ws - 1) / ws : 1;
+      if (kw == 0) {
         if (lane == 0) {
           fence_after_sync();
           issue_phase1();
@@ -631,23 +400,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         __syncwarp();
         prefetch_S(blk);                                   // every column thread has read the previous content of the S tile
       }
-      if (is_col) {
-        if (!mbar_wait(bar1, kWin ? (c1 & 1) : parity)) failed = true;
-        fence_after_sync();
-        if (!failed) epilogue1();
-        fence_async_smem();
-      }
-    }
-    fence_before_sync();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // ---- dx / dz rows of the previous block, while the second MMA phase is issued; named barrier 9 keeps the dx
-    //      tile from being rewritten before every thread has read its part -------------------------------------------
-    if (it > 0) finish_rows(prev_row0, prev_rows);
-    if (is_io) asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
-
-    if (kw == 0) {
-      if (is_svc) {
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      if (kw == 0) {
         if (lane == 0) {
           fence_after_sync();
           if (!mbar_wait(barU, parity ^ 1)) { if (a.status) atomicOr(a.status, 1); }   // S tile of this block has landed
@@ -662,26 +417,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           __syncwarp();
           prefetch_C(blk - 1);
         }
-      }
-      if (is_col) {
-        if (!mbar_wait(bar2, kWin ? (c2 & 1) : parity)) failed = true;
-        fence_after_sync();
-        if (!failed) {
-          epilogue_a(0, rows, true);
-          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
-          named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
-          if (!mbar_wait(bar2b, kWin ? (c2 & 1) : parity)) failed = true;
-          fence_after_sync();
-          epilogue_b(0, rows, true);
-        } else {
-          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
-          named_barrier(9, NTH + NIO);
-        }
-      }
-    } else if (kWin) {
-      // ================= windowed block (column threads and service warp; named barriers 11 / 12 / 13) =================
-      const size_t sblk = (size_t)a.N * PP;                // elements of one saved state
-      if (is_svc) {
+      } else if (kWin) {
+        // windowed block: MMAs of the window-entry-state walk, then of every pass (named barriers 11 / 12 / 13)
         for (int w = 0; w + 1 < npass; ++w) {              // walk producing the window-entry states
           named_barrier(11, NTH + 32);
           if (lane == 0) {
@@ -714,7 +451,297 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           prefetch_dt(blk - 1);
         }
       }
-      if (is_col) {
+      if (kWin) c2 += npass;
+      fence_before_sync();
+    }
+  } else {
+    // ================================================ column threads ================================================
+    uint32_t c1 = 0, c2 = 0, cw = 0;                     // completions so far of bar1 / bar2 / barW (windowed kernel)
+    for (int it = 0; it < nblk; ++it) {
+      const int blk = nblk - 1 - it;
+      const int row0 = blk * QB;
+      const int rows = min(QB, a.L - row0);
+      const uint32_t parity = it & 1;
+      float a0 = 0.f, alast = 0.f, cst = 0.f;
+
+      // ---- column threads: operand pass restricted to rows [w0, w1) of the block.  `first` is the ordinary pass over
+      //      the whole block (staged C, range check, waits for the staged tiles); later passes (windowed kernel only)
+      //      rebuild the operands for one window: C comes from global memory because the g' operand has taken the place
+      //      of the staged C rows, and the exponent is kept within +-100 (this only binds for single-row windows).
+      //      Sets a0 (sum of dt*A over the first half's rows), alast (over all rows) and cst (sum of both cpart). -------
+      auto phaseAB = [&](int w0, int w1, bool first, float cpart) {
+        // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
+        // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
+        const bool flipT = a.dt_tma && a.rev;
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+        const int dstep = flipT ? -NT : NT;
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+        const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+        const int bstep = flipB ? -NT : NT;
+
+        // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
+        //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
+        float dtv[32];
+        float asum = 0.f;
+        auto phaseA = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+  #pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int l = half * 32 + j;
+            float raw;
+            if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
+            else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
+            bool clamped = false;
+            float v = dt_transform(a, raw, bias, clamped);
+            if (!kFull && (l < w0 || l >= w1)) v = 0.f;
+            dtv[j] = v;
+            asum = fmaf(v, A2, asum);
+          }
+        };
+        if (first && rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
+        sXch[half * NT + n] = asum;
+        sXch[(2 + half) * NT + n] = cpart;
+        named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+        a0 = sXch[n];
+        alast = a0 + sXch[NT + n];
+        cst = sXch[2 * NT + n] + sXch[3 * NT + n];
+        if (first) {
+          // range of the factorisation: 2^(+-a) must stay finite in bf16 (see the forward kernel)
+          if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
+            if (kWin) atomicMax(sFlag, (uint32_t)(it + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
+            else unsafe = 1;
+          }
+          if (!mbar_wait(barT, parity)) failed = true;
+          if (!mbar_wait(barV, parity)) failed = true;
+        }
+        // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
+        auto phaseB = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+          uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+          const int kc = kcol >> 3;
+          float acc = half ? a0 : 0.f;
+  #pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int l = half * 32 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            acc = fmaf(dtv[j], A2, acc);
+            const float e = (kWin && !first) ? fminf(fmaxf(acc, -100.f), 100.f) : acc;
+            float cv;
+            if (kWin && !first) cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + sl) * a.C_sl + n]);
+            else cv = __bfloat162float(sC[sl * bstep]);
+            float cd = cv * ex2f(e);
+            float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-e);
+            if (!kFull && (l < w0 || l >= w1)) { cd = 0.f; bd = 0.f; }
+            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+          }
+        };
+        if (first && rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
+        fence_async_smem();
+      };
+
+      // ---- column threads: g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -------
+      auto gprime = [&]() {
+        float gc[HP];
+        tmem_ld16(t_G, gc);
+        tmem_ld8(t_G + 16, gc + 16);
+        tmem_ld_wait();
+        const float eg = ex2f(alast);
+  #pragma unroll
+        for (int j = 0; j < HP; ++j) gc[j] *= eg;
+        tmem_st16(t_G, gc);
+        tmem_st8(t_G + 16, gc + 16);
+  #pragma unroll
+        for (int c = 0; c < HP / 8; ++c)
+          *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
+              make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
+                         pack_bf16(gc[c * 8 + 4], gc[c * 8 + 5]), pack_bf16(gc[c * 8 + 6], gc[c * 8 + 7]));
+        tmem_st_wait();
+      };
+
+      // ---- column threads, epilogue 1: causal masks, bf16 operands dMm[l][s] (first half of the warps) and Mm[l][s] ----
+      auto epilogue1 = [&]() {
+        const int l = (warp & 3) * 16 + lane;
+        const uint32_t t0 = (half ? t_M : t_dM) + lane_base;
+        uint8_t* dst = smem + (half ? SM::kMm : SM::kDMm);
+        for (int c16 = (warp >> 2) % (NCG / 2 > 0 ? NCG / 2 : 1); c16 < 4; c16 += (NCG / 2 > 0 ? NCG / 2 : 1)) {
+          float mv[16];
+          tmem_ld16(t0 + c16 * 16, mv);
+          tmem_ld_wait();
+          if (lane < 16) {
+  #pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              uint32_t pk[4];
+  #pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const int s = c16 * 16 + c * 8 + j;
+                pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
+              }
+              *(uint4*)(dst + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        }
+      };
+
+      // ---- column threads, epilogue (a): the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse
+      //      cumsum of dacs, for the rows [w0, w1) of the block ------------------------------------------------------
+      auto epilogue_a = [&](int w0, int w1, bool first) {
+        const bool flipT = a.dt_tma && a.rev;
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+        const int dstep = flipT ? -NT : NT;
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+        const int bstep = flipB ? -NT : NT;
+        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
+        float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
+  #pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float bdv[8], cdv[8];
+          tmem_ld8(t_BD + ch * 8, bdv);
+          tmem_ld8(t_CD + ch * 8, cdv);
+          tmem_ld_wait();
+  #pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+            part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
+            part = fmaf(-__bfloat162float(*(const bf16*)(bd_col + off)), bdv[j], part);
+          }
+        }
+        sXch[half * NT + n] = part;
+        named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+        const float p0 = sXch[n];
+        const float total = p0 + sXch[NT + n];
+        // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
+        const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
+        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        auto epi = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          float prefix = half ? p0 : 0.f;
+          float ac = half ? a0 : 0.f;
+  #pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float bdv[8], cdv[8];
+            tmem_ld8(t_BD + ch * 8, bdv);
+            tmem_ld8(t_CD + ch * 8, cdv);
+            tmem_ld_wait();
+  #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int l = half * 32 + ch * 8 + j;
+              const int sl = kFull ? l : min(l, rows - 1);
+              const bool in = kFull || (l >= w0 && l < w1);
+              float raw;
+              if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+              else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
+              bool clamped = false;
+              float dtl = dt_transform(a, raw, bias, clamped);
+              if (!in) dtl = 0.f;
+              ac = fmaf(dtl, A2, ac);
+              const float e = (kWin && !first) ? fminf(fmaxf(ac, -100.f), 100.f) : ac;
+              const float bd = ex2f(-e) * bdv[j], cd = ex2f(e) * cdv[j];
+              const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+              const float dacs = __bfloat162float(*(const bf16*)(cd_col + off)) * cdv[j] -
+                                 __bfloat162float(*(const bf16*)(bd_col + off)) * bdv[j];
+              const float ddA = cst + total - prefix;        // sum of dacs over rows >= l, plus <S_next, G>
+              prefix += dacs;
+              float gd = fmaf(ddA, Anat, __bfloat162float(sB[sl * bstep]) * bd);
+              if (clamped) gd = 0.f;
+              else if (a.softplus) gd *= 1.f - ex2f(-dtl * LOG2E);
+              if (in) {
+                dAacc = fmaf(ddA, dtl, dAacc);
+                dbacc += gd;
+                const int64_t o = o0 + l * ostep;
+                stf((TDT*)a.ddt + o, gd);
+                a.dBh[o] = __float2bfloat16_rn(dtl * bd);
+                a.dCh[o] = __float2bfloat16_rn(cd);
+              }
+            }
+          }
+        };
+        if (first && rows == QB) epi(std::true_type{}); else epi(std::false_type{});
+      };
+
+      // ---- column threads, epilogue (b): dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) ----
+      auto epilogue_b = [&](int w0, int w1, bool first) {
+        const int l = (warp & 3) * 16 + lane;
+        for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
+          float dv[16];
+          tmem_ld16(t_dx + lane_base + c16 * 16, dv);
+          tmem_ld_wait();
+          if (lane < 16 && (first || (l >= w0 && l < w1))) {
+  #pragma unroll
+            for (int c = 0; c < 4; ++c)
+              if (c16 * 16 + c * 4 < SM::DXS)
+                *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
+                    make_uint2(pack_bf16(dv[c * 4], dv[c * 4 + 1]), pack_bf16(dv[c * 4 + 2], dv[c * 4 + 3]));
+          }
+        }
+      };
+
+        // ---- <S leaving the block, G> over this thread's state columns: the S operand tile still holds the
+        //      state entering the block processed before this one, i.e. the state leaving this block ------------
+        float cpart = 0.f;
+        {
+          float gc[HP];
+          tmem_ld16(t_G, gc);
+          tmem_ld8(t_G + 16, gc + 16);
+          if (!mbar_wait(barU, parity)) failed = true;
+          uint4 snv[HP / 8];
+  #pragma unroll
+          for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
+          tmem_ld_wait();
+  #pragma unroll
+          for (int c = 0; c < HP / 8; ++c) {
+            const uint32_t w[4] = {snv[c].x, snv[c].y, snv[c].z, snv[c].w};
+  #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
+              cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
+            }
+          }
+        }
+        if (kStageDt && !mbar_wait(barS, parity)) failed = true;
+        phaseAB(0, rows, true, cpart);
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
+      int kw = 0;
+      if (kWin) {
+        const uint32_t flag = *sFlag;
+        if ((flag >> 3) == (uint32_t)(it + 1)) kw = (int)(flag & 7);
+      }
+      const int ws = QB >> kw;
+      const int npass = kw ? (rows + ws - 1) / ws : 1;
+      if (kw == 0) {
+        gprime();
+        if (!mbar_wait(bar1, kWin ? (c1 & 1) : parity)) failed = true;
+        fence_after_sync();
+        if (!failed) epilogue1();
+        fence_async_smem();
+      }
+      fence_before_sync();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      // dx / dz rows of the previous block, while the second MMA phase is issued
+      if (it > 0) finish_groups(std::integral_constant<int, kColGroups / NTH>{}, row0 + QB, min(QB, a.L - row0 - QB), tid, NTH);
+      if (kw == 0) {
+        if (!mbar_wait(bar2, kWin ? (c2 & 1) : parity)) failed = true;
+        fence_after_sync();
+        if (!failed) {
+          epilogue_a(0, rows, true);
+          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
+          named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
+          if (!mbar_wait(bar2b, kWin ? (c2 & 1) : parity)) failed = true;
+          fence_after_sync();
+          epilogue_b(0, rows, true);
+        } else {
+          asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
+          named_barrier(9, NTH + NIO);
+        }
+      } else if (kWin) {
+        // windowed block (named barriers 11 / 12 / 13 with the service warp)
+      const size_t sblk = (size_t)a.N * PP;                // elements of one saved state
         windowed = 1;
         named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
         const float cst_block = cst;
@@ -808,12 +835,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         }
         asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
       }
+      if (kWin) { c1 += npass; c2 += npass; }
+      fence_before_sync();
     }
-    if (kWin) { c1 += npass; c2 += npass; }
-    prev_rows = rows;
-    prev_row0 = row0;
-    fence_before_sync();
   }
+  const int prev_row0 = 0, prev_rows = min(QB, a.L);     // the block processed last
 
   // the I/O warps store the dx rows of the last processed block
   const int any_unsafe = __syncthreads_or(unsafe);
