@@ -351,23 +351,23 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int row0 = blk * QB;
       const int rows = min(QB, a.L - row0);
       const uint32_t parity = blk & 1;
-        // ---- x rows of this block -> x operand tile [l][p] (swizzled rows); the tile is free once the last
-        //      MMA of the previous block has completed ---------------------------------------------------------
-        if (blk > 0 && !a.no_output && !mbar_wait(barB, parity ^ 1)) failed = true;
-        uint2 xv[XG];
-        int l = io_l0, gq = io_g0;
-  #pragma unroll
-        for (int k = 0; k < XG; ++k) {
-          xv[k] = *(const uint2*)(xp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.x_sl + gq * 4);
-          io_next(l, gq);
-        }
-        l = io_l0; gq = io_g0;
-  #pragma unroll
-        for (int k = 0; k < XG; ++k) {
-          if (l < QB) *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = l < rows ? xv[k] : make_uint2(0, 0);
-          io_next(l, gq);
-        }
-        fence_async_smem();
+      // ---- x rows of this block -> x operand tile [l][p] (swizzled rows); the tile is free once the last
+      //      MMA of the previous block has completed ---------------------------------------------------------
+      if (blk > 0 && !a.no_output && !mbar_wait(barB, parity ^ 1)) failed = true;
+      uint2 xv[XG];
+      int l = io_l0, gq = io_g0;
+#pragma unroll
+      for (int k = 0; k < XG; ++k) {
+        xv[k] = *(const uint2*)(xp + (int64_t)trow(a, row0 + min(l, rows - 1)) * a.x_sl + gq * 4);
+        io_next(l, gq);
+      }
+      l = io_l0; gq = io_g0;
+#pragma unroll
+      for (int k = 0; k < XG; ++k) {
+        if (l < QB) *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = l < rows ? xv[k] : make_uint2(0, 0);
+        io_next(l, gq);
+      }
+      fence_async_smem();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);
@@ -391,24 +391,24 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int ws = QB >> kw;
       const int npass = kw ? (rows + ws - 1) / ws : 1;
       // ---- MMAs of the block (of every window of a flagged block) ---------------------------------------------
-        if (!kWin || kw == 0) {
+      if (!kWin || kw == 0) {
+        if (lane == 0) {
+          fence_after_sync();
+          issue_mmas(false);
+        }
+        __syncwarp();
+      } else {
+        for (int w = 0; w < npass; ++w) {
+          named_barrier(11, NTH + 32);                   // window operands are in place
           if (lane == 0) {
             fence_after_sync();
-            issue_mmas(false);
+            issue_mmas(w != 0);
           }
           __syncwarp();
-        } else {
-          for (int w = 0; w < npass; ++w) {
-            named_barrier(11, NTH + 32);                   // window operands are in place
-            if (lane == 0) {
-              fence_after_sync();
-              issue_mmas(w != 0);
-            }
-            __syncwarp();
-            named_barrier(12, NTH + 32);                   // state rescaled and republished
-          }
+          named_barrier(12, NTH + 32);                   // state rescaled and republished
         }
-        if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
+      }
+      if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (a.no_output) continue;
@@ -430,71 +430,71 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int rows = min(QB, a.L - row0);
       const uint32_t parity = blk & 1;
       float alast = 0.f;
-        if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
+      if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
 
-        // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
-        // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-        const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
-        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
-        const int dstep = flipT ? -NT : NT;
-        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
-        const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
-        const int bstep = flipB ? -NT : NT;
+      // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
+      // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
+      const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
+      const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+      const int dstep = flipT ? -NT : NT;
+      const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+      const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
+      const int bstep = flipB ? -NT : NT;
 
-        // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
-        float dtv[32];
-        float asum = 0.f;
-        auto phaseA = [&](auto full) {
-          constexpr bool kFull = decltype(full)::value;
-  #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int l = half * 32 + j;
-            const int sl = kFull ? l : min(l, rows - 1);
-            float raw;
-            if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
-            else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
-            bool clamped;
-            float v = dt_transform(a, raw, bias, clamped);
-            if (!kFull && l >= rows) v = 0.f;
-            dtv[j] = v;
-            asum = fmaf(v, A2, asum);
-          }
-        };
-        if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
-        sAsum[half * NT + n] = asum;
-        named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
-        const float a0 = sAsum[n];
-        alast = a0 + sAsum[NT + n];
-        // Range of the factorisation: 2^(+-a) must stay finite in bf16.  A column whose decay over the block
-        // (or over its first half) exceeds 2^120 asks for the block to be redone in 2^k row windows, each with
-        // its own reference: the smallest k for which this thread's windows stay within 2^100.
-        if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
-          if (kWin) atomicMax(sFlag, (uint32_t)(blk + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
-          else unsafe = 1;
+      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
+      float dtv[32];
+      float asum = 0.f;
+      auto phaseA = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const int sl = kFull ? l : min(l, rows - 1);
+          float raw;
+          if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+          else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
+          bool clamped;
+          float v = dt_transform(a, raw, bias, clamped);
+          if (!kFull && l >= rows) v = 0.f;
+          dtv[j] = v;
+          asum = fmaf(v, A2, asum);
         }
+      };
+      if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
+      sAsum[half * NT + n] = asum;
+      named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
+      const float a0 = sAsum[n];
+      alast = a0 + sAsum[NT + n];
+      // Range of the factorisation: 2^(+-a) must stay finite in bf16.  A column whose decay over the block
+      // (or over its first half) exceeds 2^120 asks for the block to be redone in 2^k row windows, each with
+      // its own reference: the smallest k for which this thread's windows stay within 2^100.
+      if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
+        if (kWin) atomicMax(sFlag, (uint32_t)(blk + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
+        else unsafe = 1;
+      }
 
-        // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
-        auto phaseB = [&](auto full) {
-          constexpr bool kFull = decltype(full)::value;
-          uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-          uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
-          const int kc = kcol >> 3;
-          float acc = half ? a0 : 0.f;
-  #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int l = half * 32 + j;
-            const int sl = kFull ? l : min(l, rows - 1);
-            acc = fmaf(dtv[j], A2, acc);
-            float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
-            float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
-            if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
-            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
-            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-          }
-        };
-        if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
-        fence_async_smem();
+      // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
+      auto phaseB = [&](auto full) {
+        constexpr bool kFull = decltype(full)::value;
+        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
+        float acc = half ? a0 : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int l = half * 32 + j;
+          const int sl = kFull ? l : min(l, rows - 1);
+          acc = fmaf(dtv[j], A2, acc);
+          float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
+          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
+          if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
+          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+        }
+      };
+      if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
+      fence_async_smem();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       const uint32_t flag = kWin ? *sFlag : 0u;
@@ -502,87 +502,87 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int ws = QB >> kw;
       const int npass = kw ? (rows + ws - 1) / ws : 1;
       if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);
-        if (!kWin || kw == 0) {
-          if (!mbar_wait(barA, phA)) failed = true;
-          phA ^= 1;
-          fence_after_sync();
-        } else {
-          windowed = 1;
-          WinCtx<TDT> c;
-          c.smem = smem; c.barA = barA; c.barA2 = barA2; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
-          c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n : nullptr;
-          c.n = n; c.half = half; c.rows = rows; c.row0 = row0; c.blk = blk; c.ws = ws; c.npass = npass;
-          c.A2 = A2; c.bias = bias; c.t_S = t_S; c.phA = phA; c.failed = failed;
-          fwd_windowed_passes<NT, TDT>(a, c);
-          phA = c.phA; failed = c.failed;
-          fence_after_sync();
-        }
+      if (!kWin || kw == 0) {
+        if (!mbar_wait(barA, phA)) failed = true;
+        phA ^= 1;
+        fence_after_sync();
+      } else {
+        windowed = 1;
+        WinCtx<TDT> c;
+        c.smem = smem; c.barA = barA; c.barA2 = barA2; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
+        c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n : nullptr;
+        c.n = n; c.half = half; c.rows = rows; c.row0 = row0; c.blk = blk; c.ws = ws; c.npass = npass;
+        c.A2 = A2; c.bias = bias; c.t_S = t_S; c.phA = phA; c.failed = failed;
+        fwd_windowed_passes<NT, TDT>(a, c);
+        phA = c.phA; failed = c.failed;
+        fence_after_sync();
+      }
 
-        // ---- epilogue 1a: masked M -> bf16 operand (every warp takes 16-column groups of its 16 rows) ----
-        if (!a.no_output && !failed) {
-          const int l = (warp & 3) * 16 + lane;
-          for (int c16 = (warp >> 2) % NCG; c16 < 4; c16 += NCG) {
-            float mv[16];
-            tmem_ld16(t_M + lane_base + c16 * 16, mv);
-            tmem_ld_wait();
-            if (lane < 16) {
-  #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                uint32_t pk[4];
-  #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                  const int s = c16 * 16 + c * 8 + j;
-                  pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
-                }
-                *(uint4*)(smem + SM::kMm + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      // ---- epilogue 1a: masked M -> bf16 operand (every warp takes 16-column groups of its 16 rows) ----
+      if (!a.no_output && !failed) {
+        const int l = (warp & 3) * 16 + lane;
+        for (int c16 = (warp >> 2) % NCG; c16 < 4; c16 += NCG) {
+          float mv[16];
+          tmem_ld16(t_M + lane_base + c16 * 16, mv);
+          tmem_ld_wait();
+          if (lane < 16) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const int s = c16 * 16 + c * 8 + j;
+                pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
               }
+              *(uint4*)(smem + SM::kMm + sw128_chunk(l, c16 * 2 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
           }
         }
-        // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
-        if (kw == 0) {
-          if (!mbar_wait(barA2, phA ^ 1)) failed = true;     // phA was flipped after the barA wait of this block
-          fence_after_sync();
+      }
+      // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
+      if (kw == 0) {
+        if (!mbar_wait(barA2, phA ^ 1)) failed = true;     // phA was flipped after the barA wait of this block
+        fence_after_sync();
+      }
+      if (!failed && kw == 0) {
+        float sc[HP];
+        tmem_ld16(t_S, sc);
+        tmem_ld8(t_S + 16, sc + 16);
+        tmem_ld_wait();
+        const float el = ex2f(alast);
+#pragma unroll
+        for (int j = 0; j < HP; ++j) sc[j] *= el;
+        tmem_st16(t_S, sc);
+        tmem_st8(t_S + 16, sc + 16);
+        publish_state(sc, blk + 1, true);
+        if (blk == nblk - 1 && a.want_final) {
+          float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
+#pragma unroll
+          for (int j = 0; j < HP; ++j)
+            if (half * HP + j < a.P) fp[(size_t)(half * HP + j) * a.N] = sc[j];
         }
-        if (!failed && kw == 0) {
-          float sc[HP];
-          tmem_ld16(t_S, sc);
-          tmem_ld8(t_S + 16, sc + 16);
-          tmem_ld_wait();
-          const float el = ex2f(alast);
-  #pragma unroll
-          for (int j = 0; j < HP; ++j) sc[j] *= el;
-          tmem_st16(t_S, sc);
-          tmem_st8(t_S + 16, sc + 16);
-          publish_state(sc, blk + 1, true);
-          if (blk == nblk - 1 && a.want_final) {
-            float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
-  #pragma unroll
-            for (int j = 0; j < HP; ++j)
-              if (half * HP + j < a.P) fp[(size_t)(half * HP + j) * a.N] = sc[j];
-          }
-          tmem_st_wait();
-        }
-        fence_async_smem();
+        tmem_st_wait();
+      }
+      fence_async_smem();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (a.no_output) continue;
-        if (!mbar_wait(barB, parity)) failed = true;
-        fence_after_sync();
-        // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) ----
-        if (!failed) {
-          const int l = (warp & 3) * 16 + lane;
-          for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
-            float yv[16];
-            tmem_ld16(t_Y + lane_base + c16 * 16, yv);
-            tmem_ld_wait();
-            if (lane < 16) {
-              float4* dst = (float4*)(smem + SM::kY + (l * PP + c16 * 16) * 4);
-  #pragma unroll
-              for (int c = 0; c < 4; ++c) dst[c] = make_float4(yv[c * 4], yv[c * 4 + 1], yv[c * 4 + 2], yv[c * 4 + 3]);
-            }
+      if (!mbar_wait(barB, parity)) failed = true;
+      fence_after_sync();
+      // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) ----
+      if (!failed) {
+        const int l = (warp & 3) * 16 + lane;
+        for (int c16 = (warp >> 2) % NCG; c16 < PP / 16; c16 += NCG) {
+          float yv[16];
+          tmem_ld16(t_Y + lane_base + c16 * 16, yv);
+          tmem_ld_wait();
+          if (lane < 16) {
+            float4* dst = (float4*)(smem + SM::kY + (l * PP + c16 * 16) * 4);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[c] = make_float4(yv[c * 4], yv[c * 4 + 1], yv[c * 4 + 2], yv[c * 4 + 3]);
           }
         }
+      }
       fence_before_sync();
     }
   }

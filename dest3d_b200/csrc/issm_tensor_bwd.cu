@@ -277,43 +277,43 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       const int row0 = blk * QB;
       const int rows = min(QB, a.L - row0);
       const uint32_t parity = it & 1;
-        // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
-        //      previous block have completed -------------------------------------------------------------------------
-        if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
-  #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
-          uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
-          int l = io_l0, gq = io_g0;
-          for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
-          int lc = l, gc = gq;
-  #pragma unroll
-          for (int k = 0; k < XG / 2; ++k) {
-            const int64_t mr = trow(a, row0 + min(lc, rows - 1));
-            xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
-            gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
-            zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
-            io_next(lc, gc);
-          }
-  #pragma unroll
-          for (int k = 0; k < XG / 2; ++k) {
-            if (l < QB) {
-              const bool valid = l < rows;
-              float dy[4];
-              gate_dy(gv[k], zv[k], dy);
-              const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
-              const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
-  #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                if (!valid) dy[q] = 0.f;
-                dDacc = fmaf(dy[q], xf[q], dDacc);
-              }
-              *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = xs;
-              *(uint2*)(smem + SM::kDy + sw128_off(l, gq * 4)) = make_uint2(pack_bf16(dy[0], dy[1]), pack_bf16(dy[2], dy[3]));
-            }
-            io_next(l, gq);
-          }
+      // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
+      //      previous block have completed -------------------------------------------------------------------------
+      if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
+        uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
+        int l = io_l0, gq = io_g0;
+        for (int k = 0; k < hf * (XG / 2); ++k) io_next(l, gq);
+        int lc = l, gc = gq;
+#pragma unroll
+        for (int k = 0; k < XG / 2; ++k) {
+          const int64_t mr = trow(a, row0 + min(lc, rows - 1));
+          xv[k] = *(const uint2*)(xp + mr * a.x_sl + gc * 4);
+          gv[k] = *(const uint2*)(gp + mr * a.g_sl + gc * 4);
+          zv[k] = zp ? *(const uint2*)(zp + mr * a.z_sl + gc * 4) : make_uint2(0, 0);
+          io_next(lc, gc);
         }
-        fence_async_smem();
+#pragma unroll
+        for (int k = 0; k < XG / 2; ++k) {
+          if (l < QB) {
+            const bool valid = l < rows;
+            float dy[4];
+            gate_dy(gv[k], zv[k], dy);
+            const uint2 xs = valid ? xv[k] : make_uint2(0, 0);
+            const float xf[4] = {bf_lo(xs.x), bf_hi(xs.x), bf_lo(xs.y), bf_hi(xs.y)};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (!valid) dy[q] = 0.f;
+              dDacc = fmaf(dy[q], xf[q], dDacc);
+            }
+            *(uint2*)(smem + SM::kX + sw128_off(l, gq * 4)) = xs;
+            *(uint2*)(smem + SM::kDy + sw128_off(l, gq * 4)) = make_uint2(pack_bf16(dy[0], dy[1]), pack_bf16(dy[2], dy[3]));
+          }
+          io_next(l, gq);
+        }
+      }
+      fence_async_smem();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       fence_before_sync();
@@ -334,12 +334,12 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       const uint32_t parity = it & 1;
       // ---- service warp (one lane): MMA phase 1: dM = dy x^T, M = Cd Bd^T ---------------------------------------
       auto issue_phase1 = [&]() {
-  #pragma unroll
+#pragma unroll
         for (int kk = 0; kk < PP / 16; ++kk)
           mma_bf16_off(t_dM, dK, SM::kDy + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(64, 64), kk != 0);
-  #pragma unroll
+#pragma unroll
         for (int at = 0; at < NT / 64; ++at)
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             mma_bf16_off(t_M, dK, SM::kCd + at * (QB * 128) + kk * 32, dK, SM::kBd + at * (QB * 128) + kk * 32,
                          idesc_bf16(64, 64), (at | kk) != 0);
@@ -347,35 +347,35 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       };
       // ---- service warp (one lane): MMA phase 2: BD^T, CD^T (what the (row, state) epilogue waits for), then G, dx ----
       auto issue_phase2 = [&](bool last) {
-  #pragma unroll
+#pragma unroll
         for (int sl = 0; sl < NT / 128; ++sl) {
           const uint32_t dBD = tmem + 128 + sl * 64, dCD = tmem + 256 + sl * 64;
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < 4; ++kk) {                 // K = rows of the block
             const uint32_t oCd = SM::kCd + sl * (2 * QB * 128) + kk * 2048, oBd = SM::kBd + sl * (2 * QB * 128) + kk * 2048;
             mma_bf16_off(dBD, dMN, oCd, dMN, SM::kDMm + kk * 2048, idesc_bf16(128, 64, 1, 1), kk != 0);
             mma_bf16_off(dCD, dMN, oBd, dK, SM::kDMm + kk * 32, idesc_bf16(128, 64, 1, 0), kk != 0);
           }
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < PP / 16; ++kk) {           // K = head dim
             mma_bf16_off(dBD, dK, SM::kGop + sl * (128 * 128) + kk * 32, dK, SM::kX + kk * 32, idesc_bf16(128, 64), 1);
             mma_bf16_off(dCD, dIL, SM::kSop + sl * (128 * 16) + kk * 2 * (NT * 16), dK, SM::kDy + kk * 32, idesc_bf16(128, 64), 1);
           }
         }
         mma_commit(bar2);
-  #pragma unroll
+#pragma unroll
         for (int sl = 0; sl < NT / 128; ++sl)
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < 4; ++kk)                   // G += Cd^T dy
             mma_bf16_off(tmem + 384 + sl * PP, dMN, SM::kCd + sl * (2 * QB * 128) + kk * 2048, dMN, SM::kDy + kk * 2048,
                          idesc_bf16(128, PP, 1, 1), 1);
-  #pragma unroll
+#pragma unroll
         for (int at = 0; at < NT / 64; ++at)               // dx: K = states
-  #pragma unroll
+#pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             mma_bf16_off(t_dx, dK, SM::kBd + at * (QB * 128) + kk * 32, dMN, SM::kGop + (at * 4 + kk) * 2048,
                          idesc_bf16(64, PP, 0, 1), (at | kk) != 0);
-  #pragma unroll
+#pragma unroll
         for (int kk = 0; kk < 4; ++kk)                     // dx: K = later rows
           mma_bf16_off(t_dx, dMN, SM::kMm + kk * 2048, dMN, SM::kDy + kk * 2048, idesc_bf16(64, PP, 1, 1), 1);
         mma_commit(bar2b);
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         float asum = 0.f;
         auto phaseA = [&](auto full) {
           constexpr bool kFull = decltype(full)::value;
-  #pragma unroll
+#pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int l = half * 32 + j;
             float raw;
@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
           const int kc = kcol >> 3;
           float acc = half ? a0 : 0.f;
-  #pragma unroll
+#pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int l = half * 32 + j;
             const int sl = kFull ? l : min(l, rows - 1);
@@ -549,11 +549,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         tmem_ld8(t_G + 16, gc + 16);
         tmem_ld_wait();
         const float eg = ex2f(alast);
-  #pragma unroll
+#pragma unroll
         for (int j = 0; j < HP; ++j) gc[j] *= eg;
         tmem_st16(t_G, gc);
         tmem_st8(t_G + 16, gc + 16);
-  #pragma unroll
+#pragma unroll
         for (int c = 0; c < HP / 8; ++c)
           *(uint4*)(smem + SM::kGop + sw128_chunk(n, half * (HP / 8) + c)) =
               make_uint4(pack_bf16(gc[c * 8], gc[c * 8 + 1]), pack_bf16(gc[c * 8 + 2], gc[c * 8 + 3]),
@@ -571,10 +571,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           tmem_ld16(t0 + c16 * 16, mv);
           tmem_ld_wait();
           if (lane < 16) {
-  #pragma unroll
+#pragma unroll
             for (int c = 0; c < 2; ++c) {
               uint32_t pk[4];
-  #pragma unroll
+#pragma unroll
               for (int j = 0; j < 8; j += 2) {
                 const int s = c16 * 16 + c * 8 + j;
                 pk[j >> 1] = pack_bf16(s <= l ? mv[c * 8 + j] : 0.f, s + 1 <= l ? mv[c * 8 + j + 1] : 0.f);
@@ -597,13 +597,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
         const int kc = kcol >> 3;
         float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
-  #pragma unroll
+#pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           float bdv[8], cdv[8];
           tmem_ld8(t_BD + ch * 8, bdv);
           tmem_ld8(t_CD + ch * 8, cdv);
           tmem_ld_wait();
-  #pragma unroll
+#pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
             part = fmaf(__bfloat162float(*(const bf16*)(cd_col + off)), cdv[j], part);
@@ -615,19 +615,22 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         const float p0 = sXch[n];
         const float total = p0 + sXch[NT + n];
         // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
-        const int64_t ostep = (int64_t)(a.rev ? -1 : 1) * a.H * a.N;
+        const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
         const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        TDT* const p_ddt = (TDT*)a.ddt + o0;
+        bf16* const p_dB = a.dBh + o0;
+        bf16* const p_dC = a.dCh + o0;
         auto epi = [&](auto full) {
           constexpr bool kFull = decltype(full)::value;
           float prefix = half ? p0 : 0.f;
           float ac = half ? a0 : 0.f;
-  #pragma unroll
+#pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             float bdv[8], cdv[8];
             tmem_ld8(t_BD + ch * 8, bdv);
             tmem_ld8(t_CD + ch * 8, cdv);
             tmem_ld_wait();
-  #pragma unroll
+#pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int l = half * 32 + ch * 8 + j;
               const int sl = kFull ? l : min(l, rows - 1);
@@ -652,10 +655,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
               if (in) {
                 dAacc = fmaf(ddA, dtl, dAacc);
                 dbacc += gd;
-                const int64_t o = o0 + l * ostep;
-                stf((TDT*)a.ddt + o, gd);
-                a.dBh[o] = __float2bfloat16_rn(dtl * bd);
-                a.dCh[o] = __float2bfloat16_rn(cd);
+                const int o = l * ostep;
+                stf(p_ddt + o, gd);
+                p_dB[o] = __float2bfloat16_rn(dtl * bd);
+                p_dC[o] = __float2bfloat16_rn(cd);
               }
             }
           }
@@ -671,7 +674,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           tmem_ld16(t_dx + lane_base + c16 * 16, dv);
           tmem_ld_wait();
           if (lane < 16 && (first || (l >= w0 && l < w1))) {
-  #pragma unroll
+#pragma unroll
             for (int c = 0; c < 4; ++c)
               if (c16 * 16 + c * 4 < SM::DXS)
                 *(uint2*)(smem + SM::kDxT + (l * SM::DXS + c16 * 16 + c * 4) * 2) =
@@ -680,30 +683,30 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         }
       };
 
-        // ---- <S leaving the block, G> over this thread's state columns: the S operand tile still holds the
-        //      state entering the block processed before this one, i.e. the state leaving this block ------------
-        float cpart = 0.f;
-        {
-          float gc[HP];
-          tmem_ld16(t_G, gc);
-          tmem_ld8(t_G + 16, gc + 16);
-          if (!mbar_wait(barU, parity)) failed = true;
-          uint4 snv[HP / 8];
-  #pragma unroll
-          for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
-          tmem_ld_wait();
-  #pragma unroll
-          for (int c = 0; c < HP / 8; ++c) {
-            const uint32_t w[4] = {snv[c].x, snv[c].y, snv[c].z, snv[c].w};
-  #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
-              cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
-            }
+      // ---- <S leaving the block, G> over this thread's state columns: the S operand tile still holds the
+      //      state entering the block processed before this one, i.e. the state leaving this block ------------
+      float cpart = 0.f;
+      {
+        float gc[HP];
+        tmem_ld16(t_G, gc);
+        tmem_ld8(t_G + 16, gc + 16);
+        if (!mbar_wait(barU, parity)) failed = true;
+        uint4 snv[HP / 8];
+#pragma unroll
+        for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < HP / 8; ++c) {
+          const uint32_t w[4] = {snv[c].x, snv[c].y, snv[c].z, snv[c].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            cpart = fmaf(__uint_as_float(w[j] << 16), gc[c * 8 + 2 * j], cpart);
+            cpart = fmaf(__uint_as_float(w[j] & 0xffff0000u), gc[c * 8 + 2 * j + 1], cpart);
           }
         }
-        if (kStageDt && !mbar_wait(barS, parity)) failed = true;
-        phaseAB(0, rows, true, cpart);
+      }
+      if (kStageDt && !mbar_wait(barS, parity)) failed = true;
+      phaseAB(0, rows, true, cpart);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
@@ -742,98 +745,98 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       } else if (kWin) {
         // windowed block (named barriers 11 / 12 / 13 with the service warp)
       const size_t sblk = (size_t)a.N * PP;                // elements of one saved state
-        windowed = 1;
-        named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
-        const float cst_block = cst;
-        const size_t mine = ((size_t)half * (HP / 8) * a.N + n) * 8;          // this thread's chunks inside a state
-        const bf16* sv0 = a.saved + (bh * (nblk + 1) + blk) * sblk + mine;    // state entering the block
-        bf16* wsc = a.wscr + bh * 63 * sblk + mine;                           // slot j: state entering window j + 1
-        const uint32_t t_W = tmem + lane_base + 128 + slab * 64 + half * HP;  // accumulator of the walk
-        auto unpack = [&](const bf16* src, float* sc) {
+      windowed = 1;
+      named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
+      const float cst_block = cst;
+      const size_t mine = ((size_t)half * (HP / 8) * a.N + n) * 8;          // this thread's chunks inside a state
+      const bf16* sv0 = a.saved + (bh * (nblk + 1) + blk) * sblk + mine;    // state entering the block
+      bf16* wsc = a.wscr + bh * 63 * sblk + mine;                           // slot j: state entering window j + 1
+      const uint32_t t_W = tmem + lane_base + 128 + slab * 64 + half * HP;  // accumulator of the walk
+      auto unpack = [&](const bf16* src, float* sc) {
 #pragma unroll
-          for (int c = 0; c < HP / 8; ++c) {
-            const uint4 v = *(const uint4*)(src + (size_t)c * a.N * 8);
-            const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+        for (int c = 0; c < HP / 8; ++c) {
+          const uint4 v = *(const uint4*)(src + (size_t)c * a.N * 8);
+          const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              sc[c * 8 + 2 * j] = __uint_as_float(wd[j] << 16);
-              sc[c * 8 + 2 * j + 1] = __uint_as_float(wd[j] & 0xffff0000u);
-            }
-          }
-        };
-        {
-          float sc[HP];
-          unpack(sv0, sc);
-          tmem_st16(t_W, sc);
-          tmem_st8(t_W + 16, sc + 16);
-          tmem_st_wait();
-          for (int w = 0; w + 1 < npass; ++w) {
-            phaseAB(w * ws, min(rows, w * ws + ws), false, 0.f);
-            fence_before_sync();
-            named_barrier(11, NTH + 32);
-            if (!mbar_wait(barW, cw & 1)) failed = true;
-            ++cw;
-            fence_after_sync();
-            tmem_ld16(t_W, sc);
-            tmem_ld8(t_W + 16, sc + 16);
-            tmem_ld_wait();
-            const float el = ex2f(fminf(fmaxf(alast, -100.f), 100.f));
-#pragma unroll
-            for (int j = 0; j < HP; ++j) sc[j] *= el;
-            tmem_st16(t_W, sc);
-            tmem_st8(t_W + 16, sc + 16);
-            bf16* dst = wsc + (size_t)w * sblk;
-#pragma unroll
-            for (int c = 0; c < HP / 8; ++c)
-              *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
-                                  pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
-            tmem_st_wait();
-            fence_before_sync();
-            named_barrier(12, NTH + 32);
+          for (int j = 0; j < 4; ++j) {
+            sc[c * 8 + 2 * j] = __uint_as_float(wd[j] << 16);
+            sc[c * 8 + 2 * j + 1] = __uint_as_float(wd[j] & 0xffff0000u);
           }
         }
-        for (int w = npass - 1, k = 0; w >= 0; --w, ++k) {
-          const int w0 = w * ws, w1 = min(rows, w0 + ws);
-          // <state leaving the window, G>: the last window leaves the block (computed above); the others read the walk's copy
-          float cpart = half ? 0.f : cst_block;
-          if (w < npass - 1) {
-            float gc[HP], sn[HP];
-            tmem_ld16(t_G, gc);
-            tmem_ld8(t_G + 16, gc + 16);
-            unpack(wsc + (size_t)w * sblk, sn);
-            tmem_ld_wait();
-            cpart = 0.f;
-#pragma unroll
-            for (int j = 0; j < HP; ++j) cpart = fmaf(sn[j], gc[j], cpart);
-          }
-          {                                                // S operand tile <- state entering the window
-            const bf16* src = w ? wsc + (size_t)(w - 1) * sblk : sv0;
-#pragma unroll
-            for (int c = 0; c < HP / 8; ++c)
-              *(uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16) = *(const uint4*)(src + (size_t)c * a.N * 8);
-          }
-          phaseAB(w0, w1, false, cpart);
-          alast = fminf(fmaxf(alast, -100.f), 100.f);
-          gprime();
-          fence_async_smem();
+      };
+      {
+        float sc[HP];
+        unpack(sv0, sc);
+        tmem_st16(t_W, sc);
+        tmem_st8(t_W + 16, sc + 16);
+        tmem_st_wait();
+        for (int w = 0; w + 1 < npass; ++w) {
+          phaseAB(w * ws, min(rows, w * ws + ws), false, 0.f);
           fence_before_sync();
           named_barrier(11, NTH + 32);
-          if (!mbar_wait(bar1, (c1 + k) & 1)) failed = true;
+          if (!mbar_wait(barW, cw & 1)) failed = true;
+          ++cw;
           fence_after_sync();
-          epilogue1();
-          fence_async_smem();
+          tmem_ld16(t_W, sc);
+          tmem_ld8(t_W + 16, sc + 16);
+          tmem_ld_wait();
+          const float el = ex2f(fminf(fmaxf(alast, -100.f), 100.f));
+#pragma unroll
+          for (int j = 0; j < HP; ++j) sc[j] *= el;
+          tmem_st16(t_W, sc);
+          tmem_st8(t_W + 16, sc + 16);
+          bf16* dst = wsc + (size_t)w * sblk;
+#pragma unroll
+          for (int c = 0; c < HP / 8; ++c)
+            *(uint4*)(dst + (size_t)c * a.N * 8) = make_uint4(pack_bf16(sc[c * 8], sc[c * 8 + 1]), pack_bf16(sc[c * 8 + 2], sc[c * 8 + 3]),
+                                pack_bf16(sc[c * 8 + 4], sc[c * 8 + 5]), pack_bf16(sc[c * 8 + 6], sc[c * 8 + 7]));
+          tmem_st_wait();
           fence_before_sync();
           named_barrier(12, NTH + 32);
-          if (!mbar_wait(bar2, (c2 + k) & 1)) failed = true;
-          fence_after_sync();
-          epilogue_a(w0, w1, false);
-          if (!mbar_wait(bar2b, (c2 + k) & 1)) failed = true;
-          fence_after_sync();
-          epilogue_b(w0, w1, false);
-          fence_before_sync();
-          named_barrier(13, NTH + 32);
         }
-        asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
+      }
+      for (int w = npass - 1, k = 0; w >= 0; --w, ++k) {
+        const int w0 = w * ws, w1 = min(rows, w0 + ws);
+        // <state leaving the window, G>: the last window leaves the block (computed above); the others read the walk's copy
+        float cpart = half ? 0.f : cst_block;
+        if (w < npass - 1) {
+          float gc[HP], sn[HP];
+          tmem_ld16(t_G, gc);
+          tmem_ld8(t_G + 16, gc + 16);
+          unpack(wsc + (size_t)w * sblk, sn);
+          tmem_ld_wait();
+          cpart = 0.f;
+#pragma unroll
+          for (int j = 0; j < HP; ++j) cpart = fmaf(sn[j], gc[j], cpart);
+        }
+        {                                                // S operand tile <- state entering the window
+          const bf16* src = w ? wsc + (size_t)(w - 1) * sblk : sv0;
+#pragma unroll
+          for (int c = 0; c < HP / 8; ++c)
+            *(uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16) = *(const uint4*)(src + (size_t)c * a.N * 8);
+        }
+        phaseAB(w0, w1, false, cpart);
+        alast = fminf(fmaxf(alast, -100.f), 100.f);
+        gprime();
+        fence_async_smem();
+        fence_before_sync();
+        named_barrier(11, NTH + 32);
+        if (!mbar_wait(bar1, (c1 + k) & 1)) failed = true;
+        fence_after_sync();
+        epilogue1();
+        fence_async_smem();
+        fence_before_sync();
+        named_barrier(12, NTH + 32);
+        if (!mbar_wait(bar2, (c2 + k) & 1)) failed = true;
+        fence_after_sync();
+        epilogue_a(w0, w1, false);
+        if (!mbar_wait(bar2b, (c2 + k) & 1)) failed = true;
+        fence_after_sync();
+        epilogue_b(w0, w1, false);
+        fence_before_sync();
+        named_barrier(13, NTH + 32);
+      }
+      asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");
       }
       if (kWin) { c1 += npass; c2 += npass; }
       fence_before_sync();
