@@ -479,23 +479,29 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
         const int bstep = flipB ? -NT : NT;
 
-        // ---- phase A: dt of this thread's 32 rows and their summed log2-decay (dt is recomputed from the
-        //      staged raw values in the epilogue instead of being held in registers across the MMA phases) ------
-        float dtv[32];
+        // ---- phase A: dt of this thread's 32 rows and their summed log2-decay.  The loops over the rows run as
+        //      4 iterations of 8 unrolled rows (a quarter of the instruction footprint of full unrolling, which
+        //      measurably stalled instruction fetch); the dt values wait for phase B in this thread's own 32
+        //      columns of the CD^T accumulator, which is not live before the second MMA phase ---------------------
         float asum = 0.f;
         auto phaseA = [&](auto full) {
           constexpr bool kFull = decltype(full)::value;
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            float dv[8];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int l = half * 32 + j;
-            float raw;
-            if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
-            else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
-            bool clamped = false;
-            float v = dt_transform(a, raw, bias, clamped);
-            if (!kFull && (l < w0 || l >= w1)) v = 0.f;
-            dtv[j] = v;
-            asum = fmaf(v, A2, asum);
+            for (int j = 0; j < 8; ++j) {
+              const int l = half * 32 + ch * 8 + j;
+              float raw;
+              if (kStageDt) raw = __bfloat162float(sdt[(kFull ? l : min(l, rows - 1)) * dstep]);
+              else raw = ldf(dtp + (int64_t)trow(a, row0 + (kFull ? l : min(l, rows - 1))) * a.dt_sl + n);
+              bool clamped = false;
+              float v = dt_transform(a, raw, bias, clamped);
+              if (!kFull && (l < w0 || l >= w1)) v = 0.f;
+              dv[j] = v;
+              asum = fmaf(v, A2, asum);
+            }
+            tmem_st8(t_CD + ch * 8, dv);
           }
         };
         if (first && rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
@@ -521,21 +527,28 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
           const int kc = kcol >> 3;
           float acc = half ? a0 : 0.f;
+          tmem_st_wait();
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            float dv[8];
+            tmem_ld8(t_CD + ch * 8, dv);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int l = half * 32 + j;
-            const int sl = kFull ? l : min(l, rows - 1);
-            acc = fmaf(dtv[j], A2, acc);
-            const float e = (kWin && !first) ? fminf(fmaxf(acc, -100.f), 100.f) : acc;
-            float cv;
-            if (kWin && !first) cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + sl) * a.C_sl + n]);
-            else cv = __bfloat162float(sC[sl * bstep]);
-            float cd = cv * ex2f(e);
-            float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-e);
-            if (!kFull && (l < w0 || l >= w1)) { cd = 0.f; bd = 0.f; }
-            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
-            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+            for (int j = 0; j < 8; ++j) {
+              const int l = half * 32 + ch * 8 + j;
+              const int sl = kFull ? l : min(l, rows - 1);
+              acc = fmaf(dv[j], A2, acc);
+              const float e = (kWin && !first) ? fminf(fmaxf(acc, -100.f), 100.f) : acc;
+              float cv;
+              if (kWin && !first) cv = __bfloat162float(Cp[(int64_t)trow(a, row0 + sl) * a.C_sl + n]);
+              else cv = __bfloat162float(sC[sl * bstep]);
+              float cd = cv * ex2f(e);
+              float bd = __bfloat162float(sB[sl * bstep]) * dv[j] * ex2f(-e);
+              if (!kFull && (l < w0 || l >= w1)) { cd = 0.f; bd = 0.f; }
+              const uint32_t off = (uint32_t)((ch * 8 + j) * 128 + ((kc ^ j) << 4));
+              *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+              *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+            }
           }
         };
         if (first && rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
@@ -597,7 +610,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
         const int kc = kcol >> 3;
         float part = 0.f;                                  // sum over this thread's rows of dacs = Cd CD - Bd BD
-#pragma unroll
+#pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           float bdv[8], cdv[8];
           tmem_ld8(t_BD + ch * 8, bdv);
@@ -624,7 +637,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           constexpr bool kFull = decltype(full)::value;
           float prefix = half ? p0 : 0.f;
           float ac = half ? a0 : 0.f;
-#pragma unroll
+#pragma unroll 2
           for (int ch = 0; ch < 4; ++ch) {
             float bdv[8], cdv[8];
             tmem_ld8(t_BD + ch * 8, bdv);
