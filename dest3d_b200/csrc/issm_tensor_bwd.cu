@@ -56,7 +56,10 @@ struct BwdSmem {
 // pass of the ordinary block code restricted to the window's rows, with its own reference, the state entering the
 // window as the S operand and the rescaled G as g'.  The window-entry states come from a short forward walk over
 // the block's windows (S += Bd^T x on the tensor cores, rescale, bf16 copy to a.wscr) run first.
-template <int NT, typename TDT, bool kWin>
+// kMode fixes the row order of the staged tiles at compile time, so that their addresses need no multiply:
+// 1 = dt / B / C tiles staged in scan order (forward scan of regular arrays), 2 = staged in memory order for a
+// reversed scan (walked backwards), 0 = decided at run time (row-by-row copies, mixed layouts).
+template <int NT, typename TDT, bool kWin, int kMode>
 __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = BwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
@@ -119,7 +122,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   const uint32_t t_CD = tmem + lane_base + 256 + slab * 64 + half * 32;
   const uint32_t t_G = tmem + lane_base + 384 + slab * PP + half * HP;    // this thread's part of G[n, :]
   const int kcol = n & 63;
-  const bool flipB = a.bc_contig && a.rev;               // staged B rows are in memory order
+  const bool flipB = kMode ? kMode == 2 : (a.bc_contig && a.rev);   // staged B rows are in memory order
 
   // ---- service warp: bulk prefetches ------------------------------------------------------------------
   auto prefetch_dt = [&](int blk) {
@@ -472,7 +475,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       auto phaseAB = [&](int w0, int w1, bool first, float cpart) {
         // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
         // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-        const bool flipT = a.dt_tma && a.rev;
+        const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev);
         const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
         const int dstep = flipT ? -NT : NT;
         const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
@@ -601,7 +604,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       // ---- column threads, epilogue (a): the owner of (rows 32 half.., state n): dB_h, dC_h, ddt and the reverse
       //      cumsum of dacs, for the rows [w0, w1) of the block ------------------------------------------------------
       auto epilogue_a = [&](int w0, int w1, bool first) {
-        const bool flipT = a.dt_tma && a.rev;
+        const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev);
         const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
         const int dstep = flipT ? -NT : NT;
         const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
@@ -1005,19 +1008,27 @@ size_t tensor_bwd_workspace_bytes(const issm_params& p) {
   return total;
 }
 
+template <int NT, typename TDT, int kMode>
+static int launch_bwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_t s) {
+  const size_t smem = BwdSmem<NT>::kTotal + 1024;
+  if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, false, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return ISSM_ERR_CUDA;
+  }
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  return ISSM_OK;
+}
+
 template <int NT, typename TDT>
 static int launch_bwd(TArgs a, const issm_params& p, cudaStream_t s) {
   CUtensorMap dtmap;
   a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
-  const size_t smem = BwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-      cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return ISSM_ERR_CUDA;
-  }
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
-  return ISSM_OK;
+  // whole-tile copies of dt (when it is staged at all) and of B / C: the row order of the staged tiles is known
+  const bool tiles = a.bc_contig && (sizeof(TDT) != 2 || a.dt_tma);
+  if (!tiles) return launch_bwd_mode<NT, TDT, 0>(a, dtmap, s);
+  return a.rev ? launch_bwd_mode<NT, TDT, 2>(a, dtmap, s) : launch_bwd_mode<NT, TDT, 1>(a, dtmap, s);
 }
 
 int tensor_bwd(const issm_params& p, cudaStream_t s) {
