@@ -159,7 +159,10 @@ __device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c)
 // of the single-reference factorisation and marks its (batch, head) stream in a.redo.  kWin = true is launched
 // right behind it, returns at once for unmarked streams and redoes the marked ones from the start with the
 // windowed passes described at fwd_windowed_passes (keeping that code out of the fast kernel is worth 15 %).
-template <int NT, typename TDT, bool kWin>
+// kMode fixes the row order of the staged tiles at compile time, so that their addresses need no multiply:
+// 1 = dt / B / C tiles staged in scan order (forward scan of regular arrays), 2 = staged in memory order for a
+// reversed scan (walked backwards), 0 = decided at run time (row-by-row copies, mixed layouts).
+template <int NT, typename TDT, bool kWin, int kMode>
 __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ CUtensorMap dtmap) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 
       // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
       // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-      const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
+      const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev), flipB = kMode ? kMode == 2 : (a.bc_contig && a.rev);
       const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
       const int dstep = flipT ? -NT : NT;
       const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
@@ -681,19 +684,27 @@ bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int NT, typename TDT, int kMode>
+static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_t s) {
+  const size_t smem = FwdSmem<NT>::kTotal + 1024;
+  if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, false, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return ISSM_ERR_CUDA;
+  }
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  return ISSM_OK;
+}
+
 template <int NT, typename TDT>
 static int launch_fwd(TArgs a, const issm_params& p, cudaStream_t s) {
   CUtensorMap dtmap;
   a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
-  const size_t smem = FwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-      cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return ISSM_ERR_CUDA;
-  }
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
-  return ISSM_OK;
+  // whole-tile copies of dt (when it is staged at all) and of B / C: the row order of the staged tiles is known
+  const bool tiles = a.bc_contig && (sizeof(TDT) != 2 || a.dt_tma);
+  if (!tiles) return launch_fwd_mode<NT, TDT, 0>(a, dtmap, s);
+  return a.rev ? launch_fwd_mode<NT, TDT, 2>(a, dtmap, s) : launch_fwd_mode<NT, TDT, 1>(a, dtmap, s);
 }
 
 int tensor_fwd(const issm_params& p, cudaStream_t s) {
