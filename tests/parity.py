@@ -68,6 +68,13 @@ def cuda_run(inp, Q, opts, path="auto", device="cuda"):
                 wide = torch.zeros(b, L, H * P + 8, dtype=t.dtype, device=device)
                 wide[..., 4:4 + H * P] = t.reshape(b, L, H * P)
                 t = wide[..., 4:4 + H * P].unflatten(-1, (H, P))
+            if opts.get("noncontig_bc") and k in ("B", "C"):
+                # B and C as the two halves of one projection output, as torch.split() leaves them: row stride 2 N
+                bb, L, G, N = t.shape
+                wide = torch.zeros(bb, L, G, 2 * N, dtype=t.dtype, device=device)
+                half = slice(0, N) if k == "B" else slice(N, 2 * N)
+                wide[..., half] = t
+                t = wide[..., half]
             leaves[k] = t.requires_grad_()
     use = lambda k: leaves.get(k)
     want_final = opts.get("return_final", True)

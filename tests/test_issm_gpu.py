@@ -32,6 +32,7 @@ CASES = [
     # dt up to ~20 and dt*|A| up to ~300 per step: a range-safety case (no overflow, no NaN); float32
     # rounding is amplified by the large step sizes, so its tolerance is 10x the nominal one
     ("unbounded_dt", (1, 128, 2, 36, 64, 1, 64), {}, dict(dt_softplus=True, dt_scale=5.0, loosen=10.0)),
+    ("split_bc", (1, 130, 2, 36, 64, 1, 64), {}, dict(BENCH_OPTS, noncontig_bc=True)),
     ("L1", (1, 1, 2, 36, 64, 1, 64), {}, BENCH_OPTS),
 ]
 
@@ -66,6 +67,8 @@ TENSOR_CASES = [
     ("t_L1", (1, 1, 1, 36, 128, 1, 64), {}, BENCH_OPTS),
     ("t_groups_Dhdim", (1, 130, 4, 20, 128, 2, 128), dict(D_has_hdim=True), BENCH_OPTS),
     ("t_noncontig", (1, 128, 2, 36, 256, 1, 64), {}, dict(BENCH_OPTS, noncontig=True)),
+    ("t_split_bc", (2, 200, 2, 36, 256, 1, 64), {}, dict(BENCH_OPTS, noncontig_bc=True)),
+    ("t_split_bc_reverse", (1, 150, 2, 36, 128, 1, 64), {}, dict(BENCH_OPTS, noncontig_bc=True, reverse=True)),
     ("t_no_init_no_final", (1, 192, 2, 36, 256, 1, 64), {}, dict(BENCH_OPTS, use_initial_states=False, return_final=False, dfinal=False, use_z=False, use_D=False)),
 ]
 
