@@ -371,6 +371,9 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         io_next(l, gq);
       }
       fence_async_smem();
+      // the z rows of this block are first needed when its output rows are written, one block later: have them in L2
+      if (a.has_z && !a.no_output)
+        for (int r = io_t; r < rows; r += NIO) prefetch_l2_span(zp + (int64_t)trow(a, row0 + r) * a.z_sl, a.P * 2);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);

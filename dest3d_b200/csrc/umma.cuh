@@ -171,6 +171,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst_smem, const void* tmap, in
                ::"r"(smem_u32(dst_smem)), "l"(tmap), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
 
+// bring the 32-byte sectors of [p, p + bytes) into L2 (no register result, nothing to wait for)
+__device__ __forceinline__ void prefetch_l2_span(const void* p, int bytes) {
+  const char* c = (const char*)p;
+  for (int o = 0; o < bytes; o += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(c + bytes - 1));
+}
 __device__ __forceinline__ float ex2f(float v) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
