@@ -232,7 +232,18 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       }
     }
   };
-  if (is_svc) prefetch(0);
+  // the whole-tile copies of the block after the next one are announced to L2 at the same time
+  auto prefetch_l2 = [&](int blk) {
+    if (blk >= nblk) return;
+    const int row0 = blk * QB, rows = min(QB, a.L - row0);
+    const int64_t m0 = a.rev ? a.L - row0 - rows : row0;
+    if (kStageDt && a.dt_tma && lane == 2) tma_prefetch_2d(&dtmap, h * (int)a.dt_sh, b * a.L + (int)m0);
+    if (a.bc_contig) {
+      if (lane == 0) bulk_prefetch_l2(Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2);
+      if (lane == 1) bulk_prefetch_l2(Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2);
+    }
+  };
+  if (is_svc) { prefetch(0); prefetch_l2(1); }
 
   uint8_t* sop_col = smem + SM::kSop + (n >> 6) * SM::kAtomB;
   const int kcol = n & 63;
@@ -415,6 +426,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         }
       }
       if (blk + 1 < nblk) prefetch(blk + 1);             // every column thread is past its staging reads
+      prefetch_l2(blk + 2);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (a.no_output) continue;

@@ -177,6 +177,14 @@ __device__ __forceinline__ void prefetch_l2_span(const void* p, int bytes) {
   for (int o = 0; o < bytes; o += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
   asm volatile("prefetch.global.L2 [%0];" ::"l"(c + bytes - 1));
 }
+// L2 prefetches of the same shapes (no shared-memory destination, no barrier): the real copy issued one block
+// later then finds its data in L2
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ float ex2f(float v) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
