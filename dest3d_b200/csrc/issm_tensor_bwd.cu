@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   constexpr int HP = PP / 2;
   constexpr int NCG = NT / 64;                          // column groups of the row epilogues
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // 1024-byte aligned base, kept as "shared array + offset" so that the compiler still knows the address space
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bar1 = (uint64_t*)(smem + SM::kBars);
   uint64_t* bar2 = bar1 + 1;
   uint64_t* barS = bar1 + 2;     // dt staging

@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(128) k_umma_selftest(int M, int N, int K, int 
                                                        const bf16* __restrict__ A, const bf16* __restrict__ B,
                                                        float* __restrict__ D, float* __restrict__ Draw, int* status) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_holder;
   uint8_t* sA = smem;
