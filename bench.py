@@ -276,7 +276,7 @@ def run_mine(args):
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on the small profiling case c3s
 # (batch 16, L = 4096), from the ncu captures summarised in profiles/; traffic grows in proportion to batch x L
-NCU_C3S_TRAFFIC = {"fwd": 413.6e6 + 249.4e6, "bwd": 698.8e6 + 838.0e6}
+NCU_C3S_TRAFFIC = {"fwd": 413.5e6 + 248.0e6, "bwd": 698.5e6 + 839.5e6}
 
 
 def kernel_roofline(dev, par, dfinal, w, batch, path):
