@@ -344,6 +344,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 for multi-process launches; this arm runs on rank 0 alone and is meant to
+    # use every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     w = WORKLOADS[args.workload]
     Ls = min(512, w["L"])
     for _ in range(min(args.warmup, 1)):
