@@ -41,7 +41,7 @@ struct TArgs {
   const bf16* dout; int64_t g_sb, g_sl, g_sh;
   const float* dfinal;
   bf16* dx; void* ddt; bf16* dz; bf16* dinit;
-  bf16* dBh; bf16* dCh;                 // per-head partials (b, L, H, N)
+  uint32_t* dBCh;                       // per-head partials (b, L, H, N) of packed bf16 pairs {dB_h, dC_h}
   float* dApart; float* dbpart;         // (b, H, N)
   float* dDpart;                        // (b, H, PP)
 };

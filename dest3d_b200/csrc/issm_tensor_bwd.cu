@@ -635,8 +635,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
         const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
         TDT* const p_ddt = (TDT*)a.ddt + o0;
-        bf16* const p_dB = a.dBh + o0;
-        bf16* const p_dC = a.dCh + o0;
+        uint32_t* const p_dBC = a.dBCh + o0;
         auto epi = [&](auto full) {
           constexpr bool kFull = decltype(full)::value;
           float prefix = half ? p0 : 0.f;
@@ -674,8 +673,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
                 dbacc += gd;
                 const int o = l * ostep;
                 stf(p_ddt + o, gd);
-                p_dB[o] = __float2bfloat16_rn(dtl * bd);
-                p_dC[o] = __float2bfloat16_rn(cd);
+                p_dBC[o] = pack_bf16(dtl * bd, cd);                 // one store for the pair {dB_h, dC_h}
               }
             }
           }
@@ -924,8 +922,10 @@ __global__ void k_dD_hdim(const TArgs a) {
   }
 }
 
-// dB[b,l,g,n] = sum over the heads of group g of the bf16 per-head partials
-__global__ void k_reduce_heads_bf16(int hpg, int N, int H, size_t total, const bf16* __restrict__ part, bf16* __restrict__ out) {
+// dB[b,l,g,n], dC[b,l,g,n] = sums over the heads of group g of the per-head partials, stored as packed bf16 pairs
+// {dB_h, dC_h} per (b, l, h, n); fixed order, 8 states per thread
+__global__ void k_reduce_heads_bf16(int hpg, int N, int H, size_t total, const uint32_t* __restrict__ part,
+                                    bf16* __restrict__ outB, bf16* __restrict__ outC) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // over (b, l, g, n/8)
   if (i >= total) return;
   const int n8 = N / 8;
@@ -934,20 +934,23 @@ __global__ void k_reduce_heads_bf16(int hpg, int N, int H, size_t total, const b
   const int G = H / hpg;
   const size_t bl = blg / G;
   const int g = blg % G;
-  float acc[8];
+  float accB[8], accC[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int j = 0; j < 8; ++j) { accB[j] = 0.f; accC[j] = 0.f; }
   for (int k = 0; k < hpg; ++k) {
-    const uint4 v = *(const uint4*)(part + ((bl * H + g * hpg + k) * N) + c * 8);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const uint4* src = (const uint4*)(part + ((bl * H + g * hpg + k) * N) + c * 8);
+    const uint4 v0 = src[0], v1 = src[1];
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      acc[2 * j] += __uint_as_float(w[j] << 16);
-      acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+    for (int j = 0; j < 8; ++j) {
+      accB[j] += __uint_as_float(w[j] << 16);
+      accC[j] += __uint_as_float(w[j] & 0xffff0000u);
     }
   }
-  *(uint4*)(out + blg * N + c * 8) = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
-                                                pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  *(uint4*)(outB + blg * N + c * 8) = make_uint4(pack_bf16(accB[0], accB[1]), pack_bf16(accB[2], accB[3]),
+                                                 pack_bf16(accB[4], accB[5]), pack_bf16(accB[6], accB[7]));
+  *(uint4*)(outC + blg * N + c * 8) = make_uint4(pack_bf16(accC[0], accC[1]), pack_bf16(accC[2], accC[3]),
+                                                 pack_bf16(accC[4], accC[5]), pack_bf16(accC[6], accC[7]));
 }
 
 // out[h, j] = sum_b part[b, h, j]   (fixed order)
@@ -978,7 +981,8 @@ __global__ void k_reduce_dD(const float* __restrict__ part, int batch, int H, in
 
 // ---------------------------------------------------------------------------------------------
 struct BwdWs {
-  bf16 *dBh, *dCh, *saved, *wscr;
+  uint32_t* dBCh;
+  bf16 *saved, *wscr;
   float *dApart, *dbpart, *dDpart;
   int *redo_fwd, *redo_bwd;
 };
@@ -988,8 +992,7 @@ static BwdWs carve_bwd(const issm_params& p, size_t* total) {
   BwdWs w{};
   const size_t b = p.batch, L = p.seqlen, H = p.nheads, N = p.dstate;
   const size_t nblk = (L + QB - 1) / QB;
-  w.dBh = c.take<bf16>(b * L * H * N);
-  w.dCh = c.take<bf16>(b * L * H * N);
+  w.dBCh = c.take<uint32_t>(b * L * H * N);
   w.dApart = c.take<float>(b * H * N);
   w.dbpart = c.take<float>(b * H * N);
   w.dDpart = c.take<float>(b * H * PP);
@@ -1047,7 +1050,7 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   a.dout = (const bf16*)p.dout; a.g_sb = p.dout_sb; a.g_sl = p.dout_sl; a.g_sh = p.dout_sh;
   a.dfinal = p.has_dfinal ? p.dfinal_states : nullptr;
   a.dx = (bf16*)p.dx; a.ddt = p.ddt; a.dz = (bf16*)p.dz; a.dinit = (bf16*)p.dinitial_states;
-  a.dBh = w.dBh; a.dCh = w.dCh; a.dApart = w.dApart; a.dbpart = w.dbpart; a.dDpart = w.dDpart;
+  a.dBCh = w.dBCh; a.dApart = w.dApart; a.dbpart = w.dbpart; a.dDpart = w.dDpart;
   a.redo = w.redo_bwd; a.wscr = w.wscr;
   int rc;
   if (p.dstate == 256) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, p, s) : launch_bwd<256, float>(a, p, s);
@@ -1055,8 +1058,7 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   if (rc) return rc;
   const int hpg = p.nheads / p.ngroups;
   const size_t tot = (size_t)p.batch * p.seqlen * p.ngroups * (p.dstate / 8);
-  ISSM_LAUNCH(k_reduce_heads_bf16, (unsigned)cdiv64(tot, 256), 256, 0, s, hpg, p.dstate, p.nheads, tot, w.dBh, (bf16*)p.dB);
-  ISSM_LAUNCH(k_reduce_heads_bf16, (unsigned)cdiv64(tot, 256), 256, 0, s, hpg, p.dstate, p.nheads, tot, w.dCh, (bf16*)p.dC);
+  ISSM_LAUNCH(k_reduce_heads_bf16, (unsigned)cdiv64(tot, 256), 256, 0, s, hpg, p.dstate, p.nheads, tot, w.dBCh, (bf16*)p.dB, (bf16*)p.dC);
   const int HN = p.nheads * p.dstate;
   ISSM_LAUNCH(k_reduce_batch, (HN + 127) / 128, 128, 0, s, w.dApart, p.batch, HN, p.dA);
   if (p.has_dt_bias) ISSM_LAUNCH(k_reduce_batch, (HN + 127) / 128, 128, 0, s, w.dbpart, p.batch, HN, p.ddt_bias);
