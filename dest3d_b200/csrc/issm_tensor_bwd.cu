@@ -18,7 +18,7 @@
 //   ddt = (ddt_direct + ddA A) * [not clamped] * sigmoid(pre),  dA += ddA dt,  ddt_bias += ddt
 // (replacing issm_combined.py:451, issm_cabt_bmm.py:539, issm_chunk_scan.py:573/948,
 // issm_chunk_state.py:559/159 and the torch glue of issm_combined.py:159-175).
-// Per-head dB / dC partials go to a bf16 workspace and are summed over heads by a second kernel.
+// Per-head dB / dC partials go to a workspace as packed bf16 pairs and are summed over heads by a second kernel.
 #include "issm_tensor.cuh"
 
 namespace issm {
