@@ -1,6 +1,7 @@
-"""Builds the C-ABI shared library `libissm_b200.so` for sm_100a with nvcc, in-tree.
+"""Builds, in-tree, the C-ABI shared library `libissm_b200.so` (CUDA kernels, sm_100a, nvcc) and the torch C++
+extension `libissm_b200_torch.so` (TORCH_LIBRARY ops over that C ABI, host code only, g++).
 
-    python -m dest3d_b200.build            # build if sources are newer than the library
+    python -m dest3d_b200.build            # build what is older than its sources
     python -m dest3d_b200.build --force
 """
 import os
@@ -11,7 +12,9 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libissm_b200.so")
-SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "issm_tensor_bwd.cu", "umma_selftest.cu"]
+TORCH_LIB = os.path.join(PKG, "libissm_b200_torch.so")
+TORCH_SRC = os.path.join(CSRC, "issm_torch.cpp")
+SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "issm_tensor_bwd.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 
@@ -23,18 +26,49 @@ def _nvcc():
     raise RuntimeError("nvcc not found (set NVCC or put it on PATH)")
 
 
+HEADER = os.path.join(PKG, "..", "include", "issm_b200.h")
+
+
 def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(PKG, "..", "include", "issm_b200.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if not f.endswith(".cpp")] + [HEADER]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def build_torch_extension(force=False, verbose=False):
+    """Compile csrc/issm_torch.cpp against the installed torch and link it to libissm_b200.so (found next to
+    it at run time through an $ORIGIN rpath).  Returns the extension's path."""
+    if (not force and os.path.exists(TORCH_LIB)
+            and all(os.path.getmtime(d) <= os.path.getmtime(TORCH_LIB) for d in (TORCH_SRC, HEADER, LIB))):
+        return TORCH_LIB
+    import torch
+    from torch.utils import cpp_extension as ce
+    cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
+    cmd = ([os.environ.get("CXX") or shutil.which("g++") or "g++", "-O2", "-std=c++17", "-fPIC", "-shared",
+            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", TORCH_SRC]
+           + [f"-I{d}" for d in ce.include_paths()] + [f"-I{os.path.join(cuda_home, 'include')}"]
+           + [f"-L{d}" for d in ce.library_paths()] + ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+              f"-L{PKG}", "-lissm_b200", "-Wl,-rpath,$ORIGIN", "-o", TORCH_LIB])
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode:
+        raise RuntimeError("g++ failed building libissm_b200_torch.so")
+    return TORCH_LIB
+
+
 def build(force=False, verbose=False):
-    """Compile every CUDA source of the package into libissm_b200.so; returns the library path.
-    The sources are compiled to objects side by side (the two tensor-core files dominate the build time),
-    then linked."""
+    """Compile every CUDA source of the package into libissm_b200.so, then the torch extension; returns the
+    path of the C-ABI library.  The CUDA sources are compiled to objects side by side (the two tensor-core
+    files dominate the build time), then linked."""
+    _build_cabi(force, verbose)
+    build_torch_extension(force, verbose)
+    return LIB
+
+
+def _build_cabi(force, verbose):
     if not force and not _stale():
         return LIB
     from concurrent.futures import ThreadPoolExecutor

@@ -92,6 +92,12 @@ static int run(const issm_params* p, void* stream, int pass) {
   const size_t need = path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(*p, pass) : simt_workspace_bytes(*p, pass);
   if (need && (!p->workspace || p->workspace_bytes < need)) return ISSM_ERR_WORKSPACE;
   if ((uintptr_t)p->workspace % 256) return ISSM_ERR_ALIGN;
+  if (path == ISSM_PATH_TENSOR) {
+    // buffers the tensor-core kernels touch with 16-byte vector or bulk accesses and that the path selection
+    // does not look at (a misaligned x / B / C / dt selects the SIMT kernels instead)
+    if ((uintptr_t)p->saved_states % 16) return ISSM_ERR_ALIGN;
+    if (pass == 1 && (((uintptr_t)p->dB | (uintptr_t)p->dC) % 16)) return ISSM_ERR_ALIGN;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   if (path == ISSM_PATH_TENSOR) return pass == 0 ? tensor_fwd(*p, s) : tensor_bwd(*p, s);
   return pass == 0 ? simt_fwd(*p, s) : simt_bwd(*p, s);

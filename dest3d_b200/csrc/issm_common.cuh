@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/issm_b200.h"
 
@@ -41,6 +42,39 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Raises the dynamic shared-memory limit of a kernel ONCE per device (the attribute is per device and per
+// function): every distinct kernel gets its own table of once-flags through the tag type.  Returns ISSM_OK
+// or ISSM_ERR_CUDA; a failure is remembered and reported by every later call on that device.
+constexpr int kMaxDevices = 64;
+template <typename Tag>
+struct SmemAttrOnce {
+  template <typename Kernel>
+  static int set(Kernel kernel, size_t bytes) {
+    static std::once_flag flags[kMaxDevices];
+    static int result[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { (void)cudaGetLastError(); return ISSM_ERR_CUDA; }
+    std::call_once(flags[dev], [&] {
+      result[dev] = ISSM_OK;
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        result[dev] = ISSM_ERR_CUDA;
+      }
+    });
+    return result[dev];
+  }
+};
+
+// largest dynamic shared-memory size a block may opt into on the current device (0 on failure)
+static inline size_t max_optin_smem() {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return (size_t)v;
 }
 
 static inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -189,13 +189,16 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
   float* dwpart = (float*)p->workspace;
   float* dbpart = dwpart + (size_t)nblk * p->hidden;
   const size_t smem = (size_t)2 * NORM_BWD_WARPS * p->hidden * sizeof(float);
-  if (p->io_dtype == ISSM_F32) {
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(k_norm_bwd<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ISSM_ERR_CUDA;
-    ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
-  } else {
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(k_norm_bwd<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ISSM_ERR_CUDA;
-    ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  struct F32Tag {};
+  struct BF16Tag {};
+  if (smem > 48 * 1024) {                                  // wide rows: opt in (once per device) to the device's limit
+    const size_t lim = max_optin_smem();
+    if (smem > lim) return ISSM_ERR_SHAPE;
+    if ((p->io_dtype == ISSM_F32 ? SmemAttrOnce<F32Tag>::set(k_norm_bwd<float>, lim) : SmemAttrOnce<BF16Tag>::set(k_norm_bwd<bf16>, lim)) != ISSM_OK)
+      return ISSM_ERR_CUDA;
   }
+  if (p->io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  else ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
   ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
   if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;

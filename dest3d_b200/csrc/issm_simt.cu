@@ -633,12 +633,11 @@ static int simt_bwd_t(const issm_params& p, cudaStream_t s) {
   {
     const int ntile = (d.N + 31) / 32;
     const size_t smem = (size_t)6 * d.Q * 32 * sizeof(float);
-    static std::atomic<size_t> configured{0};
-    if (smem > 48 * 1024 && configured.load() < smem) {
-      if (cudaFuncSetAttribute(k_main<TIO, TDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return ISSM_ERR_CUDA;
-      }
+    struct MainTag {};
+    if (smem > 48 * 1024) {                                // opt in (once per device) to the device's limit
+      const size_t lim = max_optin_smem();
+      if (smem > lim) return ISSM_ERR_SHAPE;
+      if (SmemAttrOnce<MainTag>::set(k_main<TIO, TDT>, lim) != ISSM_OK) return ISSM_ERR_CUDA;
     }
     ISSM_LAUNCH((k_main<TIO, TDT>), dim3(d.nc * ntile, d.H, d.b), 256, smem, s, d,
                 (const TIO*)p.x, p.x_sb, p.x_sl, p.x_sh, (const TIO*)p.B, p.B_sb, p.B_sl, p.B_sg,

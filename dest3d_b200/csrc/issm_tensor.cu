@@ -119,8 +119,8 @@ __device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c)
     fence_async_smem();
     fence_before_sync();
     named_barrier(11, NTH + 32);
-    if (!mbar_wait(c.barA, c.phA)) c.failed = true;
-    if (!mbar_wait(c.barA2, c.phA)) c.failed = true;
+    if (!mbar_wait_warp(c.barA, c.phA)) c.failed = true;
+    if (!mbar_wait_warp(c.barA2, c.phA)) c.failed = true;
     c.phA ^= 1;
     fence_after_sync();
     {                                              // state after the window = 2^(window decay) * accumulator
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const uint32_t parity = blk & 1;
       // ---- x rows of this block -> x operand tile [l][p] (swizzled rows); the tile is free once the last
       //      MMA of the previous block has completed ---------------------------------------------------------
-      if (blk > 0 && !a.no_output && !mbar_wait(barB, parity ^ 1)) failed = true;
+      if (blk > 0 && !a.no_output && !mbar_wait_warp(barB, parity ^ 1)) failed = true;
       uint2 xv[XG];
       int l = io_l0, gq = io_g0;
 #pragma unroll
@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int rows = min(QB, a.L - row0);
       const uint32_t parity = blk & 1;
       float alast = 0.f;
-      if (!mbar_wait(barS, parity)) failed = true;       // staged dt / B / C of this block have landed
+      if (!mbar_wait_warp(barS, parity)) failed = true;  // staged dt / B / C of this block have landed
 
       // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
       // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
@@ -522,7 +522,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int npass = kw ? (rows + ws - 1) / ws : 1;
       if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);
       if (!kWin || kw == 0) {
-        if (!mbar_wait(barA, phA)) failed = true;
+        if (!mbar_wait_warp(barA, phA)) failed = true;
         phA ^= 1;
         fence_after_sync();
       } else {
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       }
       // ---- epilogue 1b: new state = 2^(a_last) * accumulator; back to TMEM, operand and saved copies ----
       if (kw == 0) {
-        if (!mbar_wait(barA2, phA ^ 1)) failed = true;     // phA was flipped after the barA wait of this block
+        if (!mbar_wait_warp(barA2, phA ^ 1)) failed = true; // phA was flipped after the barA wait of this block
         fence_after_sync();
       }
       if (!failed && kw == 0) {
@@ -586,7 +586,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       if (a.no_output) continue;
-      if (!mbar_wait(barB, parity)) failed = true;
+      if (!mbar_wait_warp(barB, parity)) failed = true;
       fence_after_sync();
       // ---- epilogue 2: accumulator rows -> shared memory (skip, gate and store happen coalesced) ----
       if (!failed) {
@@ -607,7 +607,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   }
   const int prev_row0 = (nblk - 1) * QB, prev_rows = a.L - prev_row0;   // the block processed last
 
-  const int any_unsafe = __syncthreads_or(unsafe);
+  // a wait of the last iteration can expire after that iteration's last block-wide vote: make the verdict
+  // uniform over the block before anything below depends on it
+  const int votes = __syncthreads_or((int)unsafe | (failed ? 2 : 0));
+  const int any_unsafe = votes & 1;
+  failed = (votes & 2) != 0;
   if (!failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
   if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
   if (a.status) {
@@ -703,11 +707,11 @@ bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
 template <int NT, typename TDT, int kMode>
 static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_t s) {
   const size_t smem = FwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, false, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-      cudaFuncSetAttribute(k_fwd_tensor<NT, TDT, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-    (void)cudaGetLastError();
+  struct FastTag {};
+  struct WinTag {};
+  if (SmemAttrOnce<FastTag>::set(k_fwd_tensor<NT, TDT, false, kMode>, smem) != ISSM_OK ||
+      SmemAttrOnce<WinTag>::set(k_fwd_tensor<NT, TDT, true, 0>, smem) != ISSM_OK)
     return ISSM_ERR_CUDA;
-  }
   ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
   ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
   return ISSM_OK;

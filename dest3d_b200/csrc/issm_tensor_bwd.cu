@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       const uint32_t parity = it & 1;
       // ---- x / dy tiles and dD partials of this block; the tiles are free once the MMAs of the
       //      previous block have completed -------------------------------------------------------------------------
-      if (it > 0 && !mbar_wait(kWin ? barX : bar2b, parity ^ 1)) failed = true;
+      if (it > 0 && !mbar_wait_warp(kWin ? barX : bar2b, parity ^ 1)) failed = true;
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {                     // two passes of XG / 2 groups: 3 loads per group in flight
         uint2 xv[XG / 2], gv[XG / 2], zv[XG / 2];
@@ -521,8 +521,8 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
             if (kWin) atomicMax(sFlag, (uint32_t)(it + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
             else unsafe = 1;
           }
-          if (!mbar_wait(barT, parity)) failed = true;
-          if (!mbar_wait(barV, parity)) failed = true;
+          if (!mbar_wait_warp(barT, parity)) failed = true;
+          if (!mbar_wait_warp(barV, parity)) failed = true;
         }
         // ---- phase B: this thread's rows of Cd = C 2^a and Bd = B dt 2^-a ------------------------------------
         auto phaseB = [&](auto full) {
@@ -705,7 +705,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         float gc[HP];
         tmem_ld16(t_G, gc);
         tmem_ld8(t_G + 16, gc + 16);
-        if (!mbar_wait(barU, parity)) failed = true;
+        if (!mbar_wait_warp(barU, parity)) failed = true;
         uint4 snv[HP / 8];
 #pragma unroll
         for (int c = 0; c < HP / 8; ++c) snv[c] = *(const uint4*)(smem + SM::kSop + (half * (HP / 8) + c) * (NT * 16) + n * 16);
@@ -720,7 +720,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           }
         }
       }
-      if (kStageDt && !mbar_wait(barS, parity)) failed = true;
+      if (kStageDt && !mbar_wait_warp(barS, parity)) failed = true;
       phaseAB(0, rows, true, cpart);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
@@ -734,7 +734,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       const int npass = kw ? (rows + ws - 1) / ws : 1;
       if (kw == 0) {
         gprime();
-        if (!mbar_wait(bar1, kWin ? (c1 & 1) : parity)) failed = true;
+        if (!mbar_wait_warp(bar1, kWin ? (c1 & 1) : parity)) failed = true;
         fence_after_sync();
         if (!failed) epilogue1();
         fence_async_smem();
@@ -744,13 +744,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       // dx / dz rows of the previous block, while the second MMA phase is issued
       if (it > 0) finish_groups(std::integral_constant<int, kColGroups / NTH>{}, row0 + QB, min(QB, a.L - row0 - QB), tid, NTH);
       if (kw == 0) {
-        if (!mbar_wait(bar2, kWin ? (c2 & 1) : parity)) failed = true;
+        if (!mbar_wait_warp(bar2, kWin ? (c2 & 1) : parity)) failed = true;
         fence_after_sync();
         if (!failed) {
           epilogue_a(0, rows, true);
           asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
           named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
-          if (!mbar_wait(bar2b, kWin ? (c2 & 1) : parity)) failed = true;
+          if (!mbar_wait_warp(bar2b, kWin ? (c2 & 1) : parity)) failed = true;
           fence_after_sync();
           epilogue_b(0, rows, true);
         } else {
@@ -789,7 +789,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           phaseAB(w * ws, min(rows, w * ws + ws), false, 0.f);
           fence_before_sync();
           named_barrier(11, NTH + 32);
-          if (!mbar_wait(barW, cw & 1)) failed = true;
+          if (!mbar_wait_warp(barW, cw & 1)) failed = true;
           ++cw;
           fence_after_sync();
           tmem_ld16(t_W, sc);
@@ -836,16 +836,16 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         fence_async_smem();
         fence_before_sync();
         named_barrier(11, NTH + 32);
-        if (!mbar_wait(bar1, (c1 + k) & 1)) failed = true;
+        if (!mbar_wait_warp(bar1, (c1 + k) & 1)) failed = true;
         fence_after_sync();
         epilogue1();
         fence_async_smem();
         fence_before_sync();
         named_barrier(12, NTH + 32);
-        if (!mbar_wait(bar2, (c2 + k) & 1)) failed = true;
+        if (!mbar_wait_warp(bar2, (c2 + k) & 1)) failed = true;
         fence_after_sync();
         epilogue_a(w0, w1, false);
-        if (!mbar_wait(bar2b, (c2 + k) & 1)) failed = true;
+        if (!mbar_wait_warp(bar2b, (c2 + k) & 1)) failed = true;
         fence_after_sync();
         epilogue_b(w0, w1, false);
         fence_before_sync();
@@ -860,7 +860,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   const int prev_row0 = 0, prev_rows = min(QB, a.L);     // the block processed last
 
   // the I/O warps store the dx rows of the last processed block
-  const int any_unsafe = __syncthreads_or(unsafe);
+  // a wait of the last iteration can expire after that iteration's last block-wide vote: make the verdict
+  // uniform over the block before the barriers below run under it
+  const int votes = __syncthreads_or((int)unsafe | (failed ? 2 : 0));
+  const int any_unsafe = votes & 1;
+  failed = (votes & 2) != 0;
   if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
   if (!failed && nblk > 0) finish_rows(prev_row0, prev_rows);
   __syncthreads();
@@ -1015,11 +1019,11 @@ size_t tensor_bwd_workspace_bytes(const issm_params& p) {
 template <int NT, typename TDT, int kMode>
 static int launch_bwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_t s) {
   const size_t smem = BwdSmem<NT>::kTotal + 1024;
-  if (cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, false, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-      cudaFuncSetAttribute(k_bwd_tensor<NT, TDT, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-    (void)cudaGetLastError();
+  struct FastTag {};
+  struct WinTag {};
+  if (SmemAttrOnce<FastTag>::set(k_bwd_tensor<NT, TDT, false, kMode>, smem) != ISSM_OK ||
+      SmemAttrOnce<WinTag>::set(k_bwd_tensor<NT, TDT, true, 0>, smem) != ISSM_OK)
     return ISSM_ERR_CUDA;
-  }
   ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
   ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
   return ISSM_OK;

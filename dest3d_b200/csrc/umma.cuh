@@ -156,6 +156,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   }
   return false;
 }
+// Same wait with a warp-uniform verdict (every lane of a full warp must call it): the warp-collective
+// tcgen05.ld / tcgen05.st that follow a wait may only run under a condition all 32 lanes agree on.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, limit) ? 1 : 0) != 0;
+}
 
 // ---- bulk copy global -> shared (TMA, 1-D), completion on an mbarrier ----------------------------
 // dst, src 16-byte aligned, bytes a multiple of 16.

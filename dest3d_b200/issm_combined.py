@@ -6,6 +6,12 @@ same positional/keyword arguments, return convention and gradient dtypes, so
 `reverse=True` scans from the last point to the first without flipped copies (what
 models/dest_module.py:567-573 does with four torch.flip calls), and `path` selects the kernels
 ("auto", "simt", "tensor").
+
+Two bindings reach the C ABI.  The default is the torch C++ extension (`torch.ops.issm_b200.fwd / bwd`,
+csrc/issm_torch.cpp), which validates, allocates and fills the parameter struct in C++.  The ctypes binding of
+`_lib.py` does the same from Python; it documents how any foreign-language host binds the library and is what
+the tests use when they need to control every buffer of a call.  `BINDING` (or the environment variable
+ISSM_B200_BINDING = "torch" | "ctypes") selects one; both fail loudly when the built library is missing.
 """
 import ctypes as ct
 import math
@@ -13,15 +19,17 @@ import os
 
 import torch
 
-from . import _lib
+from . import _ext, _lib
 
+BINDING = os.environ.get("ISSM_B200_BINDING", "torch")
 _PATHS = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tensor": _lib.PATH_TENSOR}
 _STATUS = {}
 
 
 def _status_word(device):
-    """One int32 per device that kernels OR error bits into (bit 0: a bounded wait expired,
-    bit 1: a 64-point block exceeded the decay range of the tensor-core factorisation)."""
+    """One int32 per device that kernels OR error bits into (bit 0 (value 1): a bounded wait
+    expired; bit 2 (value 4), informational: a 64-point block exceeded the decay range of the fast tensor-core
+    kernel and its stream was redone by the windowed kernel)."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _STATUS:
         _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
@@ -35,6 +43,12 @@ def device_status(device=None, reset=True):
     if reset and v:
         w.zero_()
     return v
+
+
+def _empty(shape, dtype, device):
+    """Every output and workspace buffer of this module is allocated here (one place for the tests to
+    substitute an allocator that surrounds each buffer with guard bands)."""
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
 
 
 def _row_major_last(t):
@@ -111,19 +125,68 @@ def _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_s
     return p, keep
 
 
+class _StatusMirror:
+    """Pinned host copy of one device's status word.  After every call an asynchronous 4-byte copy of the word
+    is enqueued behind the call's kernels; the next call on that device (or `raise_on_device_error`) looks at the
+    copy once it has landed.  An expired device-side wait therefore surfaces as a Python exception at the first
+    call made after the failing kernels have finished, without this module ever blocking on the device."""
+
+    def __init__(self, device):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.device = device
+
+    def poll(self, what):
+        if self.pending and self.event.query():
+            self.pending = False
+            v = int(self.host[0])
+            if v & 1:
+                self.host.zero_()
+                _status_word(self.device).zero_()
+                raise RuntimeError(f"{what}: a bounded device-side wait expired in an earlier ISSM call on {self.device} "
+                                   f"(status {v}); the results of that call are invalid")
+
+    def refresh(self):
+        if torch.cuda.is_current_stream_capturing():
+            return
+        self.host.copy_(_status_word(self.device), non_blocking=True)
+        self.event.record()
+        self.pending = True
+
+
+_MIRROR = {}
+
+
 def _check_status(device, what):
-    """With ISSM_B200_CHECK_STATUS=1 every call synchronises and raises if a bounded device-side wait expired
-    (debug aid: the status word is otherwise only read by `device_status`).  Bit 2 of the word is informational:
-    some 64-point block exceeded the range of the single-reference factorisation and was redone in row windows."""
+    """Surfaces device status bit 0 (a bounded wait expired).  Default: asynchronously, see _StatusMirror.  With
+    ISSM_B200_CHECK_STATUS=1 every call synchronises and raises at once (debug aid).  Bit 2 of the word is
+    informational: some 64-point block exceeded the range of the single-reference factorisation and its stream
+    was redone by the windowed kernels."""
     if os.environ.get("ISSM_B200_CHECK_STATUS") == "1":
-        v = device_status(device)
-        if v & 1:
-            raise RuntimeError(f"{what}: a bounded device-side wait expired (status {v})")
+        raise_on_device_error(device, what)
+        return
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    m = _MIRROR.get(key)
+    if m is None:
+        m = _MIRROR[key] = _StatusMirror(torch.device("cuda", key))
+    with torch.cuda.device(key):
+        m.poll(what)
+        m.refresh()
+
+
+def raise_on_device_error(device=None, what="ISSM"):
+    """Synchronise the device and raise if any ISSM call since the last check recorded an expired wait (status
+    bit 0); the word is cleared.  Call it at a point where the training loop synchronises anyway."""
+    v = device_status(device)
+    if v & 1:
+        raise RuntimeError(f"{what}: a bounded device-side wait expired (status {v}); results are invalid")
 
 
 def _workspace(p, pass_, device, keep):
     need = _lib.lib().issm_b200_workspace_bytes(ct.byref(p), pass_)
-    ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=device)
+    ws = _empty((max(int(need), 256),), torch.uint8, device)
     keep.append(ws)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
 
@@ -134,17 +197,23 @@ def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_s
     """Forward only (no autograd).  Returns (out, out_x or None, final_states or None), plus the
     saved block-entry states (or None) when `save_states` is set; counterpart of
     `_issm_chunk_scan_combined_fwd` (issm_combined.py:57-92)."""
+    if BINDING == "torch":
+        out, out_x, final, saved = _ext.ops().fwd(
+            x, dt, A, B, C, int(chunk_size), D, z, dt_bias, initial_states, bool(dt_softplus), float(dt_limit[0]),
+            float(dt_limit[1]), bool(reverse), _PATHS[path], bool(want_final), bool(save_states), _status_word(x.device))
+        _check_status(x.device, "issm_b200_fwd")
+        out_x, final, saved = _ext.opt(out_x), _ext.opt(final), _ext.opt(saved)
+        return (out, out_x, final, saved) if save_states else (out, out_x, final)
     p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
                            dt_limit, reverse, path)
     saved = None
     if save_states and _lib.lib().issm_b200_resolve_path(ct.byref(p)) == _lib.PATH_TENSOR:
         # the tensor-core backward reads the state entering every 64-point block instead of recomputing it
-        saved = torch.empty(x.shape[0], x.shape[2], (x.shape[1] + 63) // 64 + 1, B.shape[-1], 48,
-                            dtype=torch.bfloat16, device=x.device)
+        saved = _empty((x.shape[0], x.shape[2], (x.shape[1] + 63) // 64 + 1, B.shape[-1], 48), torch.bfloat16, x.device)
         p.saved_states = saved.data_ptr()
-    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-    out_x = torch.empty_like(out) if z is not None else None
-    final = torch.empty(x.shape[0], x.shape[2], x.shape[3], B.shape[-1], dtype=torch.float32, device=x.device) if want_final else None
+    out = _empty(x.shape, x.dtype, x.device)
+    out_x = _empty(x.shape, x.dtype, x.device) if z is not None else None
+    final = _empty((x.shape[0], x.shape[2], x.shape[3], B.shape[-1]), torch.float32, x.device) if want_final else None
     p.out, p.out_sb, p.out_sl, p.out_sh = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
     p.out_x, p.final_states, p.want_final = _lib.ptr(out_x), _lib.ptr(final), int(want_final)
     _workspace(p, 0, x.device, keep)
@@ -163,6 +232,13 @@ def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=No
     `out_x` is the pre-gate output saved by the forward (only read when z is given).
     Returns (dx, ddt, dA, dB, dC, dD, dz, ddt_bias, dinitial_states) with the reference's dtypes;
     dA / dD / ddt_bias are float32 here and cast by the caller."""
+    if BINDING == "torch":
+        res = _ext.ops().bwd(dout, x, dt, A, B, C, out_x, int(chunk_size), D, z, dt_bias, initial_states, dfinal_states,
+                             bool(dt_softplus), float(dt_limit[0]), float(dt_limit[1]), bool(reverse), _PATHS[path],
+                             saved_states, _status_word(x.device))
+        _check_status(x.device, "issm_b200_bwd")
+        dx, ddt, dA, dB, dC, dD, dz, dbias, dinit = res
+        return dx, ddt, dA, dB, dC, _ext.opt(dD), _ext.opt(dz), _ext.opt(dbias), _ext.opt(dinit)
     p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
                            dt_limit, reverse, path)
     dev = x.device
@@ -170,15 +246,15 @@ def issm_bwd(dout, x, dt, A, B, C, out_x, chunk_size, D=None, z=None, dt_bias=No
     doutk = _row_major_last(dout if dout.dtype == io else dout.to(io))
     keep.append(doutk)
     H, N = A.shape
-    dx = torch.empty(x.shape, dtype=io, device=dev)
-    ddt = torch.empty(dt.shape, dtype=torch.float32 if p.dt_dtype == _lib.F32 else torch.bfloat16, device=dev)
-    dB = torch.empty(B.shape, dtype=io, device=dev)
-    dC = torch.empty(C.shape, dtype=io, device=dev)
-    dz = torch.empty(x.shape, dtype=io, device=dev) if z is not None else None
-    dA = torch.empty(H, N, dtype=torch.float32, device=dev)
-    dbias = torch.empty(H, N, dtype=torch.float32, device=dev) if dt_bias is not None else None
-    dD = torch.empty(D.shape, dtype=torch.float32, device=dev) if D is not None else None
-    dinit = torch.empty(initial_states.shape, dtype=io, device=dev) if initial_states is not None else None
+    dx = _empty(x.shape, io, dev)
+    ddt = _empty(dt.shape, torch.float32 if p.dt_dtype == _lib.F32 else torch.bfloat16, dev)
+    dB = _empty(B.shape, io, dev)
+    dC = _empty(C.shape, io, dev)
+    dz = _empty(x.shape, io, dev) if z is not None else None
+    dA = _empty((H, N), torch.float32, dev)
+    dbias = _empty((H, N), torch.float32, dev) if dt_bias is not None else None
+    dD = _empty(D.shape, torch.float32, dev) if D is not None else None
+    dinit = _empty(initial_states.shape, io, dev) if initial_states is not None else None
     if z is not None:
         # out_x was allocated contiguous by the forward
         assert out_x is not None and out_x.is_contiguous()

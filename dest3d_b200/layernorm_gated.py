@@ -1,11 +1,13 @@
 """Gated RMSNorm / LayerNorm with the reference's interface (issm_triton/layernorm_gated.py:328-427)
-on top of the B200 C ABI: `RMSNorm`, `LayerNorm`, `rmsnorm_fn`, `layernorm_fn`, `LayerNormFn`.
+on top of the B200 C ABI: `RMSNorm`, `LayerNorm`, `rmsnorm_fn`, `layernorm_fn`, `LayerNormFn`.  As for the scan,
+the default binding is the torch C++ extension (`torch.ops.issm_b200.norm_fwd / norm_bwd`); with
+`issm_combined.BINDING == "ctypes"` the calls go through the ctypes binding instead.
 """
 import ctypes as ct
 
 import torch
 
-from . import _lib
+from . import _ext, _lib, issm_combined
 
 
 def _norm_params(x2, z2, weight, bias, eps, group_size, norm_before_gate, is_rms_norm):
@@ -47,6 +49,15 @@ class LayerNormFn(torch.autograd.Function):
                 z2 = z2.contiguous()
         wf = weight.detach().float().contiguous()
         bf = bias.detach().float().contiguous() if bias is not None else None
+        if issm_combined.BINDING == "torch":
+            y, rstd, mean = _ext.ops().norm_fwd(x2, z2, wf, bf, float(eps), int(group_size or 0), bool(norm_before_gate),
+                                                bool(is_rms_norm))
+            mean = _ext.opt(mean)
+            ctx.save_for_backward(x2, weight, bias, mean, rstd, z2)
+            ctx.x_shape_og, ctx.eps, ctx.group_size = x_shape_og, eps, group_size
+            ctx.norm_before_gate, ctx.is_rms_norm = norm_before_gate, is_rms_norm
+            ctx.z_dtype = None if z is None else z.dtype
+            return y.reshape(x_shape_og)
         p = _norm_params(x2, z2, wf, bf, eps, group_size, norm_before_gate, is_rms_norm)
         ng = p.hidden // p.group_size
         y = torch.empty(x2.shape, dtype=x2.dtype, device=x2.device)
@@ -77,6 +88,16 @@ class LayerNormFn(torch.autograd.Function):
         assert dy2.shape == x2.shape
         wf = weight.detach().float().contiguous()
         bf = bias.detach().float().contiguous() if bias is not None else None
+        if issm_combined.BINDING == "torch":
+            dx, dz, dw, db = _ext.ops().norm_bwd(dy2, x2, z2, wf, bf, rstd, mean, float(ctx.eps), int(ctx.group_size or 0),
+                                                 bool(ctx.norm_before_gate), bool(ctx.is_rms_norm))
+            dzo = None
+            if z2 is not None:
+                dzo = dz.reshape(ctx.x_shape_og)
+                if dzo.dtype != ctx.z_dtype:
+                    dzo = dzo.to(ctx.z_dtype)
+            return (dx.reshape(ctx.x_shape_og), dw.to(weight.dtype), db.to(bias.dtype) if bias is not None else None,
+                    dzo, None, None, None, None)
         p = _norm_params(x2, z2, wf, bf, ctx.eps, ctx.group_size, ctx.norm_before_gate, ctx.is_rms_norm)
         dev = x2.device
         dx = torch.empty(x2.shape, dtype=x2.dtype, device=dev)

@@ -137,7 +137,13 @@ size_t issm_b200_sizeof_params(void);
 size_t issm_b200_sizeof_norm_params(void);
 
 /* Bytes of workspace issm_b200_fwd (pass = 0) or issm_b200_bwd (pass = 1) needs for these
- * sizes, dtypes, flags and path; pointers in *p are ignored.  Returns 0 on invalid sizes. */
+ * sizes, dtypes, flags and path.  Returns 0 on invalid sizes.  No pointer is dereferenced, but
+ * two properties of the pointers select the kernels and with them the size, so they must be the
+ * same in this query and in the call that follows: the alignment of x, z, out, out_x, dout, dx, dz
+ * (8 bytes) and of B, C, bf16 dt (16 bytes) decides between the tensor-core and the SIMT kernels
+ * under ISSM_PATH_AUTO (null pointers count as aligned), and a backward without `saved_states`
+ * needs room to recompute them.  A query made with null pointers therefore sizes the workspace of
+ * an aligned call that passes saved_states iff it is non-null in the query. */
 size_t issm_b200_workspace_bytes(const issm_params* p, int pass);
 
 /* Which path (ISSM_PATH_SIMT or ISSM_PATH_TENSOR) a call with these sizes would take. */
@@ -159,7 +165,10 @@ int issm_b200_norm_bwd(const issm_norm_params* p, void* cuda_stream);
  *   - Limit: hidden <= 1024; a wider row returns ISSM_ERR_LIMIT and launches nothing.
  *   - Neither this call nor anything it uses allocates or frees device memory.
  *   - The first call on each device looks up the array's device address (the device of the call
- *     must be current); make that first call outside any stream capture.
+ *     must be current) and, with lazy module loading, is also what makes the driver load the
+ *     library's device code, array included: make that first (warm-up) call at start-up, outside
+ *     any stream capture.  The address is cached for the life of the process; a cudaDeviceReset of
+ *     that device invalidates it (do not reset a device and then call this entry point again).
  *   - All calls on a device share the one array, which keeps whatever the previous call left in
  *     it (each call overwrites all it reads).  Two calls whose kernels overlap in time on the same
  *     GPU - different streams, or different host threads - race on it: serialise them. */
@@ -168,15 +177,6 @@ int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* cuda_stream);
 /* Number of kernel launches the library has enqueued since load (monotonic, process-wide);
  * used by the benchmark to report how many of its own kernels ran inside a timed region. */
 uint64_t issm_b200_launch_count(void);
-
-/* Hardware self-check of the tensor-core building blocks (no counterpart in the reference):
- * one CTA computes D (M x N, float) = A (M x K, bf16) * B (N x K, bf16)^T with tcgen05.mma through
- * the same shared-memory layouts and descriptors as the ISSM tensor path.  M is 64 or 128; N and K
- * multiples of 16; kind 0 = 128-byte swizzle K-major, 1 = interleaved core matrices, 2 = 128-byte
- * swizzle MN-major.  Draw (128 x N)
- * receives the raw TMEM lanes.  status (device int, optional) is set to 1 if the wait expired. */
-int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
-                            float* D, float* Draw, int32_t* status, void* cuda_stream);
 
 #ifdef __cplusplus
 }

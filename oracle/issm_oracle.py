@@ -104,9 +104,15 @@ def _segsum(v: torch.Tensor) -> torch.Tensor:
     return d.masked_fill(~keep, -float("inf"))
 
 
+def _round_through(t: torch.Tensor, dtype) -> torch.Tensor:
+    """Value rounded to `dtype`, gradient passed straight through (how a kernel that evaluates an
+    analytic gradient formula on rounded operands behaves)."""
+    return t + (t.detach().to(dtype).to(t.dtype) - t.detach())
+
+
 def issm_scan_chunked(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None,
                       initial_states=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
-                      reverse=False, compute_dtype=torch.float32):
+                      reverse=False, compute_dtype=torch.float32, operand_rounding=None):
     """Chunked ISSM scan.  Same argument meaning as ISSM_chunk_scan_combined
     (issm_triton/issm_combined.py:16-35) plus `reverse` (scan from the last point to the first;
     equal to flipping x, dt, B, C, z along L, scanning, and flipping the output back, which is
@@ -114,11 +120,17 @@ def issm_scan_chunked(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None,
 
     Returns (out (b, L, H, P) in x.dtype, final_states (b, H, P, N) float32 [compute dtype if
     float64]).  Differentiable with torch autograd.
+
+    `operand_rounding=torch.bfloat16` emulates what the reference's Triton kernels do to the intra-chunk
+    term when B or C is bfloat16: the cumulative decay `a`, dt, B and C are all cast to the dot dtype before
+    exp(a[l] - a[s]) * B * dt * C is formed (issm_triton/issm_cabt_bmm.py:40-43,124-136).  Only used by the
+    tests that put this library's rounding error next to the reference's own.
     """
     if reverse:
         flip = lambda t: None if t is None else torch.flip(t, dims=[1])
         out, fin = issm_scan_chunked(flip(x), flip(dt), A, flip(B), flip(C), chunk_size, D, flip(z),
-                                     dt_bias, initial_states, dt_softplus, dt_limit, False, compute_dtype)
+                                     dt_bias, initial_states, dt_softplus, dt_limit, False, compute_dtype,
+                                     operand_rounding)
         return torch.flip(out, dims=[1]), fin
     b, L, H, P = x.shape
     N = B.shape[-1]
@@ -145,9 +157,16 @@ def issm_scan_chunked(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None,
     # (b, H, N, nc, Q, Q) tensor in one go, test_issm.py:40)
     y_diag = []
     for h in range(H):
-        seg = _segsum(dA[:, :, :, h].permute(0, 1, 3, 2))          # (b, nc, N, Q, Q)
-        Lmat = torch.exp(seg)
-        cabt = torch.einsum("bcln,bcsn,bcnls,bcsn->bcls", Cc[:, :, :, h], Bc[:, :, :, h], Lmat, dtc[:, :, :, h])
+        if operand_rounding is None:
+            seg = _segsum(dA[:, :, :, h].permute(0, 1, 3, 2))      # (b, nc, N, Q, Q)
+            Lmat = torch.exp(seg)
+            cabt = torch.einsum("bcln,bcsn,bcnls,bcsn->bcls", Cc[:, :, :, h], Bc[:, :, :, h], Lmat, dtc[:, :, :, h])
+        else:
+            rt = lambda t: _round_through(t, operand_rounding)
+            ar = rt(a[:, :, :, h]).permute(0, 1, 3, 2)             # (b, nc, N, Q): the rounded cumulative decay
+            keep = torch.tril(torch.ones(Q, Q, dtype=torch.bool))
+            Lmat = rt(torch.exp((ar[..., :, None] - ar[..., None, :]).masked_fill(~keep, -float("inf"))))
+            cabt = torch.einsum("bcln,bcsn,bcnls,bcsn->bcls", rt(Cc[:, :, :, h]), rt(Bc[:, :, :, h]), Lmat, rt(dtc[:, :, :, h]))
         y_diag.append(torch.einsum("bcls,bcsp->bclp", cabt, xc[:, :, :, h]))
     y = torch.stack(y_diag, dim=3)                        # (b, nc, Q, H, P)
 

@@ -1,6 +1,6 @@
 """Pins oracle/issm_oracle.py against the reference's own pure-PyTorch code.
 
-Run in a container that has the reference checkout:  python oracle/validate_against_reference.py [REF_DIR]
+Run in a container that has the reference checkout:  python oracle/validate_against_reference.py REF_DIR
 It imports `ISSM_minimal_discrete` (test_issm.py:18-67) and `rms_norm_ref`
 (issm_triton/layernorm_gated.py:8-29) UNMODIFIED and compares outputs and autograd gradients
 with the restatement on seeded inputs.  Exit code 0 = every check passed.
@@ -30,7 +30,10 @@ def check(name, a, b, rtol, atol):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python oracle/validate_against_reference.py REF_DIR   (a checkout of the reference, "
+                         "or the copy made by oracle/install_reference.py under baseline/_ref)")
+    ref_dir = sys.argv[1]
     ref_scan, ref_norm = load_reference(ref_dir)
     ok = True
     for dtype, rtol, atol in ((torch.float64, 1e-10, 1e-12), (torch.float32, 1e-4, 1e-5)):

@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory from the REFERENCE's own pure-PyTorch code.
 
-    python tests/golden/make_golden.py [REF_DIR]      (REF_DIR defaults to /root/reference)
+    python tests/golden/make_golden.py REF_DIR      (a checkout of the reference)
 
 `ISSM_minimal_discrete` (test_issm.py:18-67) and `rms_norm_ref`
 (issm_triton/layernorm_gated.py:8-29) are imported unmodified; nothing from this repository
@@ -42,7 +42,9 @@ def case_inputs(b, L, H, P, N, seed, dtype):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py REF_DIR   (a checkout of the reference)")
+    ref_dir = sys.argv[1]
     sys.path.insert(0, ref_dir)
     from test_issm import ISSM_minimal_discrete
     from issm_triton.layernorm_gated import rms_norm_ref

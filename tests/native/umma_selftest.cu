@@ -1,8 +1,19 @@
-// Self-check of the tcgen05 building blocks (operand layouts, descriptors, TMEM row mapping):
-// one CTA computes D = A * B^T for small bf16 matrices through exactly the helpers the ISSM
-// tensor path uses.  The result is compared with a plain matmul by the test-suite.
-#include "issm_common.cuh"
-#include "umma.cuh"
+// TEST-ONLY native code (built into tests/native/libissm_b200_selftest.so, never into the product library).
+//
+// 1. Self-check of the tcgen05 building blocks (operand layouts, descriptors, TMEM row mapping): one CTA
+//    computes D = A * B^T for small bf16 matrices through exactly the helpers the ISSM tensor path uses
+//    (dest3d_b200/csrc/umma.cuh).  The result is compared with a plain matmul by the test-suite.
+//      M is 64 or 128; N and K multiples of 16; kind 0 = 128-byte swizzle K-major, 1 = interleaved core
+//      matrices, 2 = 128-byte swizzle MN-major.  Draw (128 x N) receives the raw TMEM lanes.
+// 2. The bounded wait: a kernel that waits, with a short poll limit, on an mbarrier nobody ever arrives on.
+//    The wait runs out by construction (no fault, no trap, no endless loop); the kernel then records bit 0 in
+//    the status word exactly as the ISSM kernels do and returns.
+#include <cuda_runtime.h>
+
+#include "../../dest3d_b200/csrc/umma.cuh"
+
+typedef __nv_bfloat16 bf16;
+enum { ST_OK = 0, ST_ERR_SHAPE = 2, ST_ERR_CUDA = 7 };
 
 namespace issm {
 using namespace umma;
@@ -84,17 +95,36 @@ using namespace issm;
 
 extern "C" int issm_b200_selftest_umma(int M, int N, int K, int kindA, int kindB, const void* A, const void* B,
                                        float* D, float* Draw, int32_t* status, void* stream) {
-  if ((M != 64 && M != 128) || N < 16 || N > 256 || N % 16 || K < 16 || K % 16 || !A || !B || !D || !Draw) return ISSM_ERR_SHAPE;
+  if ((M != 64 && M != 128) || N < 16 || N > 256 || N % 16 || K < 16 || K % 16 || !A || !B || !D || !Draw) return ST_ERR_SHAPE;
   auto bytes = [](int kind, int rows, int K) -> size_t {
     if (kind == 0) return (size_t)rows * ((K + 63) / 64) * 128;
     if (kind == 2) return (size_t)K * ((rows + 63) / 64) * 128;
     return (size_t)rows * K * 2;
   };
-  if (kindA < 0 || kindA > 2 || kindB < 0 || kindB > 2) return ISSM_ERR_SHAPE;
+  if (kindA < 0 || kindA > 2 || kindB < 0 || kindB > 2) return ST_ERR_SHAPE;
   const size_t bytesA = bytes(kindA, M, K), bytesB = bytes(kindB, N, K);
   const size_t smem = ((bytesA + 1023) & ~(size_t)1023) + bytesB + 2048;
-  if (smem > 200 * 1024) return ISSM_ERR_SHAPE;
-  if (cudaFuncSetAttribute(k_umma_selftest, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ISSM_ERR_CUDA;
-  ISSM_LAUNCH(k_umma_selftest, 1, 128, smem, (cudaStream_t)stream, M, N, K, kindA, kindB, (const bf16*)A, (const bf16*)B, D, Draw, status);
-  return ISSM_OK;
+  if (smem > 200 * 1024) return ST_ERR_SHAPE;
+  if (cudaFuncSetAttribute(k_umma_selftest, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ST_ERR_CUDA;
+  k_umma_selftest<<<1, 128, smem, (cudaStream_t)stream>>>(M, N, K, kindA, kindB, (const bf16*)A, (const bf16*)B, D, Draw, status);
+  return cudaPeekAtLastError() == cudaSuccess ? ST_OK : ST_ERR_CUDA;
+}
+
+namespace issm {
+// Every thread of the block polls an mbarrier that has one pending arrival which never comes, at most
+// `limit` times; the expiry is reported like in the ISSM kernels (status bit 0) and the kernel returns.
+__global__ void k_bounded_wait(uint32_t limit, int* status, int* polled_out) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  __syncthreads();
+  const bool ok = mbar_wait_warp(&bar, 0, limit);
+  if (!ok && threadIdx.x == 0) atomicOr(status, 1);
+  if (threadIdx.x == 0) *polled_out = ok ? 0 : 1;
+}
+}  // namespace issm
+
+extern "C" int issm_b200_selftest_bounded_wait(uint32_t limit, int32_t* status, int32_t* expired, void* stream) {
+  if (!status || !expired || limit == 0 || limit > (1u << 16)) return ST_ERR_SHAPE;
+  issm::k_bounded_wait<<<2, 64, 0, (cudaStream_t)stream>>>(limit, status, expired);
+  return cudaPeekAtLastError() == cudaSuccess ? ST_OK : ST_ERR_CUDA;
 }

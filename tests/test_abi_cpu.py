@@ -78,6 +78,34 @@ def test_workspace_too_small_is_reported(built_lib):
     assert L.issm_b200_fwd(C.byref(p), None) == 4                             # ISSM_ERR_WORKSPACE
 
 
+def test_misaligned_tensor_path_buffers_are_reported(built_lib):
+    """saved_states, dB and dC of the tensor-core path are accessed 16 bytes at a time; a caller that passes a
+    sub-view at an 8-byte offset gets ISSM_ERR_ALIGN before anything is launched (dummy pointers, no device)."""
+    from dest3d_b200 import _lib
+    L = built_lib
+    p = _params(io_dtype=_lib.BF16, dt_dtype=_lib.BF16, path=_lib.PATH_TENSOR, dstate=256, chunk_size=256)
+    p.x_sb, p.x_sl, p.x_sh = 100 * 4 * 36, 4 * 36, 36
+    p.out_sb, p.out_sl, p.out_sh = p.x_sb, p.x_sl, p.x_sh
+    p.dout_sb, p.dout_sl, p.dout_sh = p.x_sb, p.x_sl, p.x_sh
+    p.dt_sb, p.dt_sl, p.dt_sh = 100 * 4 * 256, 4 * 256, 256
+    p.B_sb, p.B_sl, p.B_sg = 100 * 256, 256, 256
+    p.C_sb, p.C_sl, p.C_sg = 100 * 256, 256, 256
+    for f in ("x", "dt", "A", "B", "C", "out", "dout", "dx", "ddt", "dB", "dC", "dA"):
+        setattr(p, f, 4096)
+    assert L.issm_b200_resolve_path(C.byref(p)) == _lib.PATH_TENSOR
+    need = L.issm_b200_workspace_bytes(C.byref(p), 1)
+    assert need > 0
+    p.workspace, p.workspace_bytes = 1 << 20, need
+    p.saved_states = 4096 + 8
+    assert L.issm_b200_fwd(C.byref(p), None) == 5                             # ISSM_ERR_ALIGN
+    assert L.issm_b200_bwd(C.byref(p), None) == 5
+    p.saved_states = 4096
+    p.dB = 4096 + 8
+    assert L.issm_b200_bwd(C.byref(p), None) == 5
+    p.dB, p.dC = 4096, 4096 + 2
+    assert L.issm_b200_bwd(C.byref(p), None) == 5
+
+
 def test_norm_validation(built_lib):
     from dest3d_b200 import _lib
     p = _lib.IssmNormParams()

@@ -162,28 +162,45 @@ def test_golden_reference_vectors(name):
         parity.close(got, ref, torch.float32, "d" + k)
 
 
-def test_deterministic_bitwise():
-    """Two runs on the same inputs give bit-identical outputs and gradients (no atomics)."""
-    inp, Q = _inputs((2, 300, 4, 36, 64, 1, 64), {}, BENCH_OPTS, torch.float32)
-    a = parity.cuda_run(inp, Q, BENCH_OPTS, path="simt")
-    b = parity.cuda_run(inp, Q, BENCH_OPTS, path="simt")
+PATH_CASES = [("simt", torch.float32, (2, 300, 4, 36, 64, 1, 64)), ("tensor", torch.bfloat16, (2, 300, 4, 36, 256, 1, 256))]
+
+
+@pytest.mark.parametrize("path,dtype,shape", PATH_CASES, ids=["simt", "tensor"])
+def test_deterministic_bitwise(path, dtype, shape):
+    """Two runs on the same inputs give bit-identical outputs and gradients (no atomics, fixed-order sums)."""
+    inp, Q = _inputs(shape, {}, BENCH_OPTS, dtype)
+    a = parity.cuda_run(inp, Q, BENCH_OPTS, path=path)
+    b = parity.cuda_run(inp, Q, BENCH_OPTS, path=path)
     for k in a:
         if a[k] is not None:
             assert torch.equal(a[k], b[k]), k
 
 
-def test_reverse_equals_flip():
-    """reverse=True equals flip -> scan -> flip (models/dest_module.py:567-573), bit for bit."""
+@pytest.mark.parametrize("path,dtype,shape", PATH_CASES, ids=["simt", "tensor"])
+def test_reverse_equals_flip(path, dtype, shape):
+    """reverse=True equals flip -> scan -> flip (models/dest_module.py:567-573), bit for bit, outputs and
+    gradients."""
     from dest3d_b200 import ISSM_chunk_scan_combined
-    inp, Q = _inputs((2, 200, 2, 36, 64, 1, 64), {}, BENCH_OPTS, torch.float32)
+    inp, Q = _inputs(shape, {}, BENCH_OPTS, dtype)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
     fl = lambda t: torch.flip(t, dims=[1]).contiguous()
-    kw = dict(D=c["D"], z=c["z"], dt_bias=c["dt_bias"], initial_states=c["initial_states"], dt_softplus=True,
-              dt_limit=(1e-3, 1e-1), return_final_states=True, path="simt")
-    y1, f1 = ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, reverse=True, **kw)
-    kw["z"] = fl(c["z"])
-    y2, f2 = ISSM_chunk_scan_combined(fl(c["x"]), fl(c["dt"]), c["A"], fl(c["B"]), fl(c["C"]), Q, **kw)
-    assert torch.equal(y1, torch.flip(y2, dims=[1])) and torch.equal(f1, f2)
+    seq = ("x", "dt", "B", "C", "z")
+
+    def run(flipped):
+        t = {k: (fl(c[k]) if flipped and k in seq else c[k].clone()).requires_grad_() for k in seq + ("initial_states",)}
+        y, f = ISSM_chunk_scan_combined(t["x"], t["dt"], c["A"], t["B"], t["C"], Q, D=c["D"], z=t["z"], dt_bias=c["dt_bias"],
+                                        initial_states=t["initial_states"], dt_softplus=True, dt_limit=(1e-3, 1e-1),
+                                        return_final_states=True, reverse=not flipped, path=path)
+        dout = fl(c["dout"]) if flipped else c["dout"]
+        ((y.float() * dout.float()).sum() + (f * c["dfinal"]).sum()).backward()
+        unflip = (lambda v: torch.flip(v, dims=[1])) if flipped else (lambda v: v)
+        return unflip(y.detach()), f.detach(), {k: (unflip(v.grad) if k in seq else v.grad) for k, v in t.items()}
+
+    y1, f1, g1 = run(False)
+    y2, f2, g2 = run(True)
+    assert torch.equal(y1, y2) and torch.equal(f1, f2)
+    for k in g1:
+        assert torch.equal(g1[k], g2[k]), k
 
 
 def test_bad_arguments_raise():

@@ -1,10 +1,18 @@
-"""tcgen05 building blocks (operand layouts, descriptors, TMEM row mapping) against torch.matmul."""
+"""tcgen05 building blocks (operand layouts, descriptors, TMEM row mapping) against torch.matmul, and the
+bounded device-side wait; both through the test-only native library of tests/native."""
 import ctypes as ct
+import os
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+
+def selftest_lib():
+    from tests.native import build
+    path = build.LIB if os.path.exists(build.LIB) else build.build()
+    return ct.CDLL(path)
 
 CONFIGS = [
     # M, N, K, kindA, kindB   (kind 0 = 128-byte swizzle K-major, 1 = interleaved core matrices)
@@ -19,8 +27,7 @@ CONFIGS = [
 
 @pytest.mark.parametrize("cfg", CONFIGS, ids=[f"M{c[0]}N{c[1]}K{c[2]}a{c[3]}b{c[4]}" for c in CONFIGS])
 def test_umma_matches_matmul(cfg):
-    from dest3d_b200 import _lib
-    L = _lib.lib()
+    L = selftest_lib()
     M, N, K, ka, kb = cfg
     g = torch.Generator().manual_seed(M + N + K)
     A = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
@@ -46,3 +53,29 @@ def test_umma_matches_matmul(cfg):
             hits.append((lane, r, float(d[r])))
         print("lane -> best matching row (err):", [(l, r, round(e, 3)) for l, r, e in hits if e < 1e-2][:40])
     assert err < 1e-2, f"max abs err {err}"
+
+
+def test_bounded_wait_runs_out_and_the_device_stays_usable():
+    """A wait on a barrier that nobody signals gives up after its poll limit: the kernel returns, bit 0 of the
+    status word is set (what the ISSM kernels do when a copy or an MMA never completes), the Python layer turns
+    that bit into an exception, and the next ordinary call on the same device is correct."""
+    from dest3d_b200 import issm_combined
+    from oracle import issm_oracle as O
+    from tests import parity
+    L = selftest_lib()
+    L.issm_b200_selftest_bounded_wait.restype = ct.c_int
+    issm_combined.device_status()                                   # clear
+    word = issm_combined._status_word(torch.cuda.current_device())
+    expired = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = L.issm_b200_selftest_bounded_wait(ct.c_uint32(1000), ct.c_void_p(word.data_ptr()), ct.c_void_p(expired.data_ptr()),
+                                           ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert expired.item() == 1
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        issm_combined.raise_on_device_error()
+    assert issm_combined.device_status() == 0                       # the exception cleared the word
+    inp = O.make_inputs(1, 200, 2, 36, 256, seed=9, dtype=torch.bfloat16)
+    opts = dict(dt_softplus=True, dt_limit=(1e-3, 1e-1))
+    parity.compare(parity.cuda_run(inp, 256, opts, path="tensor"), parity.oracle_run(inp, 256, opts), torch.bfloat16)
+    assert issm_combined.device_status() == 0
