@@ -78,6 +78,8 @@ def lib():
     L.issm_b200_workspace_bytes.argtypes = [C.POINTER(IssmParams), C.c_int]
     L.issm_b200_resolve_path.restype = C.c_int
     L.issm_b200_resolve_path.argtypes = [C.POINTER(IssmParams)]
+    L.issm_b200_resolve_path_pass.restype = C.c_int
+    L.issm_b200_resolve_path_pass.argtypes = [C.POINTER(IssmParams), C.c_int]
     for name in ("issm_b200_fwd", "issm_b200_bwd"):
         getattr(L, name).restype = C.c_int
         getattr(L, name).argtypes = [C.POINTER(IssmParams), vp]

@@ -46,7 +46,9 @@ def build_torch_extension(force=False, verbose=False):
     import torch
     from torch.utils import cpp_extension as ce
     cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
-    cmd = ([os.environ.get("CXX") or shutil.which("g++") or "g++", "-O2", "-std=c++17", "-fPIC", "-shared",
+    # the host compiler nvcc itself uses (g++ on PATH), so that the extension shares the process-wide libstdc++ with
+    # torch: a compiler that links its own C++ runtime statically breaks exceptions thrown across the libraries
+    cmd = ([os.environ.get("ISSM_B200_CXX") or shutil.which("g++") or "g++", "-O2", "-std=c++17", "-fPIC", "-shared",
             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", TORCH_SRC]
            + [f"-I{d}" for d in ce.include_paths()] + [f"-I{os.path.join(cuda_home, 'include')}"]
            + [f"-L{d}" for d in ce.library_paths()] + ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
@@ -56,6 +58,11 @@ def build_torch_extension(force=False, verbose=False):
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode:
         raise RuntimeError("g++ failed building libissm_b200_torch.so")
+    needed = subprocess.run(["readelf", "-d", TORCH_LIB], capture_output=True, text=True).stdout
+    if needed and "libstdc++" not in needed:
+        os.remove(TORCH_LIB)
+        raise RuntimeError("libissm_b200_torch.so was linked without the shared libstdc++ (static C++ runtime): "
+                           "point ISSM_B200_CXX at the system g++")
     return TORCH_LIB
 
 

@@ -38,9 +38,9 @@ static int validate_ptrs(const issm_params* p, int pass) {
   return ISSM_OK;
 }
 
-static int resolve(const issm_params& p) {
+static int resolve(const issm_params& p, int pass) {
   if (p.path == ISSM_PATH_SIMT) return ISSM_PATH_SIMT;
-  const bool ok = tensor_path_supported(p);
+  const bool ok = tensor_path_supported(p, pass);
   if (p.path == ISSM_PATH_TENSOR) return ok ? ISSM_PATH_TENSOR : -1;
   return ok ? ISSM_PATH_TENSOR : ISSM_PATH_SIMT;
 }
@@ -72,12 +72,16 @@ extern "C" uint64_t issm_b200_launch_count(void) { return g_launches.load(); }
 
 extern "C" int issm_b200_resolve_path(const issm_params* p) {
   if (validate(p, 0)) return -1;
-  return resolve(*p);
+  return resolve(*p, 0);
+}
+extern "C" int issm_b200_resolve_path_pass(const issm_params* p, int pass) {
+  if (validate(p, pass) || (pass != 0 && pass != 1)) return -1;
+  return resolve(*p, pass);
 }
 
 extern "C" size_t issm_b200_workspace_bytes(const issm_params* p, int pass) {
   if (validate(p, pass) || (pass != 0 && pass != 1)) return 0;
-  const int path = resolve(*p);
+  const int path = resolve(*p, pass);
   if (path < 0) return 0;
   return path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(*p, pass) : simt_workspace_bytes(*p, pass);
 }
@@ -87,7 +91,7 @@ static int run(const issm_params* p, void* stream, int pass) {
   if (rc) return rc;
   rc = validate_ptrs(p, pass);
   if (rc) return rc;
-  const int path = resolve(*p);
+  const int path = resolve(*p, pass);
   if (path < 0) return ISSM_ERR_UNSUPPORTED;
   const size_t need = path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(*p, pass) : simt_workspace_bytes(*p, pass);
   if (need && (!p->workspace || p->workspace_bytes < need)) return ISSM_ERR_WORKSPACE;

@@ -98,7 +98,7 @@ size_t simt_workspace_bytes(const issm_params& p, int pass);
 int simt_fwd(const issm_params& p, cudaStream_t s);
 int simt_bwd(const issm_params& p, cudaStream_t s);
 
-bool tensor_path_supported(const issm_params& p);
+bool tensor_path_supported(const issm_params& p, int pass);
 size_t tensor_workspace_bytes(const issm_params& p, int pass);
 int tensor_fwd(const issm_params& p, cudaStream_t s);
 int tensor_bwd(const issm_params& p, cudaStream_t s);

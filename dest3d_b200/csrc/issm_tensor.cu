@@ -18,6 +18,10 @@
 // windows only the decay itself is floored, at 2^-100), and bit 2 of the status word records that it happened.
 // dt (bf16), B and C rows of the next block are prefetched into shared memory by bulk (TMA) copies
 // while the current block computes.
+// More than 256 states (dstate 512, 768, 1024): the scan is a sum over the states, so every slice of 256 states is
+// an independent scan over the same x with its own columns of dt, A, B, C and of the state; blockIdx.x is the
+// slice, each slice writes its pre-skip / pre-gate output rows as floats, and k_combine_slices adds the slices
+// and applies the D skip and the silu(z) gate.
 #include "issm_tensor.cuh"
 
 #include <cstring>
@@ -36,8 +40,8 @@ struct FwdSmem {
   static constexpr int kSB = kSdt + QB * NT * 2;
   static constexpr int kSC = kSB + QB * NT * 2;
   static constexpr int kY = kSC + QB * NT * 2;          // [64][PP] float: pre-skip, pre-gate output rows
-  static constexpr int kAsum = kY + QB * PP * 4;        // [2][NT] float: per-half sums of dt*A
-  static constexpr int kBars = kAsum + 2 * NT * 4;
+  static constexpr int kAsum = kY + QB * PP * 4;        // [4][NT] float: sums of dt*A over the four 16-row quarters of a block
+  static constexpr int kBars = kAsum + 4 * NT * 4;      //   (the windowed instantiation keeps per-half sums in the first two rows)
   static constexpr int kTotal = kBars + 64;
 };
 
@@ -187,15 +191,22 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   const bool is_io = tid >= NTH + 32;
   const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
-  if (kWin && !a.redo[b * a.H + h]) return;              // the fast kernel finished this stream
+  const int n_off = blockIdx.x * NT;                     // first state of this CTA's slice
+  const int stream = (blockIdx.x * a.b + b) * a.H + h;
+  if (kWin && !a.redo[stream]) return;                   // the fast kernel finished this stream
   const int n = tid % NT, half = (tid / NT) & 1;
-  const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
-  const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
-  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg;
+  const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh + n_off;
+  const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg + n_off;
+  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg + n_off;
   const bf16* __restrict__ xp = a.x + b * a.x_sb + h * a.x_sh;
   const bf16* __restrict__ zp = a.has_z ? a.z + b * a.z_sb + h * a.z_sh : nullptr;
-  const float A2 = __ldg(a.A + h * a.N + n) * LOG2E;
-  const float bias = a.has_bias ? __ldg(a.bias + h * a.N + n) : 0.f;
+  const float A2 = __ldg(a.A + h * a.N + n_off + n) * LOG2E;
+  const float bias = a.has_bias ? __ldg(a.bias + h * a.N + n_off + n) : 0.f;
+  // the same constants for the two adjacent states (2 pr, 2 pr + 1) of the fast instantiation's operand pass
+  const int pr0 = n_off + 2 * (tid % (NT / 2));
+  const float2 A2p = f2(__ldg(a.A + h * a.N + pr0) * LOG2E, __ldg(a.A + h * a.N + pr0 + 1) * LOG2E);
+  const float bsc = a.softplus ? LOG2E : 1.f;
+  const float2 biasL2 = a.has_bias ? f2(__ldg(a.bias + h * a.N + pr0) * bsc, __ldg(a.bias + h * a.N + pr0 + 1) * bsc) : f2(0.f);
   const int nblk = (a.L + QB - 1) / QB;
 
   // one-time setup: zero the padded operand tiles, barriers, TMEM
@@ -212,14 +223,14 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 
   // bulk prefetch of the dt / B / C rows of block `blk` (service warp, completion on barS).  When the
   // B / C rows are adjacent in memory a whole tile is ONE copy; a reversed scan then finds row l of
-  // the block at staged row rows-1-l (see srow below).
+  // the block at staged row rows-1-l.
   auto prefetch = [&](int blk) {
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     const bool dt_tile = kStageDt && a.dt_tma;
     const int64_t m0 = a.rev ? a.L - row0 - rows : row0;            // lowest memory row of the tile
     if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * 2 + (kStageDt ? (uint32_t)(dt_tile ? QB : rows) * NT * 2 : 0u));
     __syncwarp();
-    if (dt_tile && lane == 2) tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh, b * a.L + (int)m0, barS);
+    if (dt_tile && lane == 2) tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh + n_off, b * a.L + (int)m0, barS);
     if (a.bc_contig) {
       if (lane == 0) bulk_g2s(smem + SM::kSB, Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2, barS);
       if (lane == 1) bulk_g2s(smem + SM::kSC, Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2, barS);
@@ -238,7 +249,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
     if (blk >= nblk) return;
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     const int64_t m0 = a.rev ? a.L - row0 - rows : row0;
-    if (kStageDt && a.dt_tma && lane == 2) tma_prefetch_2d(&dtmap, h * (int)a.dt_sh, b * a.L + (int)m0);
+    if (kStageDt && a.dt_tma && lane == 2) tma_prefetch_2d(&dtmap, h * (int)a.dt_sh + n_off, b * a.L + (int)m0);
     if (a.bc_contig) {
       if (lane == 0) bulk_prefetch_l2(Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2);
       if (lane == 1) bulk_prefetch_l2(Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2);
@@ -259,7 +270,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 #pragma unroll
     for (int j = 0; j < HP; ++j) sc[j] = 0.f;
     if (a.has_init) {
-      const bf16* __restrict__ ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n;
+      const bf16* __restrict__ ip = a.init + (((size_t)b * a.H + h) * a.P) * a.N + n_off + n;
 #pragma unroll
       for (int j = 0; j < HP; ++j)
         if (half * HP + j < a.P) sc[j] = __bfloat162float(ip[(size_t)(half * HP + j) * a.N]);
@@ -284,47 +295,59 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   };
   auto bf_lo = [](uint32_t w) { return __uint_as_float(w << 16); };
   auto bf_hi = [](uint32_t w) { return __uint_as_float(w & 0xffff0000u); };
-  // out = (y + D x) * silu(z) for the output rows of a finished block.  The [64][P / 4] groups of the tile are
-  // dealt out one per thread: groups 0..511 to the column threads (which do them while the MMAs of the next
-  // block run and they would otherwise wait), the rest to the I/O threads.  R groups per call, loads first.
-  auto store_groups = [&](auto rtag, int t_row0, int t_rows, int g0, int gstride) {
-    constexpr int R = decltype(rtag)::value;
-    uint2 xv[R], zv[R];
-    int ls[R], gs[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int gi = g0 + r * gstride;
-      ls[r] = gi / ngrp;
-      gs[r] = gi - ls[r] * ngrp;
-      const int64_t mr = trow(a, t_row0 + min(ls[r], t_rows - 1));
-      xv[r] = *(const uint2*)(xp + mr * a.x_sl + gs[r] * 4);
-      zv[r] = a.has_z ? *(const uint2*)(zp + mr * a.z_sl + gs[r] * 4) : make_uint2(0, 0);
+  // out = (y + D x) * silu(z) for the output rows of a finished block.  The [64][P / 4] groups of the tile are dealt
+  // out one per thread: groups 0..511 to the column threads (which do them while the MMAs of the next block run and
+  // they would otherwise wait), the rest to the I/O threads.  `group_load` issues the loads of x and z, `group_store`
+  // combines them with the accumulator row in shared memory and stores.
+  struct RowGroup { uint2 xv, zv; int l, gq; };
+  auto group_load = [&](int t_row0, int t_rows, int gi) {
+    RowGroup g;
+    g.l = gi / ngrp;
+    g.gq = gi - g.l * ngrp;
+    const int64_t mr = trow(a, t_row0 + min(g.l, t_rows - 1));
+    g.xv = *(const uint2*)(xp + mr * a.x_sl + g.gq * 4);
+    g.zv = a.has_z ? *(const uint2*)(zp + mr * a.z_sl + g.gq * 4) : make_uint2(0, 0);
+    return g;
+  };
+  auto group_store = [&](const RowGroup& g, int t_row0, int t_rows) {
+    const int l = g.l, gq = g.gq;
+    if (l >= t_rows) return;
+    const float4 yv = *(const float4*)(smem + SM::kY + (l * PP + gq * 4) * 4);
+    if (a.ypart) {                                         // one slice of the states: the skip and the gate come after the sum
+      *(float4*)(a.ypart + ((((size_t)blockIdx.x * a.b + b) * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4) = yv;
+      return;
     }
+    float y[4] = {yv.x, yv.y, yv.z, yv.w};
+    const float xf[4] = {bf_lo(g.xv.x), bf_hi(g.xv.x), bf_lo(g.xv.y), bf_hi(g.xv.y)};
+    const float zf[4] = {bf_lo(g.zv.x), bf_hi(g.zv.x), bf_lo(g.zv.y), bf_hi(g.zv.y)};
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int l = ls[r], gq = gs[r];
-      if (l < t_rows) {
-        const float4 yv = *(const float4*)(smem + SM::kY + (l * PP + gq * 4) * 4);
-        float y[4] = {yv.x, yv.y, yv.z, yv.w};
-        const float xf[4] = {bf_lo(xv[r].x), bf_hi(xv[r].x), bf_lo(xv[r].y), bf_hi(xv[r].y)};
-        const float zf[4] = {bf_lo(zv[r].x), bf_hi(zv[r].x), bf_lo(zv[r].y), bf_hi(zv[r].y)};
+    for (int q = 0; q < 4; ++q)
+      y[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, xf[q], y[q]);
+    const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + gq * 4;
+    if (a.has_z) {
+      *(uint2*)(a.out_x + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          y[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, xf[q], y[q]);
-        const int64_t o = b * a.o_sb + (int64_t)trow(a, t_row0 + l) * a.o_sl + h * a.o_sh + gq * 4;
-        if (a.has_z) {
-          *(uint2*)(a.out_x + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
-#pragma unroll
-          for (int q = 0; q < 4; ++q) y[q] *= zf[q] / (1.f + ex2f(-zf[q] * LOG2E));
-        }
-        *(uint2*)(a.out + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
-      }
+      for (int q = 0; q < 4; ++q) y[q] *= __fdividef(zf[q], 1.f + ex2f(-zf[q] * LOG2E));
     }
+    *(uint2*)(a.out + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
   };
   constexpr int kColGroups = 512;                        // groups of a tile handled by the column threads
-  auto store_tile = [&](int t_row0, int t_rows) {
-    if (is_col) store_groups(std::integral_constant<int, kColGroups / NTH>{}, t_row0, t_rows, tid, NTH);
-    else if (is_io) store_groups(std::integral_constant<int, 2>{}, t_row0, t_rows, kColGroups + io_t, NIO);
+  constexpr int kColR = kColGroups / NTH;                // ... per column thread
+  constexpr int kIoR = (QB * (PP / 4) - kColGroups + NIO - 1) / NIO;   // per I/O thread
+  auto store_tile_io = [&](int t_row0, int t_rows) {     // the I/O threads' share, loads first
+    RowGroup g[kIoR];
+#pragma unroll
+    for (int r = 0; r < kIoR; ++r) g[r] = group_load(t_row0, t_rows, kColGroups + io_t + r * NIO);
+#pragma unroll
+    for (int r = 0; r < kIoR; ++r) group_store(g[r], t_row0, t_rows);
+  };
+  auto store_tile = [&](int t_row0, int t_rows) {        // a whole tile at once (after the walk)
+    if (is_col) {
+#pragma unroll
+      for (int r = 0; r < kColR; ++r) group_store(group_load(t_row0, t_rows, tid + r * NTH), t_row0, t_rows);
+    } else if (is_io) {
+      store_tile_io(t_row0, t_rows);
+    }
   };
 
   // descriptor bases (start address = shared-memory base; per-MMA byte offsets are added at issue)
@@ -388,7 +411,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         for (int r = io_t; r < rows; r += NIO) prefetch_l2_span(zp + (int64_t)trow(a, row0 + r) * a.z_sl, a.P * 2);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
-      if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);
+      if (blk > 0 && !a.no_output) store_tile_io(row0 - QB, QB);
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
     }
@@ -460,59 +483,121 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const bf16* sC = (const bf16*)(smem + SM::kSC) + n + (flipB ? (rows - 1) * NT : 0);
       const int bstep = flipB ? -NT : NT;
 
-      // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
-      float dtv[32];
-      float asum = 0.f;
-      auto phaseA = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          const int sl = kFull ? l : min(l, rows - 1);
-          float raw;
-          if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
-          else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
-          bool clamped;
-          float v = dt_transform(a, raw, bias, clamped);
-          if (!kFull && l >= rows) v = 0.f;
-          dtv[j] = v;
-          asum = fmaf(v, A2, asum);
+      if constexpr (kWin) {
+        // the windowed instantiation keeps the one-state-per-thread pass (its window code addresses rows per half)
+        // ---- phase A: dt of this thread's 32 rows and their summed log2-decay -----------------------
+        float dtv[32];
+        float asum = 0.f;
+        auto phaseA = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+  #pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int l = half * 32 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            float raw;
+            if (kStageDt) raw = __bfloat162float(sdt[sl * dstep]);
+            else raw = ldf(dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + n);
+            bool clamped;
+            float v = dt_transform(a, raw, bias, clamped);
+            if (!kFull && l >= rows) v = 0.f;
+            dtv[j] = v;
+            asum = fmaf(v, A2, asum);
+          }
+        };
+        if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
+        sAsum[half * NT + n] = asum;
+        named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
+        const float a0 = sAsum[n];
+        alast = a0 + sAsum[NT + n];
+        // Range of the factorisation: 2^(+-a) must stay finite in bf16.  A column whose decay over the block
+        // (or over its first half) exceeds 2^120 asks for the block to be redone in 2^k row windows, each with
+        // its own reference: the smallest k for which this thread's windows stay within 2^100.
+        if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
+          if (kWin) atomicMax(sFlag, (uint32_t)(blk + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
+          else unsafe = 1;
         }
-      };
-      if (rows == QB) phaseA(std::true_type{}); else phaseA(std::false_type{});
-      sAsum[half * NT + n] = asum;
-      named_barrier(1 + (warp & (NT / 32 - 1)), 64);     // the two warps that share these 32 columns
-      const float a0 = sAsum[n];
-      alast = a0 + sAsum[NT + n];
-      // Range of the factorisation: 2^(+-a) must stay finite in bf16.  A column whose decay over the block
-      // (or over its first half) exceeds 2^120 asks for the block to be redone in 2^k row windows, each with
-      // its own reference: the smallest k for which this thread's windows stay within 2^100.
-      if (!(fabsf(a0) <= 120.f && fabsf(alast) <= 120.f)) {
-        if (kWin) atomicMax(sFlag, (uint32_t)(blk + 1) * 8 + window_need<TDT>(a, sdt, dstep, dtp, row0, rows, half, n, A2, bias));
-        else unsafe = 1;
-      }
 
-      // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
-      auto phaseB = [&](auto full) {
-        constexpr bool kFull = decltype(full)::value;
-        uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
-        uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
-        const int kc = kcol >> 3;
-        float acc = half ? a0 : 0.f;
+        // ---- phase B: this thread's rows of column n of Cd = C 2^a and Bd = B dt 2^-a ------------------
+        auto phaseB = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+          uint8_t* bd_col = smem + SM::kBd + (n >> 6) * SM::kAtomB + half * (32 * 128) + ((kcol & 7) << 1);
+          const int kc = kcol >> 3;
+          float acc = half ? a0 : 0.f;
+  #pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int l = half * 32 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            acc = fmaf(dtv[j], A2, acc);
+            float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
+            float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
+            if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
+            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+            *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
+            *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
+          }
+        };
+        if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
+      } else {
+        // ---- operand pass, two adjacent states (2 pr, 2 pr + 1) and the 16 rows of quarter qr per thread: every
+        //      shared-memory access moves a bf16 pair (4 bytes) and the fp32 arithmetic runs as packed pairs --------
+        constexpr int NPR = NT / 2;
+        const int pr = tid % NPR, qr = tid / NPR;
+        const bool flipB2 = kMode ? kMode == 2 : (a.bc_contig && a.rev);
+        const uint32_t* sdt2 = (const uint32_t*)(smem + SM::kSdt) + pr + (flipT ? (rows - 1) * NPR : 0);
+        const int dstep2 = flipT ? -NPR : NPR;
+        const uint32_t* sB2 = (const uint32_t*)(smem + SM::kSB) + pr + (flipB2 ? (rows - 1) * NPR : 0);
+        const uint32_t* sC2 = (const uint32_t*)(smem + SM::kSC) + pr + (flipB2 ? (rows - 1) * NPR : 0);
+        const int bstep2 = flipB2 ? -NPR : NPR;
+        float2 dtv[16];
+        float2 asum2 = f2(0.f);
+        auto phaseA2 = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int l = half * 32 + j;
-          const int sl = kFull ? l : min(l, rows - 1);
-          acc = fmaf(dtv[j], A2, acc);
-          float cd = __bfloat162float(sC[sl * bstep]) * ex2f(acc);
-          float bd = __bfloat162float(sB[sl * bstep]) * dtv[j] * ex2f(-acc);
-          if (!kFull && l >= rows) { cd = 0.f; bd = 0.f; }
-          const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
-          *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-          *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-        }
-      };
-      if (rows == QB) phaseB(std::true_type{}); else phaseB(std::false_type{});
+          for (int j = 0; j < 16; ++j) {
+            const int l = qr * 16 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            float2 raw;
+            if constexpr (kStageDt) raw = unpack_bf16(sdt2[sl * dstep2]);
+            else raw = *(const float2*)((const float*)dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + 2 * pr);
+            float2 v = dt_transform2(a, raw, biasL2);
+            if (!kFull && l >= rows) v = f2(0.f);
+            dtv[j] = v;
+            asum2 = __ffma2_rn(v, A2p, asum2);
+          }
+        };
+        if (rows == QB) phaseA2(std::true_type{}); else phaseA2(std::false_type{});
+        *(float2*)(sAsum + qr * NT + 2 * pr) = asum2;
+        named_barrier(1 + (warp % (NPR / 32)), 128);       // the four warps that share these 64 columns
+        const float2 q0 = *(const float2*)(sAsum + 2 * pr), q1 = *(const float2*)(sAsum + NT + 2 * pr),
+                     q2 = *(const float2*)(sAsum + 2 * NT + 2 * pr), q3 = *(const float2*)(sAsum + 3 * NT + 2 * pr);
+        const float2 c1 = q0, c2 = __fadd2_rn(c1, q1), c3 = __fadd2_rn(c2, q2), c4 = __fadd2_rn(c3, q3);
+        // range of the factorisation (see the windowed instantiation above): every running sum must stay within 2^120
+        const float worst = fmaxf(fmaxf(fmaxf(fabsf(c1.x), fabsf(c1.y)), fmaxf(fabsf(c2.x), fabsf(c2.y))),
+                                  fmaxf(fmaxf(fabsf(c3.x), fabsf(c3.y)), fmaxf(fabsf(c4.x), fabsf(c4.y))));
+        if (!(worst <= 120.f)) unsafe = 1;
+        auto phaseB2 = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          const int at = pr >> 5, kc = (pr & 31) >> 2;     // 64-state atom, 16-byte chunk inside its 128-byte rows
+          uint8_t* cd_col = smem + SM::kCd + at * (QB * 128) + qr * (16 * 128) + ((pr & 3) << 2);
+          uint8_t* bd_col = smem + SM::kBd + at * SM::kAtomB + qr * (16 * 128) + ((pr & 3) << 2);
+          float2 acc = qr == 0 ? f2(0.f) : (qr == 1 ? c1 : (qr == 2 ? c2 : c3));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int l = qr * 16 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            const float2 dtj = dtv[j];
+            acc = __ffma2_rn(dtj, A2p, acc);
+            float2 cd = __fmul2_rn(unpack_bf16(sC2[sl * bstep2]), ex2f2(acc));
+            float2 bd = __fmul2_rn(__fmul2_rn(unpack_bf16(sB2[sl * bstep2]), dtj), ex2f2_neg(acc));
+            if (!kFull && l >= rows) { cd = f2(0.f); bd = f2(0.f); }
+            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+            *(uint32_t*)(cd_col + off) = pack_bf16(cd);
+            *(uint32_t*)(bd_col + off) = pack_bf16(bd);
+          }
+        };
+        if (rows == QB) phaseB2(std::true_type{}); else phaseB2(std::false_type{});
+      }
       fence_async_smem();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
@@ -520,7 +605,12 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
       const int kw = (kWin && (flag >> 3) == (uint32_t)(blk + 1)) ? (int)(flag & 7) : 0;
       const int ws = QB >> kw;
       const int npass = kw ? (rows + ws - 1) / ws : 1;
-      if (blk > 0 && !a.no_output) store_tile(row0 - QB, QB);
+      if constexpr (!kWin) alast = ((sAsum[n] + sAsum[NT + n]) + sAsum[2 * NT + n]) + sAsum[3 * NT + n];   // summed decay of column n
+      // output rows of the previous block, while the MMAs of this one run and the column threads would wait anyway
+      if (blk > 0 && !a.no_output) {
+#pragma unroll
+        for (int r = 0; r < kColR; ++r) group_store(group_load(row0 - QB, QB, tid + r * NTH), row0 - QB, QB);
+      }
       if (!kWin || kw == 0) {
         if (!mbar_wait_warp(barA, phA)) failed = true;
         phA ^= 1;
@@ -529,7 +619,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         windowed = 1;
         WinCtx<TDT> c;
         c.smem = smem; c.barA = barA; c.barA2 = barA2; c.dtp = dtp; c.savep = savep; c.sop_col = sop_col; c.sAsum = sAsum;
-        c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n : nullptr;
+        c.final_col = (blk == nblk - 1 && a.want_final) ? a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n_off + n : nullptr;
         c.n = n; c.half = half; c.rows = rows; c.row0 = row0; c.blk = blk; c.ws = ws; c.npass = npass;
         c.A2 = A2; c.bias = bias; c.t_S = t_S; c.phA = phA; c.failed = failed;
         fwd_windowed_passes<NT, TDT>(a, c);
@@ -575,7 +665,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         tmem_st8(t_S + 16, sc + 16);
         publish_state(sc, blk + 1, true);
         if (blk == nblk - 1 && a.want_final) {
-          float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n;
+          float* fp = a.final_states + (((size_t)b * a.H + h) * a.P) * a.N + n_off + n;
 #pragma unroll
           for (int j = 0; j < HP; ++j)
             if (half * HP + j < a.P) fp[(size_t)(half * HP + j) * a.N] = sc[j];
@@ -613,7 +703,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   const int any_unsafe = votes & 1;
   failed = (votes & 2) != 0;
   if (!failed && !a.no_output && nblk > 0) store_tile(prev_row0, prev_rows);   // last block's tile
-  if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
+  if (!kWin && tid == 0) a.redo[stream] = any_unsafe;
   if (a.status) {
     if (failed && tid == 0) atomicOr(a.status, 1);
     if (windowed && tid == 0) atomicOr(a.status, 4);       // informational: some block ran windowed
@@ -626,27 +716,79 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 // ---------------------------------------------------------------------------------------------
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
-bool tensor_path_supported(const issm_params& p) {
+// number of 256-state slices a call is cut into (1 for dstate 128 / 256; 0 = no tensor-core kernels for this dstate)
+static int state_slices(int dstate) {
+  if (dstate == 128 || dstate == 256) return 1;
+  if (dstate % 256 == 0 && dstate <= 1024) return dstate / 256;
+  return 0;
+}
+
+bool tensor_path_supported(const issm_params& p, int pass) {
   if (p.io_dtype != ISSM_BF16) return false;
   // the tile-I/O warps move 4 head-dim elements (8 bytes) at a time; the backward's dx tile holds 40 columns
   if (p.headdim > 40 || (p.headdim & 3)) return false;
   if ((p.x_sb | p.x_sl | p.x_sh | p.out_sb | p.out_sl | p.out_sh | p.dout_sb | p.dout_sl | p.dout_sh) & 3) return false;
   if (p.has_z && ((p.z_sb | p.z_sl | p.z_sh) & 3)) return false;
   if (((uintptr_t)p.x | (uintptr_t)p.z | (uintptr_t)p.out | (uintptr_t)p.out_x | (uintptr_t)p.dout | (uintptr_t)p.dx | (uintptr_t)p.dz) & 7) return false;
-  if (p.dstate != 128 && p.dstate != 256) return false;
+  const int slices = state_slices(p.dstate);
+  if (slices == 0 || (slices > 1 && pass != 0)) return false;   // sliced states: forward kernels only
   // bulk (TMA) row copies need 16-byte aligned rows of B, C and (bf16) dt
   if (p.B && (!aligned16(p.B) || !aligned16(p.C))) return false;
   if ((p.B_sb | p.B_sl | p.B_sg | p.C_sb | p.C_sl | p.C_sg) & 7) return false;
   if (p.dt_dtype == ISSM_BF16) {
     if (p.dt && !aligned16(p.dt)) return false;
     if ((p.dt_sb | p.dt_sl | p.dt_sh) & 7) return false;
+  } else {
+    // float dt is read from global memory two adjacent states (8 bytes) at a time
+    if (((uintptr_t)p.dt & 7) || ((p.dt_sb | p.dt_sl | p.dt_sh) & 1)) return false;
   }
   return true;
 }
 
 size_t tensor_workspace_bytes(const issm_params& p, int pass) {
-  // forward: one mark per (batch, head) stream
-  return pass == 0 ? align_up((size_t)p.batch * p.nheads * sizeof(int), 256) : tensor_bwd_workspace_bytes(p);
+  if (pass != 0) return tensor_bwd_workspace_bytes(p);
+  // forward: one mark per (slice, batch, head) stream; with more than one slice the float partial outputs
+  const int slices = state_slices(p.dstate);
+  size_t total = align_up((size_t)slices * p.batch * p.nheads * sizeof(int), 256);
+  if (slices > 1) total += align_up((size_t)slices * p.batch * p.seqlen * p.nheads * p.headdim * sizeof(float), 256);
+  return total;
+}
+
+// out = (sum over the slices of the partial outputs + D x) * silu(z); pre-gate rows to out_x when gated.
+// One thread per group of 4 consecutive head-dim elements.
+__global__ void k_combine_slices(const TArgs a, int slices, size_t groups) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  const int ngrp = a.P / 4;
+  const int gq = (int)(i % ngrp);
+  size_t r = i / ngrp;
+  const int h = (int)(r % a.H);
+  r /= a.H;
+  const int l = (int)(r % a.L);
+  const int b = (int)(r / a.L);
+  const size_t slice_stride = (size_t)a.b * a.L * a.H * a.P;
+  const float* yp = a.ypart + (((size_t)b * a.L + l) * a.H + h) * a.P + gq * 4;
+  float4 acc = *(const float4*)yp;
+  for (int s = 1; s < slices; ++s) {
+    const float4 v = *(const float4*)(yp + s * slice_stride);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  float y[4] = {acc.x, acc.y, acc.z, acc.w};
+  if (a.has_D) {
+    const uint2 xv = *(const uint2*)(a.x + b * a.x_sb + (int64_t)l * a.x_sl + h * a.x_sh + gq * 4);
+    const float xf[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16), __uint_as_float(xv.y & 0xffff0000u)};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) y[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : __ldg(a.D + h), xf[q], y[q]);
+  }
+  const int64_t o = b * a.o_sb + (int64_t)l * a.o_sl + h * a.o_sh + gq * 4;
+  if (a.has_z) {
+    *(uint2*)(a.out_x + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+    const uint2 zv = *(const uint2*)(a.z + b * a.z_sb + (int64_t)l * a.z_sl + h * a.z_sh + gq * 4);
+    const float zf[4] = {__uint_as_float(zv.x << 16), __uint_as_float(zv.x & 0xffff0000u), __uint_as_float(zv.y << 16), __uint_as_float(zv.y & 0xffff0000u)};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) y[q] *= __fdividef(zf[q], 1.f + ex2f(-zf[q] * LOG2E));
+  }
+  *(uint2*)(a.out + o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
 }
 
 TArgs make_targs(const issm_params& p) {
@@ -667,7 +809,8 @@ TArgs make_targs(const issm_params& p) {
   a.final_states = p.final_states;
   a.status = p.status;
   a.saved = (bf16*)p.saved_states;
-  a.bc_contig = (p.B_sl == p.dstate && p.C_sl == p.dstate);
+  // a whole 64-row tile of B / C is one contiguous copy only when a row IS the tile's row (not a 256-state slice of it)
+  a.bc_contig = (p.B_sl == p.dstate && p.C_sl == p.dstate && p.dstate <= 256);
   a.dt_tma = 0;
   return a;
 }
@@ -697,7 +840,7 @@ bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
   if (!fn) return false;
   const cuuint64_t gdim[2] = {width, (cuuint64_t)p.batch * p.seqlen};
   const cuuint64_t gstride[1] = {(cuuint64_t)p.dt_sl * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)p.dstate, (cuuint32_t)QB};
+  const cuuint32_t box[2] = {(cuuint32_t)(p.dstate > 256 ? 256 : p.dstate), (cuuint32_t)QB};   // one slice of the states per tile
   const cuuint32_t estr[2] = {1, 1};
   return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.dt), gdim, gstride, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -712,8 +855,13 @@ static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_
   if (SmemAttrOnce<FastTag>::set(k_fwd_tensor<NT, TDT, false, kMode>, smem) != ISSM_OK ||
       SmemAttrOnce<WinTag>::set(k_fwd_tensor<NT, TDT, true, 0>, smem) != ISSM_OK)
     return ISSM_ERR_CUDA;
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  const int slices = a.N / NT;
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  if (slices > 1 && !a.no_output) {
+    const size_t groups = (size_t)a.b * a.L * a.H * (a.P / 4);
+    ISSM_LAUNCH(k_combine_slices, (unsigned)cdiv64(groups, 256), 256, 0, s, a, slices, groups);
+  }
   return ISSM_OK;
 }
 
@@ -730,7 +878,12 @@ static int launch_fwd(TArgs a, const issm_params& p, cudaStream_t s) {
 int tensor_fwd(const issm_params& p, cudaStream_t s) {
   TArgs a = make_targs(p);
   a.redo = (int*)p.workspace;
-  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
+  const int slices = state_slices(p.dstate);
+  if (slices > 1) {
+    a.ypart = (float*)((char*)p.workspace + align_up((size_t)slices * p.batch * p.nheads * sizeof(int), 256));
+    a.saved = nullptr;                                     // the sliced forward keeps no block-entry states (its backward runs on the SIMT kernels)
+  }
+  if (p.dstate != 128) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
   return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);
 }
 
@@ -741,7 +894,7 @@ int tensor_fwd_states_only(const issm_params& p, bf16* saved, int* redo, cudaStr
   a.redo = redo;
   a.no_output = 1;
   a.want_final = 0;
-  if (p.dstate == 256) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
+  if (p.dstate != 128) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
   return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);
 }
 

@@ -22,6 +22,7 @@ struct TArgs {
   int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
   bf16* wscr;       // backward, windowed kernel: (batch, nheads, 63, state) bf16 window-entry states of the block in progress
   int* redo;        // (batch, nheads) marks: stream holds a block outside the fast kernel's range, redo it windowed
+  float* ypart;     // forward with the states cut into slices of 256 (dstate 512 ...): (slice, b, L, H, P) float partial outputs
   int dt_tma;       // dt is a regular 2-D array of rows: a 64-row tile is ONE tiled TMA load through a tensor map
   int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
   float dtmin, dtmax;
@@ -57,7 +58,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));   // one instruction: {hi, lo} -> packed pair
   return r;
 }
+__device__ __forceinline__ uint32_t pack_bf16(float2 v) { return pack_bf16(v.x, v.y); }
 
+
+// ---- two adjacent states per thread: packed fp32 pairs (one instruction per pair on sm_100) ---------------------
+__device__ __forceinline__ float2 f2(float x, float y) { return make_float2(x, y); }
+__device__ __forceinline__ float2 f2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 ex2f2(float2 v) { return make_float2(ex2f(v.x), ex2f(v.y)); }
+__device__ __forceinline__ float2 ex2f2_neg(float2 v) { return make_float2(ex2f(-v.x), ex2f(-v.y)); }
+__device__ __forceinline__ float2 lg2f2(float2 v) { return make_float2(lg2f(v.x), lg2f(v.y)); }
+// a packed bf16 pair (low half = the lower address) -> two floats
+__device__ __forceinline__ float2 unpack_bf16(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+
+// dt of one row, two adjacent states: bias, softplus (reference threshold 20, evaluated in the log2 domain: the
+// pre-activation scaled by log2 e is `t`, softplus = ln 2 * lg2(1 + 2^t), and above the threshold t * ln 2), clamp.
+// biasL = bias * log2 e when softplus is on, else the plain bias.
+__device__ __forceinline__ float2 dt_transform2(const TArgs& a, float2 raw, float2 biasL) {
+  float2 v;
+  if (a.softplus) {
+    const float2 t = __ffma2_rn(raw, f2(LOG2E), biasL);
+    float2 s = lg2f2(__fadd2_rn(ex2f2(t), f2(1.f)));
+    s.x = t.x <= 20.f * LOG2E ? s.x : t.x;
+    s.y = t.y <= 20.f * LOG2E ? s.y : t.y;
+    v = __fmul2_rn(s, f2(LN2));
+  } else {
+    v = __fadd2_rn(raw, biasL);
+  }
+  v.x = fminf(fmaxf(v.x, a.dtmin), a.dtmax);
+  v.y = fminf(fmaxf(v.y, a.dtmin), a.dtmax);
+  return v;
+}
 
 // dt of one row as the kernels use it: bias, softplus (reference threshold), clamp.
 // `clamped` reports whether the clamp changed the value (no gradient flows then).

@@ -101,6 +101,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   const float A2 = __ldg(a.A + h * a.N + n) * LOG2E;
   const float Anat = __ldg(a.A + h * a.N + n);
   const float bias = a.has_bias ? __ldg(a.bias + h * a.N + n) : 0.f;
+  // the same constants for the two adjacent states (2 pr, 2 pr + 1) of the fast instantiation's operand pass
+  const int pr0 = 2 * (tid % (NT / 2));
+  const float2 A2p = f2(__ldg(a.A + h * a.N + pr0) * LOG2E, __ldg(a.A + h * a.N + pr0 + 1) * LOG2E);
+  const float bsc = a.softplus ? LOG2E : 1.f;
+  const float2 biasL2 = a.has_bias ? f2(__ldg(a.bias + h * a.N + pr0) * bsc, __ldg(a.bias + h * a.N + pr0 + 1) * bsc) : f2(0.f);
   const int nblk = (a.L + QB - 1) / QB;
   const size_t bh = (size_t)b * a.H + h;
 
@@ -204,62 +209,70 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
     if (zp) {
       const float zf[4] = {bf_lo(zv.x), bf_hi(zv.x), bf_lo(zv.y), bf_hi(zv.y)};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) dy[q] *= zf[q] / (1.f + ex2f(-zf[q] * LOG2E));
+      for (int q = 0; q < 4; ++q) dy[q] *= __fdividef(zf[q], 1.f + ex2f(-zf[q] * LOG2E));
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q) dy[q] = __bfloat162float(__float2bfloat16_rn(dy[q]));
   };
   // Rows of a finished block: dx = accumulator tile + D dy and dz = dout * y * sigmoid(z)(1 + z(1 - sigmoid(z)))
-  // (issm_chunk_scan.py:351-360).  The [64][P / 4] groups of the tile are dealt out one per thread: groups 0..511
-  // to the column threads, which do them while the second MMA phase of the next block runs and they would
-  // otherwise wait, the rest to the I/O threads.  R groups per call, loads first.
-  auto finish_groups = [&](auto rtag, int t_row0, int t_rows, int g0, int gstride) {
-    constexpr int R = decltype(rtag)::value;
-    uint2 gv[R], zv[R], yv[R];
-    int ls[R], gs[R];
+  // (issm_chunk_scan.py:351-360).  The [64][P / 4] groups of the tile are dealt out one per thread: groups 0..511 to
+  // the column threads (which do them while the second MMA phase of the next block runs and they would otherwise
+  // wait), the rest to the I/O threads.  `group_load` issues the loads of dout, z and the saved pre-gate output,
+  // `group_store` combines them with the dx row in shared memory and stores.
+  struct RowGroup { uint2 gv, zv, yv; int l, gq; };
+  auto group_load = [&](int t_row0, int t_rows, int gi) {
+    RowGroup g;
+    g.l = gi / ngrp;
+    g.gq = gi - g.l * ngrp;
+    const int64_t mr = trow(a, t_row0 + min(g.l, t_rows - 1));
+    g.gv = *(const uint2*)(gp + mr * a.g_sl + g.gq * 4);
+    g.zv = zp ? *(const uint2*)(zp + mr * a.z_sl + g.gq * 4) : make_uint2(0, 0);
+    g.yv = zp ? *(const uint2*)(yp + mr * a.o_sl + g.gq * 4) : make_uint2(0, 0);
+    return g;
+  };
+  auto group_store = [&](const RowGroup& g, int t_row0, int t_rows) {
+    const int l = g.l, gq = g.gq;
+    if (l >= t_rows) return;
+    const uint2 tv = *(const uint2*)(smem + SM::kDxT + (l * SM::DXS + gq * 4) * 2);
+    float v[4] = {bf_lo(tv.x), bf_hi(tv.x), bf_lo(tv.y), bf_hi(tv.y)};
+    float dy[4] = {bf_lo(g.gv.x), bf_hi(g.gv.x), bf_lo(g.gv.y), bf_hi(g.gv.y)};
+    const size_t o = (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4;
+    if (zp) {
+      const float zf[4] = {bf_lo(g.zv.x), bf_hi(g.zv.x), bf_lo(g.zv.y), bf_hi(g.zv.y)};
+      const float yf[4] = {bf_lo(g.yv.x), bf_hi(g.yv.x), bf_lo(g.yv.y), bf_hi(g.yv.y)};
+      float dzv[4];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int gi = g0 + r * gstride;
-      ls[r] = gi / ngrp;
-      gs[r] = gi - ls[r] * ngrp;
-      const int64_t mr = trow(a, t_row0 + min(ls[r], t_rows - 1));
-      gv[r] = *(const uint2*)(gp + mr * a.g_sl + gs[r] * 4);
-      zv[r] = zp ? *(const uint2*)(zp + mr * a.z_sl + gs[r] * 4) : make_uint2(0, 0);
-      yv[r] = zp ? *(const uint2*)(yp + mr * a.o_sl + gs[r] * 4) : make_uint2(0, 0);
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int l = ls[r], gq = gs[r];
-      if (l < t_rows) {
-        const uint2 tv = *(const uint2*)(smem + SM::kDxT + (l * SM::DXS + gq * 4) * 2);
-        float v[4] = {bf_lo(tv.x), bf_hi(tv.x), bf_lo(tv.y), bf_hi(tv.y)};
-        float dy[4] = {bf_lo(gv[r].x), bf_hi(gv[r].x), bf_lo(gv[r].y), bf_hi(gv[r].y)};
-        const size_t o = (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4;
-        if (zp) {
-          const float zf[4] = {bf_lo(zv[r].x), bf_hi(zv[r].x), bf_lo(zv[r].y), bf_hi(zv[r].y)};
-          const float yf[4] = {bf_lo(yv[r].x), bf_hi(yv[r].x), bf_lo(yv[r].y), bf_hi(yv[r].y)};
-          float dzv[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float sg = 1.f / (1.f + ex2f(-zf[q] * LOG2E));
-            dzv[q] = dy[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
-            dy[q] *= zf[q] * sg;
-          }
-          *(uint2*)(a.dz + o) = make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
-        }
-        if (a.has_D) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, __bfloat162float(__float2bfloat16_rn(dy[q])), v[q]);
-        }
-        *(uint2*)(a.dx + o) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+      for (int q = 0; q < 4; ++q) {
+        const float sg = __fdividef(1.f, 1.f + ex2f(-zf[q] * LOG2E));
+        dzv[q] = dy[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
+        dy[q] *= zf[q] * sg;
       }
+      *(uint2*)(a.dz + o) = make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
     }
+    if (a.has_D) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : dscalar, __bfloat162float(__float2bfloat16_rn(dy[q])), v[q]);
+    }
+    *(uint2*)(a.dx + o) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
   };
   constexpr int kColGroups = 512;                        // groups of a tile handled by the column threads
-  auto finish_rows = [&](int t_row0, int t_rows) {
-    if (is_col) finish_groups(std::integral_constant<int, kColGroups / NTH>{}, t_row0, t_rows, tid, NTH);
-    else if (is_io) finish_groups(std::integral_constant<int, 2>{}, t_row0, t_rows, kColGroups + io_t, NIO);
+  constexpr int kColR = kColGroups / NTH;                // ... per column thread
+  constexpr int kIoR = (QB * (PP / 4) - kColGroups + NIO - 1) / NIO;   // per I/O thread
+  auto finish_rows_io = [&](int t_row0, int t_rows) {    // the I/O threads' share, loads first
+    RowGroup g[kIoR];
+#pragma unroll
+    for (int r = 0; r < kIoR; ++r) g[r] = group_load(t_row0, t_rows, kColGroups + io_t + r * NIO);
+#pragma unroll
+    for (int r = 0; r < kIoR; ++r) group_store(g[r], t_row0, t_rows);
+  };
+  auto finish_rows = [&](int t_row0, int t_rows) {       // a whole tile at once (after the walk)
+    if (is_col) {
+#pragma unroll
+      for (int r = 0; r < kColR; ++r) group_store(group_load(t_row0, t_rows, tid + r * NTH), t_row0, t_rows);
+    } else if (is_io) {
+      finish_rows_io(t_row0, t_rows);
+    }
   };
 
   // descriptor bases
@@ -324,7 +337,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       if (__syncthreads_or(failed)) { failed = true; break; }
       // dx / dz rows of the previous block beyond the column threads' share; named barrier 9 keeps the dx tile
       // from being rewritten before every thread has read its part
-      if (it > 0) finish_groups(std::integral_constant<int, 2>{}, row0 + QB, min(QB, a.L - row0 - QB), kColGroups + io_t, NIO);
+      if (it > 0) finish_rows_io(row0 + QB, min(QB, a.L - row0 - QB));
       asm volatile("bar.arrive 9, %0;" ::"r"(NTH + NIO) : "memory");
       fence_before_sync();
     }
@@ -466,7 +479,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       const int row0 = blk * QB;
       const int rows = min(QB, a.L - row0);
       const uint32_t parity = it & 1;
-      float a0 = 0.f, alast = 0.f, cst = 0.f;
+      float a0 = 0.f, alast = 0.f, cst = 0.f, cpart_own = 0.f;
 
       // ---- column threads: operand pass restricted to rows [w0, w1) of the block.  `first` is the ordinary pass over
       //      the whole block (staged C, range check, waits for the staged tiles); later passes (windowed kernel only)
@@ -559,6 +572,71 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         fence_async_smem();
       };
 
+      // ---- fast instantiation: the operand pass with two adjacent states (2 pr, 2 pr + 1) and the 16 rows of quarter
+      //      qr per thread: every shared-memory access moves a bf16 pair and the fp32 arithmetic runs as packed pairs.
+      //      The quarter sums of dt*A go through sXch ([4][NT]); a0 / alast of the thread's own column n are read from
+      //      there after the next block-wide barrier (column n belongs to another group of warps than the pair). -------
+      auto phaseAB_pairs = [&]() {
+        constexpr int NPR = NT / 2;
+        const int pr = tid % NPR, qr = tid / NPR;
+        const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev);
+        const uint32_t* sdt2 = (const uint32_t*)(smem + SM::kSdt) + pr + (flipT ? (rows - 1) * NPR : 0);
+        const int dstep2 = flipT ? -NPR : NPR;
+        const uint32_t* sB2 = (const uint32_t*)(smem + SM::kSB) + pr + (flipB ? (rows - 1) * NPR : 0);
+        const uint32_t* sC2 = (const uint32_t*)(smem + SM::kSC) + pr + (flipB ? (rows - 1) * NPR : 0);
+        const int bstep2 = flipB ? -NPR : NPR;
+        float2 dtv[16];
+        float2 asum2 = f2(0.f);
+        auto phaseA2 = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int l = qr * 16 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            float2 raw;
+            if constexpr (kStageDt) raw = unpack_bf16(sdt2[sl * dstep2]);
+            else raw = *(const float2*)((const float*)dtp + (int64_t)trow(a, row0 + sl) * a.dt_sl + 2 * pr);
+            float2 v = dt_transform2(a, raw, biasL2);
+            if (!kFull && l >= rows) v = f2(0.f);
+            dtv[j] = v;
+            asum2 = __ffma2_rn(v, A2p, asum2);
+          }
+        };
+        if (rows == QB) phaseA2(std::true_type{}); else phaseA2(std::false_type{});
+        *(float2*)(sXch + qr * NT + 2 * pr) = asum2;
+        named_barrier(1 + (warp % (NPR / 32)), 128);       // the four warps that share these 64 columns
+        const float2 q0 = *(const float2*)(sXch + 2 * pr), q1 = *(const float2*)(sXch + NT + 2 * pr),
+                     q2 = *(const float2*)(sXch + 2 * NT + 2 * pr), q3 = *(const float2*)(sXch + 3 * NT + 2 * pr);
+        const float2 c1 = q0, c2 = __fadd2_rn(c1, q1), c3 = __fadd2_rn(c2, q2), c4 = __fadd2_rn(c3, q3);
+        // range of the factorisation: 2^(+-a) must stay finite in bf16 (see the forward kernel)
+        const float worst = fmaxf(fmaxf(fmaxf(fabsf(c1.x), fabsf(c1.y)), fmaxf(fabsf(c2.x), fabsf(c2.y))),
+                                  fmaxf(fmaxf(fabsf(c3.x), fabsf(c3.y)), fmaxf(fabsf(c4.x), fabsf(c4.y))));
+        if (!(worst <= 120.f)) unsafe = 1;
+        if (!mbar_wait_warp(barT, parity)) failed = true;
+        if (!mbar_wait_warp(barV, parity)) failed = true;
+        auto phaseB2 = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          const int at = pr >> 5, kc = (pr & 31) >> 2;     // 64-state atom, 16-byte chunk inside its 128-byte rows
+          uint8_t* cd_col = smem + SM::kCd + at * (QB * 128) + qr * (16 * 128) + ((pr & 3) << 2);
+          uint8_t* bd_col = smem + SM::kBd + at * (QB * 128) + qr * (16 * 128) + ((pr & 3) << 2);
+          float2 acc = qr == 0 ? f2(0.f) : (qr == 1 ? c1 : (qr == 2 ? c2 : c3));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int l = qr * 16 + j;
+            const int sl = kFull ? l : min(l, rows - 1);
+            acc = __ffma2_rn(dtv[j], A2p, acc);
+            float2 cd = __fmul2_rn(unpack_bf16(sC2[sl * bstep2]), ex2f2(acc));
+            float2 bd = __fmul2_rn(__fmul2_rn(unpack_bf16(sB2[sl * bstep2]), dtv[j]), ex2f2_neg(acc));
+            if (!kFull && l >= rows) { cd = f2(0.f); bd = f2(0.f); }
+            const uint32_t off = (uint32_t)(j * 128 + ((kc ^ (j & 7)) << 4));
+            *(uint32_t*)(cd_col + off) = pack_bf16(cd);
+            *(uint32_t*)(bd_col + off) = pack_bf16(bd);
+          }
+        };
+        if (rows == QB) phaseB2(std::true_type{}); else phaseB2(std::false_type{});
+        fence_async_smem();
+      };
+
       // ---- column threads: g' = 2^(a_last) G: back into TMEM for the accumulate MMA, bf16 copy as operand row -------
       auto gprime = [&]() {
         float gc[HP];
@@ -628,9 +706,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           }
         }
         sXch[half * NT + n] = part;
+        if constexpr (!kWin) sXch[(2 + half) * NT + n] = cpart_own;
         named_barrier(1 + (warp & (NT / 32 - 1)), 64);
         const float p0 = sXch[n];
         const float total = p0 + sXch[NT + n];
+        if constexpr (!kWin) cst = sXch[2 * NT + n] + sXch[3 * NT + n];   // <S leaving the block, G> of column n
         // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
         const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
         const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
@@ -681,6 +761,117 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         if (first && rows == QB) epi(std::true_type{}); else epi(std::false_type{});
       };
 
+      // ---- fast instantiation: the same (row, state) epilogue over the whole block with the rows taken two at a time,
+      //      so that the fp32 arithmetic runs as packed pairs (the running sums along the rows stay scalar) -------------
+      auto epilogue_a_pairs = [&]() {
+        const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev);
+        const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
+        const int dstep = flipT ? -NT : NT;
+        const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
+        const int bstep = flipB ? -NT : NT;
+        const uint8_t* cd_col = smem + SM::kCd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const uint8_t* bd_col = smem + SM::kBd + (n >> 6) * (QB * 128) + half * (32 * 128) + ((kcol & 7) << 1);
+        const int kc = kcol >> 3;
+        auto opnd = [&](const uint8_t* col, int r) {      // rows r, r + 1 of this thread's column of an operand tile
+          return f2(__bfloat162float(*(const bf16*)(col + (uint32_t)(r * 128 + ((kc ^ (r & 7)) << 4)))),
+                    __bfloat162float(*(const bf16*)(col + (uint32_t)((r + 1) * 128 + ((kc ^ ((r + 1) & 7)) << 4)))));
+        };
+        float2 part2 = f2(0.f);                            // sum over this thread's rows of dacs = Cd CD - Bd BD
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          float bdv[8], cdv[8];
+          tmem_ld8(t_BD + ch * 8, bdv);
+          tmem_ld8(t_CD + ch * 8, cdv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            part2 = __ffma2_rn(opnd(cd_col, ch * 8 + j), f2(cdv[j], cdv[j + 1]), part2);
+            part2 = __ffma2_rn(opnd(bd_col, ch * 8 + j), f2(-bdv[j], -bdv[j + 1]), part2);
+          }
+        }
+        sXch[half * NT + n] = part2.x + part2.y;
+        sXch[(2 + half) * NT + n] = cpart_own;
+        named_barrier(1 + (warp & (NT / 32 - 1)), 64);
+        const float p0 = sXch[n];
+        const float total = p0 + sXch[NT + n];
+        cst = sXch[2 * NT + n] + sXch[3 * NT + n];         // <S leaving the block, G> of column n
+        const float base = cst + total;                    // ddA[l] = base - sum of dacs over the rows before l
+        const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
+        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        TDT* const p_ddt = (TDT*)a.ddt + o0;
+        uint32_t* const p_dBC = a.dBCh + o0;
+        const float biasL = bias * (a.softplus ? LOG2E : 1.f);
+        auto epi = [&](auto full) {
+          constexpr bool kFull = decltype(full)::value;
+          float prefix = half ? p0 : 0.f;
+          float ac = half ? a0 : 0.f;
+          float2 dA2 = f2(0.f), db2 = f2(0.f);
+#pragma unroll 2
+          for (int ch = 0; ch < 4; ++ch) {
+            float bdv[8], cdv[8];
+            tmem_ld8(t_BD + ch * 8, bdv);
+            tmem_ld8(t_CD + ch * 8, cdv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              const int l = half * 32 + ch * 8 + j;
+              const int s0 = kFull ? l : min(l, rows - 1), s1 = kFull ? l + 1 : min(l + 1, rows - 1);
+              const bool in0 = kFull || l < rows, in1 = kFull || l + 1 < rows;
+              float2 raw;
+              if (kStageDt) raw = f2(__bfloat162float(sdt[s0 * dstep]), __bfloat162float(sdt[s1 * dstep]));
+              else raw = f2(ldf(dtp + (int64_t)trow(a, row0 + s0) * a.dt_sl + n), ldf(dtp + (int64_t)trow(a, row0 + s1) * a.dt_sl + n));
+              // dt transform (see dt_transform2) keeping the unclamped value: no gradient flows through a clamped dt
+              float2 v;
+              if (a.softplus) {
+                const float2 t = __ffma2_rn(raw, f2(LOG2E), f2(biasL));
+                float2 sp = lg2f2(__fadd2_rn(ex2f2(t), f2(1.f)));
+                sp.x = t.x <= 20.f * LOG2E ? sp.x : t.x;
+                sp.y = t.y <= 20.f * LOG2E ? sp.y : t.y;
+                v = __fmul2_rn(sp, f2(LN2));
+              } else {
+                v = __fadd2_rn(raw, f2(biasL));
+              }
+              float2 dtl = f2(fminf(fmaxf(v.x, a.dtmin), a.dtmax), fminf(fmaxf(v.y, a.dtmin), a.dtmax));
+              const bool cl0 = dtl.x != v.x, cl1 = dtl.y != v.y;
+              if (!in0) dtl.x = 0.f;
+              if (!in1) dtl.y = 0.f;
+              const float ac0 = fmaf(dtl.x, A2, ac);
+              ac = fmaf(dtl.y, A2, ac0);
+              const float2 e = f2(ac0, ac);
+              const float2 bdv2 = f2(bdv[j], bdv[j + 1]), cdv2 = f2(cdv[j], cdv[j + 1]);
+              const float2 bd = __fmul2_rn(ex2f2_neg(e), bdv2), cd = __fmul2_rn(ex2f2(e), cdv2);
+              const float2 tb = __fmul2_rn(opnd(bd_col, ch * 8 + j), bdv2);
+              const float2 co = opnd(cd_col, ch * 8 + j);
+              const float dacs0 = fmaf(co.x, cdv2.x, -tb.x), dacs1 = fmaf(co.y, cdv2.y, -tb.y);
+              const float ddA0 = base - prefix;              // sum of dacs over rows >= l, plus <S_next, G>
+              prefix += dacs0;
+              const float ddA1 = base - prefix;
+              prefix += dacs1;
+              const float2 ddA = f2(ddA0, ddA1);
+              const float2 Bv = f2(__bfloat162float(sB[s0 * bstep]), __bfloat162float(sB[s1 * bstep]));
+              float2 gd = __ffma2_rn(ddA, f2(Anat), __fmul2_rn(Bv, bd));
+              if (a.softplus) gd = __fmul2_rn(gd, __ffma2_rn(ex2f2(__fmul2_rn(dtl, f2(-LOG2E))), f2(-1.f), f2(1.f)));
+              if (cl0) gd.x = 0.f;
+              if (cl1) gd.y = 0.f;
+              const float2 dBh = __fmul2_rn(dtl, bd);
+              if (kFull) {
+                dA2 = __ffma2_rn(ddA, dtl, dA2);
+                db2 = __fadd2_rn(db2, gd);
+              } else {
+                if (in0) { dA2.x = fmaf(ddA0, dtl.x, dA2.x); db2.x += gd.x; }
+                if (in1) { dA2.y = fmaf(ddA1, dtl.y, dA2.y); db2.y += gd.y; }
+              }
+              const int o = l * ostep;
+              if (in0) { stf(p_ddt + o, gd.x); p_dBC[o] = pack_bf16(dBh.x, cd.x); }               // one store for the pair {dB_h, dC_h}
+              if (in1) { stf(p_ddt + o + ostep, gd.y); p_dBC[o + ostep] = pack_bf16(dBh.y, cd.y); }
+            }
+          }
+          dAacc += dA2.x + dA2.y;
+          dbacc += db2.x + db2.y;
+        };
+        if (rows == QB) epi(std::true_type{}); else epi(std::false_type{});
+      };
+
       // ---- column threads, epilogue (b): dx rows -> shared memory (every warp takes 16-column groups of its 16 rows) ----
       auto epilogue_b = [&](int w0, int w1, bool first) {
         const int l = (warp & 3) * 16 + lane;
@@ -721,9 +912,15 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         }
       }
       if (kStageDt && !mbar_wait_warp(barS, parity)) failed = true;
-      phaseAB(0, rows, true, cpart);
+      if constexpr (kWin) phaseAB(0, rows, true, cpart);
+      else phaseAB_pairs();
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
+      if constexpr (!kWin) {                               // summed decay of this thread's own column n (see phaseAB_pairs)
+        a0 = sXch[n] + sXch[NT + n];
+        alast = (a0 + sXch[2 * NT + n]) + sXch[3 * NT + n];
+        cpart_own = cpart;                                 // joins the other half's part in the epilogue's exchange
+      }
       // windowed kernel: has some column asked for this block to be cut into 2^kw windows?
       int kw = 0;
       if (kWin) {
@@ -742,12 +939,17 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       // dx / dz rows of the previous block, while the second MMA phase is issued
-      if (it > 0) finish_groups(std::integral_constant<int, kColGroups / NTH>{}, row0 + QB, min(QB, a.L - row0 - QB), tid, NTH);
+      if (it > 0) {
+#pragma unroll
+        for (int r = 0; r < kColR; ++r)
+          group_store(group_load(row0 + QB, min(QB, a.L - row0 - QB), tid + r * NTH), row0 + QB, min(QB, a.L - row0 - QB));
+      }
       if (kw == 0) {
         if (!mbar_wait_warp(bar2, kWin ? (c2 & 1) : parity)) failed = true;
         fence_after_sync();
         if (!failed) {
-          epilogue_a(0, rows, true);
+          if constexpr (kWin) epilogue_a(0, rows, true);
+          else epilogue_a_pairs();
           asm volatile("bar.arrive 10, %0;" ::"r"(NTH + 32) : "memory");      // B staging reads are done
           named_barrier(9, NTH + NIO);                     // the previous block's dx rows have left the tile
           if (!mbar_wait_warp(bar2b, kWin ? (c2 & 1) : parity)) failed = true;

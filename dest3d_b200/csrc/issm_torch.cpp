@@ -139,7 +139,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> fwd(const Tensor& x, const Tensor& dt
   Tensor out_x = z ? at::empty(c.x.sizes(), opt) : none_like(out);
   Tensor fin = want_final ? at::empty({p.batch, p.nheads, p.headdim, p.dstate}, opt.dtype(at::kFloat)) : none_like(out);
   Tensor saved = none_like(out);
-  if (save_states && issm_b200_resolve_path(&p) == ISSM_PATH_TENSOR) {
+  if (save_states && issm_b200_resolve_path_pass(&p, 1) == ISSM_PATH_TENSOR) {
     // the tensor-core backward reads the state entering every 64-point block instead of recomputing it
     saved = at::empty({p.batch, p.nheads, (p.seqlen + 63) / 64 + 1, p.dstate, 48}, opt.dtype(at::kBFloat16));
     p.saved_states = saved.data_ptr();

@@ -207,7 +207,7 @@ def issm_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_s
     p, keep = _fill_common(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus,
                            dt_limit, reverse, path)
     saved = None
-    if save_states and _lib.lib().issm_b200_resolve_path(ct.byref(p)) == _lib.PATH_TENSOR:
+    if save_states and _lib.lib().issm_b200_resolve_path_pass(ct.byref(p), 1) == _lib.PATH_TENSOR:
         # the tensor-core backward reads the state entering every 64-point block instead of recomputing it
         saved = _empty((x.shape[0], x.shape[2], (x.shape[1] + 63) // 64 + 1, B.shape[-1], 48), torch.bfloat16, x.device)
         p.saved_states = saved.data_ptr()

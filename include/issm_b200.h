@@ -146,8 +146,13 @@ size_t issm_b200_sizeof_norm_params(void);
  * an aligned call that passes saved_states iff it is non-null in the query. */
 size_t issm_b200_workspace_bytes(const issm_params* p, int pass);
 
-/* Which path (ISSM_PATH_SIMT or ISSM_PATH_TENSOR) a call with these sizes would take. */
+/* Which path (ISSM_PATH_SIMT or ISSM_PATH_TENSOR) a forward call with these sizes would take; -1 when the
+ * requested path does not cover them. */
 int issm_b200_resolve_path(const issm_params* p);
+/* The same per pass (0 = forward, 1 = backward).  They can differ: for dstate 512 / 768 / 1024 the forward runs
+ * on the tensor-core kernels (one 256-state slice per CTA, partial outputs summed by a combine kernel) while the
+ * backward runs on the SIMT kernels; `saved_states` is only of use when the BACKWARD takes the tensor path. */
+int issm_b200_resolve_path_pass(const issm_params* p, int pass);
 
 int issm_b200_fwd(const issm_params* p, void* cuda_stream);
 int issm_b200_bwd(const issm_params* p, void* cuda_stream);

@@ -41,15 +41,19 @@ def test_c1_bidirectional_layer_with_gated_rmsnorm(dtype, path):
                                        dt_limit=(1e-3, 1e-1), path=path)
     yn2 = norm(y2.reshape(b, L, H * P), Cc["z"].reshape(b, L, H * P))
     ((yn2.float() * dout.cuda().float()).sum() + (fin2 * inp["dfinal"].cuda()).sum()).backward()
-    parity.close(yn2, yn, dtype, "normed out")
+    # the scan's outputs literally; what passes through the norm (which divides by the row RMS and so amplifies the
+    # error its input carries) relative to the reference tensor's largest magnitude
+    parity.close(y2, y, dtype, "out", literal=False)       # average of two scans that can cancel (each is checked literally elsewhere)
     parity.close(fin2, fin, dtype, "final")
+    parity.close(yn2, yn, dtype, "normed out", literal=False)
     parity.close(norm.weight.grad, R["w"].grad, dtype, "dW")
     for k in names[:-1]:
-        parity.close(Cc[k].grad, R[k].grad, dtype, "d" + k)
+        parity.close(Cc[k].grad, R[k].grad, dtype, "d" + k, literal=False)
 
 
 @pytest.mark.parametrize("dtype,path,N,Q", [(torch.bfloat16, "tensor", 256, 128), (torch.float32, "simt", 512, 128),
-                                             (torch.bfloat16, "simt", 512, 128)], ids=["bf16_tensor_n256", "f32_n512", "bf16_n512"])
+                                             (torch.bfloat16, "simt", 512, 128), (torch.bfloat16, "tensor", 512, 128)],
+                         ids=["bf16_tensor_n256", "f32_n512", "bf16_n512", "bf16_tensor_n512"])
 def test_c2_stacked_layers_chain_states(dtype, path, N, Q):
     from dest3d_b200 import ISSM_chunk_scan_combined
     b, L, H, P, layers = 1, 192, 2, 36, 3

@@ -69,8 +69,11 @@ def oracle_scan(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initia
     return (out, fin) if return_final_states else out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16_autocast"])
 def test_reference_caller_through_the_shim(dest_module, dtype):
+    """float32: parameters and activations in float32 (fp32 kernels), nominal float32 tolerance.  bfloat16: the
+    float32 module under torch.autocast, as the detector is trained: x, B, C, z and the initial states reach the
+    scan in bfloat16 and dt in float32 (autocast keeps softplus in float32), which is the tensor-core path."""
     dm = dest_module
     torch.manual_seed(0)
     batch, L, K, d_model, d_dist, nheads = 1, 384, 256, 144, 16, 8           # d_inner 288 = 8 heads x 36, 256 query states
@@ -81,9 +84,7 @@ def test_reference_caller_through_the_shim(dest_module, dtype):
         gpu.D.copy_(torch.randn(nheads))
         gpu.key_norm.weight.copy_(1 + 0.02 * torch.randn(2 * d_model))
         gpu.dt_proj.weight.mul_(0.2)
-    # both runs start from the same parameters, rounded to the dtype the GPU module holds them in
-    state = {k: v.detach().to(dtype).float() for k, v in gpu.state_dict().items()}
-    gpu.load_state_dict(state)
+    state = {k: v.detach().clone() for k, v in gpu.state_dict().items()}
     in_key, in_query = torch.randn(batch, L, d_model), torch.randn(batch, K, d_model) / 4
     dist, xyz = torch.randn(batch, L, K, d_dist), torch.randn(batch, L, 3)
     mask = (torch.rand(batch, L, K) > 0.1).float()
@@ -98,19 +99,32 @@ def test_reference_caller_through_the_shim(dest_module, dtype):
         dm.RMSNormGated = real_norm
     ref.load_state_dict(state)
     ref = ref.double()
-    cast = lambda t: t.to(dtype).double()                     # the oracle sees the inputs as the GPU run rounds them
+    cast = lambda t: t.double()
     try:
         ok_ref, oq_ref = ref(cast(in_key), cast(in_query), cast(dist), cast(xyz), mask)   # float32 mask: the multiply branch (dest_module.py:556-557)
         ((ok_ref * gk.double()).sum() + (oq_ref * gq.double()).sum()).backward()
     finally:
         dm.ISSM_chunk_scan_combined = real_scan
 
-    gpu = gpu.cuda().to(dtype)
-    c = lambda t: t.to(dtype).cuda()
+    gpu = gpu.cuda()
+    c = lambda t: t.cuda()
     torch.backends.cudnn.allow_tf32 = False                  # the module's depthwise convolution, in float32
     torch.backends.cuda.matmul.allow_tf32 = False
-    ok, oq = gpu(c(in_key), c(in_query), c(dist), c(xyz), mask.cuda())     # float32 mask: dt = softplus(...) * mask
-    ((ok.float() * gk.cuda()).sum() + (oq.float() * gq.cuda()).sum()).backward()
+    seen = []
+    real = dm.ISSM_chunk_scan_combined
+
+    def spy(x, dt, *a, **k):
+        seen.append((x.dtype, dt.dtype))
+        return real(x, dt, *a, **k)
+
+    dm.ISSM_chunk_scan_combined = spy
+    try:
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+            ok, oq = gpu(c(in_key), c(in_query), c(dist), c(xyz), mask.cuda())     # float32 mask: dt = softplus(...) * mask
+        ((ok.float() * gk.cuda()).sum() + (oq.float() * gq.cuda()).sum()).backward()
+    finally:
+        dm.ISSM_chunk_scan_combined = real
+    assert seen == [(dtype, torch.float32)] * 2, seen        # both scan directions, in the expected dtypes
     rep = []
     loosen = 1.0 if dtype == torch.float32 else 4.0           # bf16 linear layers around the scan add their own rounding
     parity.close(ok, ok_ref, dtype, "out_key", rep, loosen, literal=False)

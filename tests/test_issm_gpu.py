@@ -86,6 +86,30 @@ def test_parity_tensor(case):
     parity.compare(got, ref, torch.bfloat16, want_final=opts.get("return_final", True))
 
 
+@pytest.mark.parametrize("shape", [(1, 384, 2, 36, 512, 1, 128), (2, 200, 3, 32, 768, 1, 64), (1, 130, 2, 36, 1024, 1, 256)],
+                         ids=["n512", "n768", "n1024"])
+@pytest.mark.parametrize("reverse", [False, True], ids=["forward_scan", "reversed_scan"])
+def test_parity_more_than_256_states(shape, reverse):
+    """dstate 512 / 768 / 1024 (bf16): the forward runs on the tensor-core kernels, one 256-state slice per CTA with
+    the partial outputs summed by the combine kernel; the backward of these sizes runs on the SIMT kernels."""
+    import ctypes as ct
+    from dest3d_b200 import _lib, issm_combined
+    b, L, H, P, N, G, Q = shape
+    inp = O.make_inputs(b, L, H, P, N, G=G, seed=N + L, dtype=torch.bfloat16)
+    opts = dict(BENCH_OPTS, reverse=reverse)
+    c = {k: v.cuda() for k, v in inp.items() if torch.is_tensor(v)}
+    prm, _ = issm_combined._fill_common(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, c["D"], c["z"], c["dt_bias"], c["initial_states"],
+                                        True, (1e-3, 1e-1), reverse, "auto")
+    assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(prm), 0) == _lib.PATH_TENSOR
+    assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(prm), 1) == _lib.PATH_SIMT
+    ref = parity.oracle_run(inp, 64, opts)
+    issm_combined.device_status()
+    got = parity.cuda_run(inp, Q, opts, path="auto")
+    assert issm_combined.device_status() == 0
+    rep = parity.compare(got, ref, torch.bfloat16)
+    print(f"dstate {N}", parity.format_report(rep))
+
+
 # dt = softplus(scale * raw + offset) with |A| up to 16: the summed decay of a 64-point block leaves the range
 # of the single-reference factorisation (2^120), so the windowed kernels redo those streams
 WINDOWED_CASES = [
@@ -207,7 +231,7 @@ def test_bad_arguments_raise():
     from dest3d_b200 import ISSM_chunk_scan_combined, _lib
     inp, Q = _inputs((1, 64, 2, 8, 16, 1, 16), {}, BENCH_OPTS, torch.float32)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
-    with pytest.raises(_lib.IssmError):
+    with pytest.raises(RuntimeError, match="error 2"):                               # ISSM_ERR_SHAPE from the C ABI
         ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], 512)          # chunk_size > 256
     with pytest.raises(NotImplementedError):
         ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, seq_idx=torch.zeros(1, 64, dtype=torch.int32))
