@@ -407,6 +407,19 @@ def kernel_roofline(dev, par, dfinal, w, batch, path, dtype):
         tnb, _, _ = _median_ms(lambda: torch.autograd.grad(y, (xk, zk, wk), dy, retain_graph=True))
         out.update({"norm_fwd_ms": tnf, "norm_bwd_ms": tnb, "norm_fwd_frac": nf / (tnf * 1e-3) / 1e9 / hbm,
                     "norm_bwd_frac": nb / (tnb * 1e-3) / 1e9 / hbm})
+        # the same two kernels on 2^18 rows (151 MB per tensor, larger than L2): at the detector's 8192 rows a call
+        # moves 14 MB and is bound by launch latency, not by HBM
+        rows = 1 << 18
+        g = torch.Generator(device="cuda").manual_seed(3)
+        xl = torch.randn(rows, H * P, device="cuda", generator=g).to(dtype).requires_grad_()
+        zl = torch.randn(rows, H * P, device="cuda", generator=g).to(dtype).requires_grad_()
+        dyl = torch.randn(rows, H * P, device="cuda", generator=g).to(dtype)
+        nfl, nbl = norm_bytes(rows, H * P, e)
+        tl_f, _, yl = _median_ms(lambda: rmsnorm_fn(xl, wk, None, zl, eps=1e-5, norm_before_gate=False))
+        tl_b, _, _ = _median_ms(lambda: torch.autograd.grad(yl, (xl, zl, wk), dyl, retain_graph=True))
+        out.update({"norm_large_rows": rows, "norm_large_fwd_ms": tl_f, "norm_large_bwd_ms": tl_b,
+                    "norm_large_fwd_frac": nfl / (tl_f * 1e-3) / 1e9 / hbm, "norm_large_bwd_frac": nbl / (tl_b * 1e-3) / 1e9 / hbm})
+        del xl, zl, dyl, yl
     which = max(stages, key=lambda k: stages[k][0])
     t, nbytes, tag = stages[which]
     ach = nbytes / (t * 1e-3) / 1e9

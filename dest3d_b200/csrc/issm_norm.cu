@@ -1,7 +1,13 @@
 // Gated RMS / Layer norm, forward and backward (issm_triton/layernorm_gated.py:35-95, 145-258).
-// Memory-bound: one warp per row, features strided over lanes, statistics by warp shuffles.
-// Weight/bias gradients are accumulated per warp in shared memory without atomics and reduced
-// over blocks in a fixed order, so results are bitwise reproducible.
+// Memory-bound: one warp per row, statistics by warp shuffles.  Two families of kernels:
+//  * k_norm_fwd_vec / k_norm_bwd_vec: one statistics group per row (the detector's case), rows that fit the warp's
+//    registers and 16-byte aligned rows: every tensor is read ONCE with 128-bit loads, the row lives in registers
+//    between the statistics and the output, and the weight / bias gradients accumulate in registers over the rows
+//    of a warp (a lane always owns the same features);
+//  * k_norm_fwd / k_norm_bwd: any group size, width and alignment (features strided over lanes, per-warp
+//    shared-memory accumulators).
+// Weight/bias gradients are reduced over warps and blocks in a fixed order without atomics, so results are
+// bitwise reproducible.
 #include "issm_common.cuh"
 
 namespace issm {
@@ -60,7 +66,219 @@ __global__ void k_norm_fwd(issm_norm_params np) {
   }
 }
 
+// ---- vector kernels ------------------------------------------------------------------------------------
+// 16 bytes of a row as floats: 8 bf16 or 4 float values
+template <typename T> struct Vec16;
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const bf16* p, float* v) {
+    const uint4 w = *(const uint4*)p;
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(u[i] << 16); v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float* v) {
+    uint32_t u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      u[i] = *(const uint32_t*)&h;
+    }
+    *(uint4*)p = make_uint4(u[0], u[1], u[2], u[3]);
+  }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 w = *(const float4*)p;
+    v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+};
+
+// Chunk c of lane `lane` covers features [(c * 32 + lane) * V, +V); CH chunks per lane cover up to 32 * V * CH features.
+template <typename T, int CH>
+__global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
+  constexpr int V = Vec16<T>::N;
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= np.rows) return;
+  const int H = np.hidden;
+  const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
+  const T* z = np.has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
+  T* y = (T*)np.y + (int64_t)row * np.y_sr;
+  const bool pre_gate = z && !np.norm_before_gate, post_gate = z && np.norm_before_gate;
+  float v[CH][V], zg[CH][V];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int f0 = (c * 32 + lane) * V;
+    if (f0 < H) {
+      Vec16<T>::load(x + f0, v[c]);
+      if (z) Vec16<T>::load(z + f0, zg[c]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        if (z) zg[c][i] = siluf_(zg[c][i]);
+        if (pre_gate) v[c][i] *= zg[c][i];
+        s1 += v[c][i];
+        s2 = fmaf(v[c][i], v[c][i], s2);
+      }
+    }
+  }
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  float mean = 0.f, var;
+  if (np.is_rms) {
+    var = s2 / H;
+  } else {
+    mean = s1 / H;
+    float sv = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+      if ((c * 32 + lane) * V < H) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) sv = fmaf(v[c][i] - mean, v[c][i] - mean, sv);
+      }
+    var = warp_sum(sv) / H;
+  }
+  const float rstd = rsqrtf(var + np.eps);
+  if (lane == 0) {
+    np.rstd[row] = rstd;
+    if (!np.is_rms && np.mean) np.mean[row] = mean;
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int f0 = (c * 32 + lane) * V;
+    if (f0 < H) {
+      float w[V], o[V];
+      Vec16<float>::load(np.weight + f0, w);
+      if (V == 8) Vec16<float>::load(np.weight + f0 + 4, w + 4);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        o[i] = (v[c][i] - mean) * rstd * w[i];
+        if (np.has_bias) o[i] += np.bias[f0 + i];
+        if (post_gate) o[i] *= zg[c][i];
+      }
+      Vec16<T>::store(y + f0, o);
+    }
+  }
+}
+
 constexpr int NORM_BWD_WARPS = 4;
+
+// grid = nblk blocks of NORM_BWD_WARPS warps; block i handles rows [i*rpb, (i+1)*rpb); partial dw/db -> (nblk, hidden)
+template <typename T, int CH>
+__global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_params np, int rpb, float* __restrict__ dwpart,
+                                                                        float* __restrict__ dbpart) {
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ float sm[];                          // [2][NORM_BWD_WARPS][hidden]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = np.hidden;
+  const bool pre_gate = np.has_z && !np.norm_before_gate, post_gate = np.has_z && np.norm_before_gate;
+  float dwacc[CH][V], dbacc[CH][V], w[CH][V];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int f0 = (c * 32 + lane) * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) { dwacc[c][i] = 0.f; dbacc[c][i] = 0.f; w[c][i] = f0 < H ? np.weight[f0 + i] : 0.f; }
+  }
+  const int r_end = min(np.rows, (int)(blockIdx.x + 1) * rpb);
+  for (int row = blockIdx.x * rpb + warp; row < r_end; row += NORM_BWD_WARPS) {
+    const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
+    const T* z = np.has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
+    const T* dy = (const T*)np.dy + (int64_t)row * np.dy_sr;
+    T* dx = (T*)np.dx + (int64_t)row * H;
+    T* dz = np.has_z ? (T*)np.dz + (int64_t)row * H : nullptr;
+    const float rstd = np.rstd[row];
+    const float mean = np.is_rms ? 0.f : np.mean[row];
+    float xr[CH][V], zv[CH][V], go[CH][V];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int f0 = (c * 32 + lane) * V;
+      if (f0 < H) {
+        Vec16<T>::load(x + f0, xr[c]);
+        Vec16<T>::load(dy + f0, go[c]);
+        if (z) Vec16<T>::load(z + f0, zv[c]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float vv = pre_gate ? xr[c][i] * siluf_(zv[c][i]) : xr[c][i];
+          const float xh = (vv - mean) * rstd;
+          const float g_out = post_gate ? go[c][i] * siluf_(zv[c][i]) : go[c][i];
+          const float wdy = g_out * w[c][i];
+          c1 = fmaf(xh, wdy, c1);
+          c2 += wdy;
+        }
+      }
+    }
+    c1 = warp_sum(c1) / H;
+    c2 = np.is_rms ? 0.f : warp_sum(c2) / H;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int f0 = (c * 32 + lane) * V;
+      if (f0 < H) {
+        float odx[V], odz[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float zz = z ? zv[c][i] : 0.f;
+          const float sz = z ? siluf_(zz) : 1.f;
+          const float vv = pre_gate ? xr[c][i] * sz : xr[c][i];
+          const float xh = (vv - mean) * rstd;
+          const float g_out = post_gate ? go[c][i] * sz : go[c][i];
+          const float wdy = g_out * w[c][i];
+          const float dv = (wdy - xh * c1 - c2) * rstd;
+          dwacc[c][i] = fmaf(g_out, xh, dwacc[c][i]);
+          dbacc[c][i] += g_out;
+          if (pre_gate) {
+            odx[i] = dv * sz;
+            odz[i] = dv * xr[c][i] * dsiluf_(zz);
+          } else {
+            odx[i] = dv;
+            float yv = xh * w[c][i];
+            if (np.has_bias) yv += np.bias[f0 + i];
+            odz[i] = post_gate ? go[c][i] * yv * dsiluf_(zz) : 0.f;
+          }
+        }
+        Vec16<T>::store(dx + f0, odx);
+        if (z) Vec16<T>::store(dz + f0, odz);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int f0 = (c * 32 + lane) * V;
+    if (f0 < H) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        sm[(size_t)warp * H + f0 + i] = dwacc[c][i];
+        sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + f0 + i] = dbacc[c][i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int f = threadIdx.x; f < H; f += blockDim.x) {
+    float a = 0.f, b = 0.f;
+    for (int wq = 0; wq < NORM_BWD_WARPS; ++wq) {
+      a += sm[(size_t)wq * H + f];
+      b += sm[(size_t)NORM_BWD_WARPS * H + (size_t)wq * H + f];
+    }
+    dwpart[(size_t)blockIdx.x * H + f] = a;
+    dbpart[(size_t)blockIdx.x * H + f] = b;
+  }
+}
+
+// chunks per lane the vector kernels need for this call, or 0 when it has to take the general kernels
+static int norm_vec_chunks(const issm_norm_params& p, bool bwd) {
+  const int V = p.io_dtype == ISSM_BF16 ? 8 : 4, esz = p.io_dtype == ISSM_BF16 ? 2 : 4;
+  if (p.group_size != p.hidden || p.hidden % V) return 0;
+  auto ok = [&](const void* ptr, int64_t stride) { return ((uintptr_t)ptr % 16 == 0) && ((stride * esz) % 16 == 0); };
+  if (!ok(p.x, p.x_sr) || (p.has_z && !ok(p.z, p.z_sr)) || ((uintptr_t)p.weight % 16)) return 0;
+  if (!bwd && !ok(p.y, p.y_sr)) return 0;
+  if (bwd && (!ok(p.dy, p.dy_sr) || !ok(p.dx, p.hidden) || (p.has_z && !ok(p.dz, p.hidden)))) return 0;
+  const int need = (p.hidden + 32 * V - 1) / (32 * V);
+  return need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 0;
+}
+
+
 
 // grid = nblk blocks; block i handles rows [i*rpb, (i+1)*rpb); partial dw/db -> ws (nblk, hidden)
 template <typename T>
@@ -157,6 +375,24 @@ static int norm_validate(const issm_norm_params* p, bool bwd) {
   return ISSM_OK;
 }
 
+// the backward main kernel of one call (vector kernels when the call qualifies, see norm_vec_chunks)
+static int launch_norm_bwd_main(const issm_norm_params& p, int nblk, int rpb, float* dwpart, float* dbpart, size_t smem, cudaStream_t s) {
+  const int ch = norm_vec_chunks(p, true);
+#define ISSM_NORM_BWD_VEC(T)                                                                                          \
+  do {                                                                                                                \
+    if (ch == 1) ISSM_LAUNCH((k_norm_bwd_vec<T, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);      \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_bwd_vec<T, 2>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart); \
+    else ISSM_LAUNCH((k_norm_bwd_vec<T, 4>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);              \
+  } while (0)
+  if (ch) {                                               // rows of at most 1024 (bf16) / 512 (float) features: 32 KiB of shared memory at most
+    if (p.io_dtype == ISSM_F32) ISSM_NORM_BWD_VEC(float); else ISSM_NORM_BWD_VEC(bf16);
+    return ISSM_OK;
+  }
+  if (p.io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);
+  else ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);
+  return ISSM_OK;
+}
+
 }  // namespace issm
 
 using namespace issm;
@@ -173,6 +409,17 @@ extern "C" int issm_b200_norm_fwd(const issm_norm_params* p, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   const int wpb = 8;
   const unsigned grid = (p->rows + wpb - 1) / wpb;
+  const int ch = norm_vec_chunks(*p, false);
+#define ISSM_NORM_FWD_VEC(T)                                                                                   \
+  do {                                                                                                         \
+    if (ch == 1) ISSM_LAUNCH((k_norm_fwd_vec<T, 1>), grid, wpb * 32, 0, s, *p);                                \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_fwd_vec<T, 2>), grid, wpb * 32, 0, s, *p);                           \
+    else ISSM_LAUNCH((k_norm_fwd_vec<T, 4>), grid, wpb * 32, 0, s, *p);                                        \
+  } while (0)
+  if (ch) {
+    if (p->io_dtype == ISSM_F32) ISSM_NORM_FWD_VEC(float); else ISSM_NORM_FWD_VEC(bf16);
+    return ISSM_OK;
+  }
   if (p->io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_fwd<float>), grid, wpb * 32, 0, s, *p);
   else ISSM_LAUNCH((k_norm_fwd<bf16>), grid, wpb * 32, 0, s, *p);
   return ISSM_OK;
@@ -197,8 +444,8 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
     if ((p->io_dtype == ISSM_F32 ? SmemAttrOnce<F32Tag>::set(k_norm_bwd<float>, lim) : SmemAttrOnce<BF16Tag>::set(k_norm_bwd<bf16>, lim)) != ISSM_OK)
       return ISSM_ERR_CUDA;
   }
-  if (p->io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
-  else ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  rc = launch_norm_bwd_main(*p, nblk, rpb, dwpart, dbpart, smem, s);
+  if (rc) return rc;
   ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
   if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;
@@ -255,8 +502,8 @@ extern "C" int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* strea
   float* dbpart = scratch + (size_t)nblk * p->hidden;
   const size_t smem = (size_t)2 * NORM_BWD_WARPS * p->hidden * sizeof(float);   // <= 32 KiB here
   // every block writes its whole row of partials, so nothing in the scratch has to start at zero
-  if (p->io_dtype == ISSM_F32) ISSM_LAUNCH((k_norm_bwd<float>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
-  else ISSM_LAUNCH((k_norm_bwd<bf16>), nblk, NORM_BWD_WARPS * 32, smem, s, *p, rpb, dwpart, dbpart);
+  rc = launch_norm_bwd_main(*p, nblk, rpb, dwpart, dbpart, smem, s);
+  if (rc) return rc;
   ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
   if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;

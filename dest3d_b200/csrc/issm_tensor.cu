@@ -87,7 +87,7 @@ __device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c)
   constexpr int NTH = 2 * NT, HP = PP / 2;
   uint8_t* smem = c.smem;
   const int n = c.n, half = c.half, rows = c.rows, kcol = n & 63;
-  const bool flipT = a.dt_tma && a.rev, flipB = a.bc_contig && a.rev;
+  const bool flipT = a.dt_tma && a.rev, flipB = (a.bc_contig || a.bc_tma) && a.rev;
   const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
   const int dstep = flipT ? -NT : NT;
   const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
@@ -167,7 +167,7 @@ __device__ __noinline__ void fwd_windowed_passes(const TArgs& a, WinCtx<TDT>& c)
 // 1 = dt / B / C tiles staged in scan order (forward scan of regular arrays), 2 = staged in memory order for a
 // reversed scan (walked backwards), 0 = decided at run time (row-by-row copies, mixed layouts).
 template <int NT, typename TDT, bool kWin, int kMode>
-__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ CUtensorMap dtmap) {
+__global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_constant__ TArgs a, const __grid_constant__ FwdMaps maps) {
   using SM = FwdSmem<NT>;
   constexpr bool kStageDt = sizeof(TDT) == 2;
   constexpr int NTH = 2 * NT;                           // column threads
@@ -228,17 +228,21 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     const bool dt_tile = kStageDt && a.dt_tma;
     const int64_t m0 = a.rev ? a.L - row0 - rows : row0;            // lowest memory row of the tile
-    if (lane == 0) mbar_expect_tx(barS, (uint32_t)rows * NT * 2 * 2 + (kStageDt ? (uint32_t)(dt_tile ? QB : rows) * NT * 2 : 0u));
+    // a tiled TMA load always delivers the whole 64-row box (rows past the array's end are filled with zeros)
+    if (lane == 0) mbar_expect_tx(barS, (uint32_t)(a.bc_tma ? QB : rows) * NT * 2 * 2 + (kStageDt ? (uint32_t)(dt_tile ? QB : rows) * NT * 2 : 0u));
     __syncwarp();
-    if (dt_tile && lane == 2) tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh + n_off, b * a.L + (int)m0, barS);
-    if (a.bc_contig) {
+    if (dt_tile && lane == 2) tma_load_2d(smem + SM::kSdt, &maps.dt, h * (int)a.dt_sh + n_off, b * a.L + (int)m0, barS);
+    if (a.bc_tma) {
+      if (lane == 0) tma_load_2d(smem + SM::kSB, &maps.B, g * (int)a.B_sg + n_off, b * a.L + (int)m0, barS);
+      if (lane == 1) tma_load_2d(smem + SM::kSC, &maps.C, g * (int)a.C_sg + n_off, b * a.L + (int)m0, barS);
+    } else if (a.bc_contig) {
       if (lane == 0) bulk_g2s(smem + SM::kSB, Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2, barS);
       if (lane == 1) bulk_g2s(smem + SM::kSC, Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2, barS);
     }
     for (int l = lane; l < rows; l += 32) {
       const int64_t mr = trow(a, row0 + l);
       if (kStageDt && !dt_tile) bulk_g2s(smem + SM::kSdt + l * NT * 2, (const bf16*)dtp + mr * a.dt_sl, NT * 2, barS);
-      if (!a.bc_contig) {
+      if (!a.bc_contig && !a.bc_tma) {
         bulk_g2s(smem + SM::kSB + l * NT * 2, Bp + mr * a.B_sl, NT * 2, barS);
         bulk_g2s(smem + SM::kSC + l * NT * 2, Cp + mr * a.C_sl, NT * 2, barS);
       }
@@ -249,8 +253,11 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
     if (blk >= nblk) return;
     const int row0 = blk * QB, rows = min(QB, a.L - row0);
     const int64_t m0 = a.rev ? a.L - row0 - rows : row0;
-    if (kStageDt && a.dt_tma && lane == 2) tma_prefetch_2d(&dtmap, h * (int)a.dt_sh + n_off, b * a.L + (int)m0);
-    if (a.bc_contig) {
+    if (kStageDt && a.dt_tma && lane == 2) tma_prefetch_2d(&maps.dt, h * (int)a.dt_sh + n_off, b * a.L + (int)m0);
+    if (a.bc_tma) {
+      if (lane == 0) tma_prefetch_2d(&maps.B, g * (int)a.B_sg + n_off, b * a.L + (int)m0);
+      if (lane == 1) tma_prefetch_2d(&maps.C, g * (int)a.C_sg + n_off, b * a.L + (int)m0);
+    } else if (a.bc_contig) {
       if (lane == 0) bulk_prefetch_l2(Bp + m0 * a.B_sl, (uint32_t)rows * NT * 2);
       if (lane == 1) bulk_prefetch_l2(Cp + m0 * a.C_sl, (uint32_t)rows * NT * 2);
     }
@@ -476,7 +483,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 
       // Staged tiles are addressed as base + l * step in units of rows: a tile that was copied in memory
       // order for a reversed scan is walked backwards.  Full blocks run a guard-free instantiation.
-      const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev), flipB = kMode ? kMode == 2 : (a.bc_contig && a.rev);
+      const bool flipT = kMode ? kMode == 2 : (a.dt_tma && a.rev), flipB = kMode ? kMode == 2 : ((a.bc_contig || a.bc_tma) && a.rev);
       const bf16* sdt = (const bf16*)(smem + SM::kSdt) + n + (flipT ? (rows - 1) * NT : 0);
       const int dstep = flipT ? -NT : NT;
       const bf16* sB = (const bf16*)(smem + SM::kSB) + n + (flipB ? (rows - 1) * NT : 0);
@@ -543,7 +550,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
         //      shared-memory access moves a bf16 pair (4 bytes) and the fp32 arithmetic runs as packed pairs --------
         constexpr int NPR = NT / 2;
         const int pr = tid % NPR, qr = tid / NPR;
-        const bool flipB2 = kMode ? kMode == 2 : (a.bc_contig && a.rev);
+        const bool flipB2 = kMode ? kMode == 2 : ((a.bc_contig || a.bc_tma) && a.rev);
         const uint32_t* sdt2 = (const uint32_t*)(smem + SM::kSdt) + pr + (flipT ? (rows - 1) * NPR : 0);
         const int dstep2 = flipT ? -NPR : NPR;
         const uint32_t* sB2 = (const uint32_t*)(smem + SM::kSB) + pr + (flipB2 ? (rows - 1) * NPR : 0);
@@ -829,26 +836,32 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
+bool make_rows_tensor_map(const void* base, int64_t sb, int64_t sl, int64_t width, int batch, int seqlen, int box_w, CUtensorMap* out) {
   memset(out, 0, sizeof(*out));
-  if (p.dt_dtype != ISSM_BF16) return false;
   // rows (b, l) must form one regular array: batch stride = seqlen * row stride; 16-byte aligned rows
-  if (p.dt_sb != (int64_t)p.seqlen * p.dt_sl || (p.dt_sl & 7) || (p.dt_sh & 7) || ((uintptr_t)p.dt & 15)) return false;
-  const uint64_t width = (uint64_t)(p.nheads - 1) * p.dt_sh + p.dstate;
-  if (width > (uint64_t)p.dt_sl || (uint64_t)p.batch * p.seqlen > 0x7fffffffull) return false;
+  if (!base || sb != (int64_t)seqlen * sl || (sl & 7) || ((uintptr_t)base & 15)) return false;
+  if (width > sl || width < box_w || (uint64_t)batch * seqlen > 0x7fffffffull) return false;
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
-  const cuuint64_t gdim[2] = {width, (cuuint64_t)p.batch * p.seqlen};
-  const cuuint64_t gstride[1] = {(cuuint64_t)p.dt_sl * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)(p.dstate > 256 ? 256 : p.dstate), (cuuint32_t)QB};   // one slice of the states per tile
+  const cuuint64_t gdim[2] = {(cuuint64_t)width, (cuuint64_t)batch * seqlen};
+  const cuuint64_t gstride[1] = {(cuuint64_t)sl * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)box_w, (cuuint32_t)QB};
   const cuuint32_t estr[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.dt), gdim, gstride, box, estr,
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out) {
+  memset(out, 0, sizeof(*out));
+  if (p.dt_dtype != ISSM_BF16 || (p.dt_sh & 7)) return false;
+  // one tile = one 256-state slice (or all 128 / 256 states) of one head, 64 rows
+  return make_rows_tensor_map(p.dt, p.dt_sb, p.dt_sl, (int64_t)(p.nheads - 1) * p.dt_sh + p.dstate, p.batch, p.seqlen,
+                              p.dstate > 256 ? 256 : p.dstate, out);
+}
+
 template <int NT, typename TDT, int kMode>
-static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_t s) {
+static int launch_fwd_mode(const TArgs& a, const FwdMaps& maps, cudaStream_t s) {
   const size_t smem = FwdSmem<NT>::kTotal + 1024;
   struct FastTag {};
   struct WinTag {};
@@ -856,8 +869,8 @@ static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_
       SmemAttrOnce<WinTag>::set(k_fwd_tensor<NT, TDT, true, 0>, smem) != ISSM_OK)
     return ISSM_ERR_CUDA;
   const int slices = a.N / NT;
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
-  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, false, kMode>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, maps);
+  ISSM_LAUNCH((k_fwd_tensor<NT, TDT, true, 0>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, maps);   // marked streams only
   if (slices > 1 && !a.no_output) {
     const size_t groups = (size_t)a.b * a.L * a.H * (a.P / 4);
     ISSM_LAUNCH(k_combine_slices, (unsigned)cdiv64(groups, 256), 256, 0, s, a, slices, groups);
@@ -867,12 +880,19 @@ static int launch_fwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_
 
 template <int NT, typename TDT>
 static int launch_fwd(TArgs a, const issm_params& p, cudaStream_t s) {
-  CUtensorMap dtmap;
-  a.dt_tma = make_dt_tensor_map(p, &dtmap) ? 1 : 0;
+  FwdMaps maps;
+  a.dt_tma = make_dt_tensor_map(p, &maps.dt) ? 1 : 0;
+  // B / C rows that are not adjacent in memory (a 256-state slice of a wider row, the two halves of one projection
+  // output): a 64-row tile is one tiled TMA load each when the rows form a regular 2-D array
+  const int box = p.dstate > 256 ? 256 : p.dstate;
+  a.bc_tma = (!a.bc_contig && !((p.B_sg | p.C_sg) & 7) &&
+              make_rows_tensor_map(p.B, p.B_sb, p.B_sl, (int64_t)(p.ngroups - 1) * p.B_sg + p.dstate, p.batch, p.seqlen, box, &maps.B) &&
+              make_rows_tensor_map(p.C, p.C_sb, p.C_sl, (int64_t)(p.ngroups - 1) * p.C_sg + p.dstate, p.batch, p.seqlen, box, &maps.C)) ? 1 : 0;
+  if (!a.bc_tma) { memset(&maps.B, 0, sizeof(maps.B)); memset(&maps.C, 0, sizeof(maps.C)); }
   // whole-tile copies of dt (when it is staged at all) and of B / C: the row order of the staged tiles is known
-  const bool tiles = a.bc_contig && (sizeof(TDT) != 2 || a.dt_tma);
-  if (!tiles) return launch_fwd_mode<NT, TDT, 0>(a, dtmap, s);
-  return a.rev ? launch_fwd_mode<NT, TDT, 2>(a, dtmap, s) : launch_fwd_mode<NT, TDT, 1>(a, dtmap, s);
+  const bool tiles = (a.bc_contig || a.bc_tma) && (sizeof(TDT) != 2 || a.dt_tma);
+  if (!tiles) return launch_fwd_mode<NT, TDT, 0>(a, maps, s);
+  return a.rev ? launch_fwd_mode<NT, TDT, 2>(a, maps, s) : launch_fwd_mode<NT, TDT, 1>(a, maps, s);
 }
 
 int tensor_fwd(const issm_params& p, cudaStream_t s) {

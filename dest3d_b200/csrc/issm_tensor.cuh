@@ -25,6 +25,7 @@ struct TArgs {
   float* ypart;     // forward with the states cut into slices of 256 (dstate 512 ...): (slice, b, L, H, P) float partial outputs
   int dt_tma;       // dt is a regular 2-D array of rows: a 64-row tile is ONE tiled TMA load through a tensor map
   int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
+  int bc_tma;       // forward: B and C are regular 2-D arrays of rows (any row pitch): a 64-row tile is one tiled TMA load each
   float dtmin, dtmax;
   const bf16* x; int64_t x_sb, x_sl, x_sh;
   const void* dt; int64_t dt_sb, dt_sl, dt_sh;
@@ -173,6 +174,11 @@ TArgs make_targs(const issm_params& p);
 // Tensor map over bf16 dt viewed as (batch*seqlen rows) x (row pitch) with a (dstate x 64 rows) box; false if dt
 // is not laid out as one regular 2-D array (then the kernels fall back to one bulk copy per row).
 bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out);
+// Tensor map over a bf16 array viewed as (batch*seqlen rows) x (row pitch `sl` elements) with a (box_w x 64 rows) box;
+// false if the rows do not form one regular 2-D array (batch stride != seqlen * row stride) or are not 16-byte aligned.
+bool make_rows_tensor_map(const void* base, int64_t sb, int64_t sl, int64_t width, int batch, int seqlen, int box_w, CUtensorMap* out);
+// the forward kernel's tensor maps (one kernel parameter)
+struct FwdMaps { CUtensorMap dt, B, C; };
 int tensor_fwd_states_only(const issm_params& p, bf16* saved, int* redo, cudaStream_t s);
 size_t tensor_bwd_workspace_bytes(const issm_params& p);
 

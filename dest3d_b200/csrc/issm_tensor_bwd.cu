@@ -806,7 +806,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
           float prefix = half ? p0 : 0.f;
           float ac = half ? a0 : 0.f;
           float2 dA2 = f2(0.f), db2 = f2(0.f);
-#pragma unroll 2
+#pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             float bdv[8], cdv[8];
             tmem_ld8(t_BD + ch * 8, bdv);

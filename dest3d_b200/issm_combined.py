@@ -285,8 +285,7 @@ class ISSMChunkScanCombinedFn(torch.autograd.Function):
     def forward(ctx, x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
                 seq_idx=None, dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False,
                 reverse=False, path="auto"):
-        if seq_idx is not None:
-            raise NotImplementedError("seq_idx (packed variable-length batches) is not supported")
+        assert seq_idx is None, "ISSM_chunk_scan_combined splits packed batches before it reaches the autograd function"
         need_grad = any(ctx.needs_input_grad)
         res = issm_fwd(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, dt_softplus, dt_limit,
                        reverse, path, want_final=return_final_states, save_states=need_grad)
@@ -334,13 +333,53 @@ def ISSM_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias
         z: (batch, seqlen, nheads, headdim)
         dt_bias: (nheads, dstate) or (nheads,)
         initial_states: (batch, nheads, headdim, dstate)
-        seq_idx: must be None
+        seq_idx: (batch, seqlen) or None; sequences packed along seqlen, no state crosses a change of seq_idx
         dt_softplus: Whether to apply softplus to dt
     Return:
         out: (batch, seqlen, nheads, headdim), or (out, final_states (batch, nheads, headdim, dstate) fp32)
     """
-    return ISSMChunkScanCombinedFn.apply(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx,
+    if seq_idx is not None:
+        return _scan_packed(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
+                            return_final_states, reverse, path)
+    return ISSMChunkScanCombinedFn.apply(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, None,
                                          dt_softplus, dt_limit, return_final_states, reverse, path)
+
+
+def _scan_packed(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
+                 return_final_states, reverse, path):
+    """seq_idx (batch, seqlen): several sequences packed along seqlen; no state flows from one to the next.
+
+    The reference threads seq_idx through every kernel: the state is multiplied by zero wherever seq_idx changes
+    (issm_triton/issm_state_passing.py:92-99), rows only see earlier rows of their own sequence
+    (issm_triton/issm_cabt_bmm.py:14) and the incoming state only reaches rows whose seq_idx equals that of the
+    row before (issm_triton/issm_chunk_scan.py:122-131), where the row "before the first" counts as sequence 0 -
+    so initial_states only enter when the first sequence has index 0.  For the usual packed layout (each sequence
+    one contiguous run of seq_idx) that is exactly one independent scan per run, which is how it is done here: the
+    runs are found on the host (one device-to-host copy of seq_idx) and every run is one call of the kernels on a
+    view of the inputs; autograd stitches the gradients.  final_states are those of the last run in scan order."""
+    batch, seqlen = x.shape[0], x.shape[1]
+    assert seq_idx.shape == (batch, seqlen)
+    idx = seq_idx.detach().to("cpu")
+    outs, finals = [], []
+    for b in range(batch):
+        row = idx[b]
+        change = (torch.nonzero(row[1:] != row[:-1]).flatten() + 1).tolist()
+        bounds = [0] + change + [seqlen]
+        runs = list(zip(bounds[:-1], bounds[1:]))
+        first = runs[-1] if reverse else runs[0]           # the run the scan enters first
+        ys, fin = [], None
+        for (s, e) in (reversed(runs) if reverse else runs):
+            init = None
+            if initial_states is not None and (s, e) == first and int(row[e - 1 if reverse else s]) == 0:
+                init = initial_states[b:b + 1]
+            sl = lambda t: None if t is None else t[b:b + 1, s:e]
+            y, fin = ISSMChunkScanCombinedFn.apply(sl(x), sl(dt), A, sl(B), sl(C), chunk_size, D, sl(z), dt_bias, init, None,
+                                                   dt_softplus, dt_limit, True, reverse, path)
+            ys.append(y)
+        outs.append(torch.cat(ys[::-1] if reverse else ys, dim=1))
+        finals.append(fin)
+    out = torch.cat(outs, dim=0)
+    return (out, torch.cat(finals, dim=0)) if return_final_states else out
 
 
 def issm_bidirectional_scan(x, x_back, dt, A, B, C, B_back, C_back, chunk_size, D=None, z=None, dt_bias=None,

@@ -227,13 +227,61 @@ def test_reverse_equals_flip(path, dtype, shape):
         assert torch.equal(g1[k], g2[k]), k
 
 
+@pytest.mark.parametrize("path,dtype", [("simt", torch.float32), ("tensor", torch.bfloat16)], ids=["simt_f32", "tensor_bf16"])
+@pytest.mark.parametrize("reverse", [False, True], ids=["forward_scan", "reversed_scan"])
+def test_packed_sequences_seq_idx(path, dtype, reverse):
+    """seq_idx packs several sequences along seqlen: outputs, final states and every gradient equal those of one
+    independent oracle scan per sequence (the state is reset where seq_idx changes; initial_states enter the first
+    sequence only, and only when its index is 0: issm_triton/issm_state_passing.py:92-99)."""
+    from dest3d_b200 import ISSM_chunk_scan_combined
+    b, L, H, P, N, Q = 2, 300, 2, 36, 256, 64
+    inp = O.make_inputs(b, L, H, P, N, seed=77, dtype=dtype)
+    lens = [[100, 137, 63], [7, 293]]
+    first_index = [0, 3]                                     # sample 1 starts with index 3: its initial state is dropped
+    seq_idx = torch.cat([torch.cat([torch.full((n,), first_index[i] + k, dtype=torch.int32) for k, n in enumerate(l)])[None]
+                         for i, l in enumerate(lens)])
+    opts = dict(BENCH_OPTS, reverse=reverse)
+    # oracle: one scan per run, float64
+    leaves = {k: inp[k].detach().double().requires_grad_() for k in parity.GRADS}
+    outs, fins = [], []
+    for i, l in enumerate(lens):
+        ys, s0, fin = [], 0, None
+        runs = []
+        for n in l:
+            runs.append((s0, s0 + n))
+            s0 += n
+        order = list(reversed(runs)) if reverse else runs
+        for j, (s, e) in enumerate(order):
+            first_run_index = first_index[i] + (len(l) - 1 if reverse else 0)
+            init = leaves["initial_states"][i:i + 1] if (j == 0 and first_run_index == 0) else None
+            y, fin = O.issm_scan_chunked(leaves["x"][i:i + 1, s:e], leaves["dt"][i:i + 1, s:e], leaves["A"], leaves["B"][i:i + 1, s:e],
+                                         leaves["C"][i:i + 1, s:e], 64, D=leaves["D"], z=leaves["z"][i:i + 1, s:e],
+                                         dt_bias=leaves["dt_bias"], initial_states=init, dt_softplus=True, dt_limit=(1e-3, 1e-1),
+                                         reverse=reverse, compute_dtype=torch.float64)
+            ys.append(y)
+        outs.append(torch.cat(ys[::-1] if reverse else ys, dim=1))
+        fins.append(fin)
+    ref_out, ref_fin = torch.cat(outs), torch.cat(fins)
+    ((ref_out * inp["dout"].double()).sum() + (ref_fin * inp["dfinal"].double()).sum()).backward()
+    g = {k: inp[k].detach().clone().cuda().requires_grad_() for k in parity.GRADS}
+    out, fin = ISSM_chunk_scan_combined(g["x"], g["dt"], g["A"], g["B"], g["C"], Q, D=g["D"], z=g["z"], dt_bias=g["dt_bias"],
+                                        initial_states=g["initial_states"], seq_idx=seq_idx.cuda(), dt_softplus=True,
+                                        dt_limit=(1e-3, 1e-1), return_final_states=True, reverse=reverse, path=path)
+    ((out.float() * inp["dout"].cuda().float()).sum() + (fin * inp["dfinal"].cuda()).sum()).backward()
+    parity.close(out, ref_out, dtype, "out")
+    parity.close(fin, ref_fin, dtype, "final")
+    for k in parity.GRADS:
+        if leaves[k].grad is None:                           # no run of the reversed scan starts with index 0: initial_states unused
+            assert g[k].grad is None or float(g[k].grad.abs().max()) == 0.0, k
+            continue
+        parity.close(g[k].grad, leaves[k].grad, dtype, "d" + k)
+
+
 def test_bad_arguments_raise():
     from dest3d_b200 import ISSM_chunk_scan_combined, _lib
     inp, Q = _inputs((1, 64, 2, 8, 16, 1, 16), {}, BENCH_OPTS, torch.float32)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
     with pytest.raises(RuntimeError, match="error 2"):                               # ISSM_ERR_SHAPE from the C ABI
         ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], 512)          # chunk_size > 256
-    with pytest.raises(NotImplementedError):
-        ISSM_chunk_scan_combined(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, seq_idx=torch.zeros(1, 64, dtype=torch.int32))
     with pytest.raises(RuntimeError):
         ISSM_chunk_scan_combined(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], Q)  # CPU tensors
