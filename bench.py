@@ -354,7 +354,7 @@ def run_mine(args):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on the small profiling case c3s
 # (batch 16, L = 4096) from the ncu captures summarised in profiles/k_fwd_tensor_c3s.md and
 # profiles/k_bwd_tensor_c3s.md; traffic grows in proportion to batch x L
-NCU_C3S_TRAFFIC = {"fwd": 413.5e6 + 248.0e6, "bwd": 698.5e6 + 839.5e6}
+NCU_C3S_TRAFFIC = {"fwd": 413.6e6 + 247.9e6, "bwd": 698.3e6 + 835.9e6}
 NCU_C3S_SOURCE = "ncu capture of the c3s case (profiles/k_fwd_tensor_c3s.md, profiles/k_bwd_tensor_c3s.md), scaled by batch x L"
 
 
