@@ -278,6 +278,35 @@ def run_mine(args):
     L, H, P, N = w["L"], w["H"], w["P"], w["N"]
     value = gbatch * L * N * nl * args.steps / (ms * 1e-3)
 
+    # The same step replayed from a CUDA graph (one GPU, --graph): at the detector's size a step is ~20 short launches
+    # and the eager number is bound by launch latency; a training loop with static shapes can capture it once.
+    graph_info = None
+    if args.graph and world == 1:
+        try:
+            torch.cuda.synchronize()
+            gstream = torch.cuda.Stream()
+            with torch.cuda.stream(gstream):
+                for _ in range(2):
+                    step()                                  # warm the allocator's pools on the capture stream
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=gstream):
+                step()
+            for _ in range(args.warmup):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            gms = e0.elapsed_time(e1) / args.steps
+            status_or_die("the graph replay")
+            graph_info = {"ms_per_step": gms, "value": gbatch * L * N * nl / (gms * 1e-3), "unit": UNIT}
+            del graph
+        except Exception as exc:                            # a capture that is refused is reported, not fatal
+            graph_info = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+
     # end to end through the public call with HOST buffers: H2D of the step's inputs from pinned memory,
     # the layer, D2H of the combined output, final states and packed parameter gradients.  The steps are
     # pipelined the way a training loop with a prefetching loader runs them: the H2D copy of step i+1 (copy
@@ -345,7 +374,7 @@ def run_mine(args):
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
                         "pipelining": "H2D of step i+1 overlaps the layer of step i (two device buffer sets)"},
-                "gpu_launches": int(launches), "device_status": status, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+                "gpu_launches": int(launches), "cuda_graph": graph_info, "device_status": status, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -539,6 +568,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES))
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph (one GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -172,6 +172,8 @@ def _check_status(device, what):
     if m is None:
         m = _MIRROR[key] = _StatusMirror(torch.device("cuda", key))
     with torch.cuda.device(key):
+        if torch.cuda.is_current_stream_capturing():     # inside a CUDA-graph capture: neither query nor copy
+            return
         m.poll(what)
         m.refresh()
 
