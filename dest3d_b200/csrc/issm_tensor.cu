@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
   const int kcol = n & 63;
   // saved block-entry states: (b, H, nblk + 1, PP / 8, N, 8) bf16, i.e. per block the interleaved
   // [head-dim chunk][state][8] layout the backward uses directly as an MMA operand
-  bf16* savep = a.saved ? a.saved + (((size_t)b * a.H + h) * (nblk + 1)) * a.N * PP + ((size_t)half * (HP / 8) * a.N + n) * 8 : nullptr;
+  bf16* savep = a.saved ? a.saved + (((size_t)b * a.H + h) * (nblk + 1)) * a.N * PP + ((size_t)half * (HP / 8) * a.N + n_off + n) * 8 : nullptr;
   auto publish_state = [&](const float* sc, int blk_index, bool save) {
     publish_state_cols(a, sc, sop_col, kcol, half, savep, blk_index, save);
   };
@@ -724,7 +724,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 // number of 256-state slices a call is cut into (1 for dstate 128 / 256; 0 = no tensor-core kernels for this dstate)
-static int state_slices(int dstate) {
+int state_slices(int dstate) {
   if (dstate == 128 || dstate == 256) return 1;
   if (dstate % 256 == 0 && dstate <= 1024) return dstate / 256;
   return 0;
@@ -738,7 +738,7 @@ bool tensor_path_supported(const issm_params& p, int pass) {
   if (p.has_z && ((p.z_sb | p.z_sl | p.z_sh) & 3)) return false;
   if (((uintptr_t)p.x | (uintptr_t)p.z | (uintptr_t)p.out | (uintptr_t)p.out_x | (uintptr_t)p.dout | (uintptr_t)p.dx | (uintptr_t)p.dz) & 7) return false;
   const int slices = state_slices(p.dstate);
-  if (slices == 0 || (slices > 1 && pass != 0)) return false;   // sliced states: forward kernels only
+  if (slices == 0) return false;
   // bulk (TMA) row copies need 16-byte aligned rows of B, C and (bf16) dt
   if (p.B && (!aligned16(p.B) || !aligned16(p.C))) return false;
   if ((p.B_sb | p.B_sl | p.B_sg | p.C_sb | p.C_sl | p.C_sg) & 7) return false;
@@ -901,7 +901,6 @@ int tensor_fwd(const issm_params& p, cudaStream_t s) {
   const int slices = state_slices(p.dstate);
   if (slices > 1) {
     a.ypart = (float*)((char*)p.workspace + align_up((size_t)slices * p.batch * p.nheads * sizeof(int), 256));
-    a.saved = nullptr;                                     // the sliced forward keeps no block-entry states (its backward runs on the SIMT kernels)
   }
   if (p.dstate != 128) return p.dt_dtype == ISSM_BF16 ? launch_fwd<256, bf16>(a, p, s) : launch_fwd<256, float>(a, p, s);
   return p.dt_dtype == ISSM_BF16 ? launch_fwd<128, bf16>(a, p, s) : launch_fwd<128, float>(a, p, s);

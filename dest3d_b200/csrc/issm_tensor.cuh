@@ -22,6 +22,7 @@ struct TArgs {
   int has_D, D_has_hdim, has_z, has_bias, softplus, has_init, want_final, no_output;
   bf16* wscr;       // backward, windowed kernel: (batch, nheads, 63, state) bf16 window-entry states of the block in progress
   int* redo;        // (batch, nheads) marks: stream holds a block outside the fast kernel's range, redo it windowed
+  bf16* dxpart;     // backward with state slices: (slice, b, L, H, P) bf16 partial dx rows (before the D skip)
   float* ypart;     // forward with the states cut into slices of 256 (dstate 512 ...): (slice, b, L, H, P) float partial outputs
   int dt_tma;       // dt is a regular 2-D array of rows: a 64-row tile is ONE tiled TMA load through a tensor map
   int bc_contig;    // B and C rows of one (batch, group) are adjacent in memory: a 64-row tile is one bulk copy
@@ -179,6 +180,7 @@ bool make_dt_tensor_map(const issm_params& p, CUtensorMap* out);
 bool make_rows_tensor_map(const void* base, int64_t sb, int64_t sl, int64_t width, int batch, int seqlen, int box_w, CUtensorMap* out);
 // the forward kernel's tensor maps (one kernel parameter)
 struct FwdMaps { CUtensorMap dt, B, C; };
+int state_slices(int dstate);
 int tensor_fwd_states_only(const issm_params& p, bf16* saved, int* redo, cudaStream_t s);
 size_t tensor_bwd_workspace_bytes(const issm_params& p);
 

@@ -89,20 +89,25 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   const bool is_io = tid >= NTH + 32;
   const int io_t = tid - NTH - 32;
   const int h = blockIdx.y, b = blockIdx.z, g = h / a.hpg;
-  if (kWin && !a.redo[b * a.H + h]) return;              // the fast kernel finished this stream
+  // more than 256 states: blockIdx.x is a slice of 256 states, an independent scan over the same x (see the forward
+  // kernel); its dx rows are partial sums that k_combine_dx adds, everything per state is the slice's own
+  const int n_off = blockIdx.x * NT;
+  const int stream = (blockIdx.x * a.b + b) * a.H + h;
+  if (kWin && !a.redo[stream]) return;                   // the fast kernel finished this stream
   const int n = tid % NT, half = (tid / NT) & 1;
-  const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh;
-  const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg;
-  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg;
+  const int ng = n_off + n;                              // state index in the (nheads, dstate) / (..., dstate) arrays
+  const TDT* __restrict__ dtp = (const TDT*)a.dt + b * a.dt_sb + h * a.dt_sh + n_off;
+  const bf16* __restrict__ Bp = a.B + b * a.B_sb + g * a.B_sg + n_off;
+  const bf16* __restrict__ Cp = a.C + b * a.C_sb + g * a.C_sg + n_off;
   const bf16* __restrict__ xp = a.x + b * a.x_sb + h * a.x_sh;
   const bf16* __restrict__ zp = a.has_z ? a.z + b * a.z_sb + h * a.z_sh : nullptr;
   const bf16* __restrict__ yp = a.has_z ? a.out_x + b * a.o_sb + h * a.o_sh : nullptr;
   const bf16* __restrict__ gp = a.dout + b * a.g_sb + h * a.g_sh;
-  const float A2 = __ldg(a.A + h * a.N + n) * LOG2E;
-  const float Anat = __ldg(a.A + h * a.N + n);
-  const float bias = a.has_bias ? __ldg(a.bias + h * a.N + n) : 0.f;
+  const float A2 = __ldg(a.A + h * a.N + ng) * LOG2E;
+  const float Anat = __ldg(a.A + h * a.N + ng);
+  const float bias = a.has_bias ? __ldg(a.bias + h * a.N + ng) : 0.f;
   // the same constants for the two adjacent states (2 pr, 2 pr + 1) of the fast instantiation's operand pass
-  const int pr0 = 2 * (tid % (NT / 2));
+  const int pr0 = n_off + 2 * (tid % (NT / 2));
   const float2 A2p = f2(__ldg(a.A + h * a.N + pr0) * LOG2E, __ldg(a.A + h * a.N + pr0 + 1) * LOG2E);
   const float bsc = a.softplus ? LOG2E : 1.f;
   const float2 biasL2 = a.has_bias ? f2(__ldg(a.bias + h * a.N + pr0) * bsc, __ldg(a.bias + h * a.N + pr0 + 1) * bsc) : f2(0.f);
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
     if (a.dt_tma) {                                        // one tiled TMA load; the tile is staged in memory order
       if (lane == 0) {
         mbar_expect_tx(barS, (uint32_t)QB * NT * 2);
-        tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh, b * a.L + (a.rev ? a.L - row0 - rows : row0), barS);
+        tma_load_2d(smem + SM::kSdt, &dtmap, h * (int)a.dt_sh + n_off, b * a.L + (a.rev ? a.L - row0 - rows : row0), barS);
       }
       return;
     }
@@ -175,7 +180,14 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   auto prefetch_S = [&](int blk) {
     if (lane == 0) {
       mbar_expect_tx(barU, (uint32_t)NT * PP * 2);
-      bulk_g2s(smem + SM::kSop, a.saved + (bh * (nblk + 1) + blk) * (size_t)a.N * PP, (uint32_t)NT * PP * 2, barU);
+      const bf16* src = a.saved + (bh * (nblk + 1) + blk) * (size_t)a.N * PP;
+      if (a.N == NT) {
+        bulk_g2s(smem + SM::kSop, src, (uint32_t)NT * PP * 2, barU);
+      } else {                                             // a slice of the states: its part of each of the PP / 8 head-dim chunks
+#pragma unroll
+        for (int c = 0; c < PP / 8; ++c)
+          bulk_g2s(smem + SM::kSop + c * (NT * 16), src + ((size_t)c * a.N + n_off) * 8, (uint32_t)NT * 16, barU);
+      }
     }
   };
   if (is_svc) { prefetch_dt(nblk - 1); prefetch_B(nblk - 1); prefetch_C(nblk - 1); prefetch_S(nblk); }
@@ -183,7 +195,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   // ---- column threads: G <- dfinal ---------------------------------------------------------------------
   if (is_col) {
     float gc[HP];
-    const float* __restrict__ df = a.dfinal ? a.dfinal + (bh * a.P) * a.N + n : nullptr;
+    const float* __restrict__ df = a.dfinal ? a.dfinal + (bh * a.P) * a.N + ng : nullptr;
 #pragma unroll
     for (int j = 0; j < HP; ++j) gc[j] = (df && half * HP + j < a.P) ? df[(size_t)(half * HP + j) * a.N] : 0.f;
     tmem_st16(t_G, gc);
@@ -234,6 +246,10 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
     const int l = g.l, gq = g.gq;
     if (l >= t_rows) return;
     const uint2 tv = *(const uint2*)(smem + SM::kDxT + (l * SM::DXS + gq * 4) * 2);
+    if (a.dxpart) {                                        // one slice of the states: D dy and dz come after the sum over the slices
+      *(uint2*)(a.dxpart + ((((size_t)blockIdx.x * a.b + b) * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4) = tv;
+      return;
+    }
     float v[4] = {bf_lo(tv.x), bf_hi(tv.x), bf_lo(tv.y), bf_hi(tv.y)};
     float dy[4] = {bf_lo(g.gv.x), bf_hi(g.gv.x), bf_lo(g.gv.y), bf_hi(g.gv.y)};
     const size_t o = (((size_t)b * a.L + trow(a, t_row0 + l)) * a.H + h) * a.P + gq * 4;
@@ -713,7 +729,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         if constexpr (!kWin) cst = sXch[2 * NT + n] + sXch[3 * NT + n];   // <S leaving the block, G> of column n
         // output element of row l: index o0 + l * ostep (rows of a reversed scan go down in memory)
         const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
-        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + ng;
         TDT* const p_ddt = (TDT*)a.ddt + o0;
         uint32_t* const p_dBC = a.dBCh + o0;
         auto epi = [&](auto full) {
@@ -797,7 +813,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         cst = sXch[2 * NT + n] + sXch[3 * NT + n];         // <S leaving the block, G> of column n
         const float base = cst + total;                    // ddA[l] = base - sum of dacs over the rows before l
         const int ostep = (a.rev ? -1 : 1) * a.H * a.N;
-        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + n;
+        const int64_t o0 = (((int64_t)b * a.L + trow(a, row0)) * a.H + h) * a.N + ng;
         TDT* const p_ddt = (TDT*)a.ddt + o0;
         uint32_t* const p_dBC = a.dBCh + o0;
         const float biasL = bias * (a.softplus ? LOG2E : 1.f);
@@ -965,7 +981,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
       windowed = 1;
       named_barrier(9, NTH + NIO);                       // the previous block's dx rows have left the tile
       const float cst_block = cst;
-      const size_t mine = ((size_t)half * (HP / 8) * a.N + n) * 8;          // this thread's chunks inside a state
+      const size_t mine = ((size_t)half * (HP / 8) * a.N + ng) * 8;          // this thread's chunks inside a state
       const bf16* sv0 = a.saved + (bh * (nblk + 1) + blk) * sblk + mine;    // state entering the block
       bf16* wsc = a.wscr + bh * 63 * sblk + mine;                           // slot j: state entering window j + 1
       const uint32_t t_W = tmem + lane_base + 128 + slab * 64 + half * HP;  // accumulator of the walk
@@ -1067,7 +1083,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
   const int votes = __syncthreads_or((int)unsafe | (failed ? 2 : 0));
   const int any_unsafe = votes & 1;
   failed = (votes & 2) != 0;
-  if (!kWin && tid == 0) a.redo[b * a.H + h] = any_unsafe;
+  if (!kWin && tid == 0) a.redo[stream] = any_unsafe;
   if (!failed && nblk > 0) finish_rows(prev_row0, prev_rows);
   __syncthreads();
   if (!failed) {
@@ -1077,7 +1093,7 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
         tmem_ld16(t_G, gc);
         tmem_ld8(t_G + 16, gc + 16);
         tmem_ld_wait();
-        bf16* dp = a.dinit + (bh * a.P) * a.N + n;
+        bf16* dp = a.dinit + (bh * a.P) * a.N + ng;
 #pragma unroll
         for (int j = 0; j < HP; ++j)
           if (half * HP + j < a.P) dp[(size_t)(half * HP + j) * a.N] = __float2bfloat16_rn(gc[j]);
@@ -1090,13 +1106,13 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_bwd_tensor(const __grid_con
     if (is_io) red[io_t] = dDacc;
     __syncthreads();
     if (is_col && half == 0) {
-      a.dApart[bh * a.N + n] = sXch[n] + sXch[NT + n];
-      a.dbpart[bh * a.N + n] = sXch[2 * NT + n] + sXch[3 * NT + n];
+      a.dApart[bh * a.N + ng] = sXch[n] + sXch[NT + n];
+      a.dbpart[bh * a.N + ng] = sXch[2 * NT + n] + sXch[3 * NT + n];
     }
     if (tid == 0) {                                       // scalar dD partial of this (batch, head)
       float sacc = 0.f;
       for (int i = 0; i < NIO; ++i) sacc += red[i];
-      a.dDpart[bh] = sacc;
+      if (blockIdx.x == 0) a.dDpart[bh] = sacc;            // dy . x does not depend on the states: one slice reports it
     }
   }
   if (a.status) {
@@ -1126,6 +1142,51 @@ __global__ void k_dD_hdim(const TArgs a) {
     acc = warp_sum(acc);
     if (lane == 0) a.dDpart[((size_t)b * a.H + h) * PP + p] = acc;
   }
+}
+
+// State slices: dx = sum over the slices of the partial dx rows + D dy, and dz = dout y sigmoid(z)(1 + z(1 - sigmoid(z)))
+// (what group_store of the scan kernel does for a single slice).  One thread per group of 4 head-dim elements.
+__global__ void k_combine_dx(const TArgs a, int slices, size_t groups) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  const int ngrp = a.P / 4;
+  const int gq = (int)(i % ngrp);
+  size_t r = i / ngrp;
+  const int h = (int)(r % a.H);
+  r /= a.H;
+  const int l = (int)(r % a.L);
+  const int b = (int)(r / a.L);
+  auto lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+  auto hi = [](uint32_t w) { return __uint_as_float(w & 0xffff0000u); };
+  const size_t o = (((size_t)b * a.L + l) * a.H + h) * a.P + gq * 4;
+  const size_t slice_stride = (size_t)a.b * a.L * a.H * a.P;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < slices; ++s) {
+    const uint2 tv = *(const uint2*)(a.dxpart + s * slice_stride + o);
+    v[0] += lo(tv.x); v[1] += hi(tv.x); v[2] += lo(tv.y); v[3] += hi(tv.y);
+  }
+  const uint2 gv = *(const uint2*)(a.dout + b * a.g_sb + (int64_t)l * a.g_sl + h * a.g_sh + gq * 4);
+  float dy[4] = {lo(gv.x), hi(gv.x), lo(gv.y), hi(gv.y)};
+  if (a.has_z) {
+    const uint2 zv = *(const uint2*)(a.z + b * a.z_sb + (int64_t)l * a.z_sl + h * a.z_sh + gq * 4);
+    const uint2 yv = *(const uint2*)(a.out_x + b * a.o_sb + (int64_t)l * a.o_sl + h * a.o_sh + gq * 4);
+    const float zf[4] = {lo(zv.x), hi(zv.x), lo(zv.y), hi(zv.y)};
+    const float yf[4] = {lo(yv.x), hi(yv.x), lo(yv.y), hi(yv.y)};
+    float dzv[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float sg = __fdividef(1.f, 1.f + ex2f(-zf[q] * LOG2E));
+      dzv[q] = dy[q] * yf[q] * sg * (1.f + zf[q] * (1.f - sg));
+      dy[q] *= zf[q] * sg;
+    }
+    *(uint2*)(a.dz + o) = make_uint2(pack_bf16(dzv[0], dzv[1]), pack_bf16(dzv[2], dzv[3]));
+  }
+  if (a.has_D) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      v[q] = fmaf(a.D_has_hdim ? __ldg(a.D + h * a.P + gq * 4 + q) : __ldg(a.D + h), __bfloat162float(__float2bfloat16_rn(dy[q])), v[q]);
+  }
+  *(uint2*)(a.dx + o) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
 }
 
 // dB[b,l,g,n], dC[b,l,g,n] = sums over the heads of group g of the per-head partials, stored as packed bf16 pairs
@@ -1188,7 +1249,7 @@ __global__ void k_reduce_dD(const float* __restrict__ part, int batch, int H, in
 // ---------------------------------------------------------------------------------------------
 struct BwdWs {
   uint32_t* dBCh;
-  bf16 *saved, *wscr;
+  bf16 *saved, *wscr, *dxpart;
   float *dApart, *dbpart, *dDpart;
   int *redo_fwd, *redo_bwd;
 };
@@ -1202,8 +1263,10 @@ static BwdWs carve_bwd(const issm_params& p, size_t* total) {
   w.dApart = c.take<float>(b * H * N);
   w.dbpart = c.take<float>(b * H * N);
   w.dDpart = c.take<float>(b * H * PP);
-  w.redo_fwd = c.take<int>(b * H);
-  w.redo_bwd = c.take<int>(b * H);
+  const size_t slices = (size_t)state_slices(p.dstate);
+  w.redo_fwd = c.take<int>(slices * b * H);
+  w.redo_bwd = c.take<int>(slices * b * H);
+  w.dxpart = slices > 1 ? c.take<bf16>(slices * b * L * H * p.headdim) : nullptr;
   w.wscr = c.take<bf16>(b * H * 63 * N * PP);             // window-entry states of one block per stream (windowed kernel)
   w.saved = p.saved_states ? nullptr : c.take<bf16>(b * H * (nblk + 1) * N * PP);
   *total = c.off;
@@ -1226,8 +1289,13 @@ static int launch_bwd_mode(const TArgs& a, const CUtensorMap& dtmap, cudaStream_
   if (SmemAttrOnce<FastTag>::set(k_bwd_tensor<NT, TDT, false, kMode>, smem) != ISSM_OK ||
       SmemAttrOnce<WinTag>::set(k_bwd_tensor<NT, TDT, true, 0>, smem) != ISSM_OK)
     return ISSM_ERR_CUDA;
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false, kMode>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
-  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true, 0>), dim3(1, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  const int slices = a.N / NT;
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, false, kMode>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);
+  ISSM_LAUNCH((k_bwd_tensor<NT, TDT, true, 0>), dim3(slices, a.H, a.b), 2 * NT + 128, smem, s, a, dtmap);   // marked streams only
+  if (slices > 1) {
+    const size_t groups = (size_t)a.b * a.L * a.H * (a.P / 4);
+    ISSM_LAUNCH(k_combine_dx, (unsigned)cdiv64(groups, 256), 256, 0, s, a, slices, groups);
+  }
   return ISSM_OK;
 }
 
@@ -1257,9 +1325,9 @@ int tensor_bwd(const issm_params& p, cudaStream_t s) {
   a.dfinal = p.has_dfinal ? p.dfinal_states : nullptr;
   a.dx = (bf16*)p.dx; a.ddt = p.ddt; a.dz = (bf16*)p.dz; a.dinit = (bf16*)p.dinitial_states;
   a.dBCh = w.dBCh; a.dApart = w.dApart; a.dbpart = w.dbpart; a.dDpart = w.dDpart;
-  a.redo = w.redo_bwd; a.wscr = w.wscr;
+  a.redo = w.redo_bwd; a.wscr = w.wscr; a.dxpart = w.dxpart;
   int rc;
-  if (p.dstate == 256) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, p, s) : launch_bwd<256, float>(a, p, s);
+  if (p.dstate != 128) rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<256, bf16>(a, p, s) : launch_bwd<256, float>(a, p, s);
   else rc = p.dt_dtype == ISSM_BF16 ? launch_bwd<128, bf16>(a, p, s) : launch_bwd<128, float>(a, p, s);
   if (rc) return rc;
   const int hpg = p.nheads / p.ngroups;

@@ -149,9 +149,9 @@ size_t issm_b200_workspace_bytes(const issm_params* p, int pass);
 /* Which path (ISSM_PATH_SIMT or ISSM_PATH_TENSOR) a forward call with these sizes would take; -1 when the
  * requested path does not cover them. */
 int issm_b200_resolve_path(const issm_params* p);
-/* The same per pass (0 = forward, 1 = backward).  They can differ: for dstate 512 / 768 / 1024 the forward runs
- * on the tensor-core kernels (one 256-state slice per CTA, partial outputs summed by a combine kernel) while the
- * backward runs on the SIMT kernels; `saved_states` is only of use when the BACKWARD takes the tensor path. */
+/* The same per pass (0 = forward, 1 = backward); `saved_states` is only of use when the BACKWARD takes the
+ * tensor path.  (dstate 512 / 768 / 1024 run on the tensor-core kernels in both passes: one 256-state slice per
+ * CTA, the partial output rows / partial dx rows summed by a combine kernel.) */
 int issm_b200_resolve_path_pass(const issm_params* p, int pass);
 
 int issm_b200_fwd(const issm_params* p, void* cuda_stream);

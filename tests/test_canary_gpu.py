@@ -52,6 +52,7 @@ CASES = [
     ("single_point", (1, 1, 2, 36, 128, 1, 64)),
     ("exact_blocks", (1, 128, 2, 36, 256, 1, 128)),
     ("headdim_40", (1, 70, 2, 40, 128, 1, 64)),
+    ("two_state_slices", (1, 101, 2, 36, 512, 1, 64)),
 ]
 
 

@@ -90,8 +90,8 @@ def test_parity_tensor(case):
                          ids=["n512", "n768", "n1024"])
 @pytest.mark.parametrize("reverse", [False, True], ids=["forward_scan", "reversed_scan"])
 def test_parity_more_than_256_states(shape, reverse):
-    """dstate 512 / 768 / 1024 (bf16): the forward runs on the tensor-core kernels, one 256-state slice per CTA with
-    the partial outputs summed by the combine kernel; the backward of these sizes runs on the SIMT kernels."""
+    """dstate 512 / 768 / 1024 (bf16) on the tensor-core kernels: one 256-state slice per CTA, the partial output rows
+    (forward) and partial dx rows (backward) summed by the combine kernels."""
     import ctypes as ct
     from dest3d_b200 import _lib, issm_combined
     b, L, H, P, N, G, Q = shape
@@ -101,10 +101,10 @@ def test_parity_more_than_256_states(shape, reverse):
     prm, _ = issm_combined._fill_common(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, c["D"], c["z"], c["dt_bias"], c["initial_states"],
                                         True, (1e-3, 1e-1), reverse, "auto")
     assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(prm), 0) == _lib.PATH_TENSOR
-    assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(prm), 1) == _lib.PATH_SIMT
+    assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(prm), 1) == _lib.PATH_TENSOR
     ref = parity.oracle_run(inp, 64, opts)
     issm_combined.device_status()
-    got = parity.cuda_run(inp, Q, opts, path="auto")
+    got = parity.cuda_run(inp, Q, opts, path="tensor")
     assert issm_combined.device_status() == 0
     rep = parity.compare(got, ref, torch.bfloat16)
     print(f"dstate {N}", parity.format_report(rep))
@@ -121,6 +121,7 @@ WINDOWED_CASES = [
     ("w_single_row_windows", (1, 150, 2, 32, 256, 1, 64), 5.0, 4.0, dict(dt_softplus=True, loosen=10.0)),
     ("w_float_dt", (1, 160, 2, 36, 256, 1, 64), 1.0, 2.0, dict(dt_softplus=True, f32dt=True)),
     ("w_no_z_no_init", (1, 130, 2, 36, 128, 1, 64), 1.0, 2.0, dict(dt_softplus=True, use_z=False, use_initial_states=False)),
+    ("w_n512_slices", (1, 150, 2, 36, 512, 1, 64), 1.0, 4.0, dict(dt_softplus=True, reverse=True)),
 ]
 
 
