@@ -12,9 +12,12 @@
 
 namespace issm {
 
-__device__ __forceinline__ float siluf_(float v) { return v * sigmoidf_(v); }
+// sigmoid through the hardware exponential and reciprocal (about 2 ulp each; the exact expf and IEEE division cost
+// ~40 instructions per element and made these kernels compute-bound)
+__device__ __forceinline__ float fast_sigmoid(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
+__device__ __forceinline__ float siluf_(float v) { return v * fast_sigmoid(v); }
 __device__ __forceinline__ float dsiluf_(float v) {
-  const float s = sigmoidf_(v);
+  const float s = fast_sigmoid(v);
   return s * (1.f + v * (1.f - s));
 }
 
@@ -71,8 +74,8 @@ __global__ void k_norm_fwd(issm_norm_params np) {
 template <typename T> struct Vec16;
 template <> struct Vec16<bf16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const bf16* p, float* v) {
-    const uint4 w = *(const uint4*)p;
+  static __device__ __forceinline__ void load(const bf16* p, float* v) { unpack(*(const uint4*)p, v); }
+  static __device__ __forceinline__ void unpack(uint4 w, float* v) {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(u[i] << 16); v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
@@ -89,9 +92,9 @@ template <> struct Vec16<bf16> {
 };
 template <> struct Vec16<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float* v) {
-    const float4 w = *(const float4*)p;
-    v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+  static __device__ __forceinline__ void load(const float* p, float* v) { unpack(*(const uint4*)p, v); }
+  static __device__ __forceinline__ void unpack(uint4 w, float* v) {
+    v[0] = __uint_as_float(w.x); v[1] = __uint_as_float(w.y); v[2] = __uint_as_float(w.z); v[3] = __uint_as_float(w.w);
   }
   static __device__ __forceinline__ void store(float* p, const float* v) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
 };
@@ -100,65 +103,88 @@ template <> struct Vec16<float> {
 template <typename T, int CH>
 __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
   constexpr int V = Vec16<T>::N;
-  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (row >= np.rows) return;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
   const int H = np.hidden;
-  const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
-  const T* z = np.has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
-  T* y = (T*)np.y + (int64_t)row * np.y_sr;
-  const bool pre_gate = z && !np.norm_before_gate, post_gate = z && np.norm_before_gate;
-  float v[CH][V], zg[CH][V];
-  float s1 = 0.f, s2 = 0.f;
+  const bool has_z = np.has_z != 0;
+  const bool pre_gate = has_z && !np.norm_before_gate, post_gate = has_z && np.norm_before_gate;
+  // a warp walks rows first, first + warps, ...; the 16-byte loads of the next row are issued (kept packed, 4 registers
+  // per chunk) before the current row is worked on
+  uint4 nx[CH], nz[CH];
+  auto issue = [&](int row) {
+    const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
+    const T* z = has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
 #pragma unroll
-  for (int c = 0; c < CH; ++c) {
-    const int f0 = (c * 32 + lane) * V;
-    if (f0 < H) {
-      Vec16<T>::load(x + f0, v[c]);
-      if (z) Vec16<T>::load(z + f0, zg[c]);
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        if (z) zg[c][i] = siluf_(zg[c][i]);
-        if (pre_gate) v[c][i] *= zg[c][i];
-        s1 += v[c][i];
-        s2 = fmaf(v[c][i], v[c][i], s2);
+    for (int c = 0; c < CH; ++c) {
+      const int f0 = (c * 32 + lane) * V;
+      if (f0 < H) {
+        nx[c] = *(const uint4*)(x + f0);
+        if (has_z) nz[c] = *(const uint4*)(z + f0);
       }
     }
-  }
-  s1 = warp_sum(s1);
-  s2 = warp_sum(s2);
-  float mean = 0.f, var;
-  if (np.is_rms) {
-    var = s2 / H;
-  } else {
-    mean = s1 / H;
-    float sv = 0.f;
+  };
+  int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row < np.rows) issue(row);
+  for (; row < np.rows; row += warps) {
+    T* y = (T*)np.y + (int64_t)row * np.y_sr;
+    float v[CH][V], zg[CH][V];
+    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int c = 0; c < CH; ++c)
+    for (int c = 0; c < CH; ++c) {
+      if ((c * 32 + lane) * V < H) {
+        Vec16<T>::unpack(nx[c], v[c]);
+        if (has_z) Vec16<T>::unpack(nz[c], zg[c]);
+      }
+    }
+    if (row + warps < np.rows) issue(row + warps);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
       if ((c * 32 + lane) * V < H) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) sv = fmaf(v[c][i] - mean, v[c][i] - mean, sv);
+        for (int i = 0; i < V; ++i) {
+          if (has_z) zg[c][i] = siluf_(zg[c][i]);
+          if (pre_gate) v[c][i] *= zg[c][i];
+          s1 += v[c][i];
+          s2 = fmaf(v[c][i], v[c][i], s2);
+        }
       }
-    var = warp_sum(sv) / H;
-  }
-  const float rstd = rsqrtf(var + np.eps);
-  if (lane == 0) {
-    np.rstd[row] = rstd;
-    if (!np.is_rms && np.mean) np.mean[row] = mean;
-  }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    float mean = 0.f, var;
+    if (np.is_rms) {
+      var = s2 / H;
+    } else {
+      mean = s1 / H;
+      float sv = 0.f;
 #pragma unroll
-  for (int c = 0; c < CH; ++c) {
-    const int f0 = (c * 32 + lane) * V;
-    if (f0 < H) {
-      float w[V], o[V];
-      Vec16<float>::load(np.weight + f0, w);
-      if (V == 8) Vec16<float>::load(np.weight + f0 + 4, w + 4);
+      for (int c = 0; c < CH; ++c)
+        if ((c * 32 + lane) * V < H) {
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        o[i] = (v[c][i] - mean) * rstd * w[i];
-        if (np.has_bias) o[i] += np.bias[f0 + i];
-        if (post_gate) o[i] *= zg[c][i];
+          for (int i = 0; i < V; ++i) sv = fmaf(v[c][i] - mean, v[c][i] - mean, sv);
+        }
+      var = warp_sum(sv) / H;
+    }
+    const float rstd = rsqrtf(var + np.eps);
+    if (lane == 0) {
+      np.rstd[row] = rstd;
+      if (!np.is_rms && np.mean) np.mean[row] = mean;
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int f0 = (c * 32 + lane) * V;
+      if (f0 < H) {
+        float w[V], o[V];
+        Vec16<float>::load(np.weight + f0, w);
+        if (V == 8) Vec16<float>::load(np.weight + f0 + 4, w + 4);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          o[i] = (v[c][i] - mean) * rstd * w[i];
+          if (np.has_bias) o[i] += np.bias[f0 + i];
+          if (post_gate) o[i] *= zg[c][i];
+        }
+        Vec16<T>::store(y + f0, o);
       }
-      Vec16<T>::store(y + f0, o);
     }
   }
 }
@@ -182,23 +208,49 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
     for (int i = 0; i < V; ++i) { dwacc[c][i] = 0.f; dbacc[c][i] = 0.f; w[c][i] = f0 < H ? np.weight[f0 + i] : 0.f; }
   }
   const int r_end = min(np.rows, (int)(blockIdx.x + 1) * rpb);
-  for (int row = blockIdx.x * rpb + warp; row < r_end; row += NORM_BWD_WARPS) {
+  const bool has_z = np.has_z != 0;
+  // the 16-byte loads of the warp's next row are issued (kept packed, 4 registers per chunk) before the current row is
+  // worked on
+  uint4 nx[CH], ng[CH], nz[CH];
+  float nrstd = 0.f, nmean = 0.f;
+  auto issue = [&](int row) {
     const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
-    const T* z = np.has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
+    const T* zp = has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
     const T* dy = (const T*)np.dy + (int64_t)row * np.dy_sr;
-    T* dx = (T*)np.dx + (int64_t)row * H;
-    T* dz = np.has_z ? (T*)np.dz + (int64_t)row * H : nullptr;
-    const float rstd = np.rstd[row];
-    const float mean = np.is_rms ? 0.f : np.mean[row];
-    float xr[CH][V], zv[CH][V], go[CH][V];
-    float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int f0 = (c * 32 + lane) * V;
       if (f0 < H) {
-        Vec16<T>::load(x + f0, xr[c]);
-        Vec16<T>::load(dy + f0, go[c]);
-        if (z) Vec16<T>::load(z + f0, zv[c]);
+        nx[c] = *(const uint4*)(x + f0);
+        ng[c] = *(const uint4*)(dy + f0);
+        if (has_z) nz[c] = *(const uint4*)(zp + f0);
+      }
+    }
+    nrstd = np.rstd[row];
+    nmean = np.is_rms ? 0.f : np.mean[row];
+  };
+  if ((int)(blockIdx.x * rpb + warp) < r_end) issue(blockIdx.x * rpb + warp);
+  for (int row = blockIdx.x * rpb + warp; row < r_end; row += NORM_BWD_WARPS) {
+    const bool z = has_z;
+    T* dx = (T*)np.dx + (int64_t)row * H;
+    T* dz = has_z ? (T*)np.dz + (int64_t)row * H : nullptr;
+    const float rstd = nrstd;
+    const float mean = nmean;
+    float xr[CH][V], zv[CH][V], go[CH][V];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if ((c * 32 + lane) * V < H) {
+        Vec16<T>::unpack(nx[c], xr[c]);
+        Vec16<T>::unpack(ng[c], go[c]);
+        if (has_z) Vec16<T>::unpack(nz[c], zv[c]);
+      }
+    }
+    if (row + NORM_BWD_WARPS < r_end) issue(row + NORM_BWD_WARPS);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int f0 = (c * 32 + lane) * V;
+      if (f0 < H) {
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           const float vv = pre_gate ? xr[c][i] * siluf_(zv[c][i]) : xr[c][i];
@@ -220,7 +272,9 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           const float zz = z ? zv[c][i] : 0.f;
-          const float sz = z ? siluf_(zz) : 1.f;
+          const float sgm = z ? fast_sigmoid(zz) : 1.f;
+          const float sz = z ? zz * sgm : 1.f;
+          const float dsz = sgm * (1.f + zz * (1.f - sgm));   // d silu / dz
           const float vv = pre_gate ? xr[c][i] * sz : xr[c][i];
           const float xh = (vv - mean) * rstd;
           const float g_out = post_gate ? go[c][i] * sz : go[c][i];
@@ -230,12 +284,12 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
           dbacc[c][i] += g_out;
           if (pre_gate) {
             odx[i] = dv * sz;
-            odz[i] = dv * xr[c][i] * dsiluf_(zz);
+            odz[i] = dv * xr[c][i] * dsz;
           } else {
             odx[i] = dv;
             float yv = xh * w[c][i];
             if (np.has_bias) yv += np.bias[f0 + i];
-            odz[i] = post_gate ? go[c][i] * yv * dsiluf_(zz) : 0.f;
+            odz[i] = post_gate ? go[c][i] * yv * dsz : 0.f;
           }
         }
         Vec16<T>::store(dx + f0, odx);
@@ -351,12 +405,23 @@ __global__ void k_norm_bwd(issm_norm_params np, int rpb, float* __restrict__ dwp
   }
 }
 
-__global__ void k_norm_reduce(const float* __restrict__ part, int count, int stride, float* __restrict__ out) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= stride) return;
+// out[j] = sum over the `count` partial rows of part[i][j], in a fixed order: 32 features x 8 row groups per block;
+// group g adds rows g, g + 8, ... in order, then the eight group sums are added in order
+__global__ void __launch_bounds__(256) k_norm_reduce(const float* __restrict__ part, int count, int stride, float* __restrict__ out) {
+  __shared__ float sacc[8][33];
+  const int fx = threadIdx.x & 31, gy = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + fx;
   float acc = 0.f;
-  for (int i = 0; i < count; ++i) acc += part[(size_t)i * stride + j];
-  out[j] = acc;
+  if (j < stride)
+    for (int i = gy; i < count; i += 8) acc += part[(size_t)i * stride + j];
+  sacc[gy][fx] = acc;
+  __syncthreads();
+  if (gy == 0 && j < stride) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) t += sacc[g][fx];
+    out[j] = t;
+  }
 }
 
 static int norm_blocks(const issm_norm_params& p) {
@@ -410,11 +475,12 @@ extern "C" int issm_b200_norm_fwd(const issm_norm_params* p, void* stream) {
   const int wpb = 8;
   const unsigned grid = (p->rows + wpb - 1) / wpb;
   const int ch = norm_vec_chunks(*p, false);
+  const unsigned vgrid = grid < 148u * 4u ? grid : 148u * 4u;   // the vector kernel walks the rows with a grid stride (one resident wave)
 #define ISSM_NORM_FWD_VEC(T)                                                                                   \
   do {                                                                                                         \
-    if (ch == 1) ISSM_LAUNCH((k_norm_fwd_vec<T, 1>), grid, wpb * 32, 0, s, *p);                                \
-    else if (ch == 2) ISSM_LAUNCH((k_norm_fwd_vec<T, 2>), grid, wpb * 32, 0, s, *p);                           \
-    else ISSM_LAUNCH((k_norm_fwd_vec<T, 4>), grid, wpb * 32, 0, s, *p);                                        \
+    if (ch == 1) ISSM_LAUNCH((k_norm_fwd_vec<T, 1>), vgrid, wpb * 32, 0, s, *p);                               \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_fwd_vec<T, 2>), vgrid, wpb * 32, 0, s, *p);                          \
+    else ISSM_LAUNCH((k_norm_fwd_vec<T, 4>), vgrid, wpb * 32, 0, s, *p);                                       \
   } while (0)
   if (ch) {
     if (p->io_dtype == ISSM_F32) ISSM_NORM_FWD_VEC(float); else ISSM_NORM_FWD_VEC(bf16);
@@ -446,8 +512,8 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
   }
   rc = launch_norm_bwd_main(*p, nblk, rpb, dwpart, dbpart, smem, s);
   if (rc) return rc;
-  ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
-  if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
+  ISSM_LAUNCH(k_norm_reduce, (p->hidden + 31) / 32, 256, 0, s, dwpart, nblk, p->hidden, p->dweight);
+  if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 31) / 32, 256, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;
 }
 
@@ -504,7 +570,7 @@ extern "C" int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* strea
   // every block writes its whole row of partials, so nothing in the scratch has to start at zero
   rc = launch_norm_bwd_main(*p, nblk, rpb, dwpart, dbpart, smem, s);
   if (rc) return rc;
-  ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dwpart, nblk, p->hidden, p->dweight);
-  if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 127) / 128, 128, 0, s, dbpart, nblk, p->hidden, p->dbias);
+  ISSM_LAUNCH(k_norm_reduce, (p->hidden + 31) / 32, 256, 0, s, dwpart, nblk, p->hidden, p->dweight);
+  if (p->has_bias) ISSM_LAUNCH(k_norm_reduce, (p->hidden + 31) / 32, 256, 0, s, dbpart, nblk, p->hidden, p->dbias);
   return ISSM_OK;
 }

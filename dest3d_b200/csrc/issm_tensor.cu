@@ -427,7 +427,6 @@ __global__ void __launch_bounds__(2 * NT + 128, 1) k_fwd_tensor(const __grid_con
     for (int blk = 0; blk < nblk; ++blk) {
       const int row0 = blk * QB;
       const int rows = min(QB, a.L - row0);
-      const uint32_t parity = blk & 1;
       fence_before_sync();
       if (__syncthreads_or(failed)) { failed = true; break; }
       // A block some column flagged is redone in windows of ws = 64 >> kw rows (the operands built above are

@@ -100,49 +100,6 @@ __device__ __forceinline__ float dt_transform(const TArgs& a, float raw, float b
   return fminf(fmaxf(v, a.dtmin), a.dtmax);
 }
 
-// One pass over the 64 rows of a block for the state column owned by the calling thread: dt
-// transform, running cumulative log2-decay `a` (relative to the block start), and this column of the
-// two MMA operands
-//     Cd[l,n] = C[l,n] 2^(a[l])        Bd[l,n] = B[l,n] dt[l] 2^(-a[l])
-// written into the 128-byte-swizzle atoms (cd_col / bd_col point at the thread's 64-column atom).
-// Rows beyond `rows` are zero-filled.  sdt / sB / sC are the thread's column in the [64][NT] bf16
-// staging tiles; when dt or C is not staged it is read from global memory (row index clamped so
-// the address stays valid).  Returns a at the block end.
-template <int NT, typename TDT, bool kStageDt, bool kStageC>
-__device__ __forceinline__ float build_operands(const TArgs& a, int rows, int row0, int kcol,
-                                                const bf16* sdt, const TDT* __restrict__ dtg,
-                                                const bf16* sB, const bf16* sC, const bf16* __restrict__ Cg,
-                                                uint8_t* cd_col, uint8_t* bd_col, float A2, float bias) {
-  float acc = 0.f;
-#pragma unroll 1
-  for (int l0 = 0; l0 < QB; l0 += 8) {
-    float dv[8], cv[8], bv[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int l = l0 + j;
-      const int64_t mr = trow(a, row0 + min(l, rows - 1));
-      dv[j] = kStageDt ? __bfloat162float(sdt[l * NT]) : ldf(dtg + mr * a.dt_sl);
-      cv[j] = kStageC ? __bfloat162float(sC[l * NT]) : __bfloat162float(Cg[mr * a.C_sl]);
-      bv[j] = __bfloat162float(sB[l * NT]);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int l = l0 + j;
-      const bool valid = l < rows;
-      bool clamped;
-      const float v = valid ? dt_transform(a, dv[j], bias, clamped) : 0.f;
-      acc = fmaf(v, A2, acc);
-      const float cd = valid ? cv[j] * ex2f(acc) : 0.f;
-      const float bd = valid ? bv[j] * v * ex2f(-acc) : 0.f;
-      // l0 is a multiple of 8, so the swizzle term of row l only depends on j
-      const uint32_t off = (uint32_t)(l * 128 + ((((kcol >> 3) ^ j) << 4) | ((kcol & 7) << 1)));
-      *(bf16*)(cd_col + off) = __float2bfloat16_rn(cd);
-      *(bf16*)(bd_col + off) = __float2bfloat16_rn(bd);
-    }
-  }
-  return acc;
-}
-
 // ---- blocks outside the range of the single-reference factorisation (rare; kept out of line) -------------------
 // Smallest k in 1..6 such that, with the block cut into 2^k windows of 64 >> k rows, the summed log2-decay
 // of every window of this thread's 32 rows stays within 2^100 (k = 6, single rows, always qualifies: there
