@@ -3,3 +3,4 @@ Python interface.  Importing the operators requires the built CUDA library; ther
 from .issm_combined import (ISSM_chunk_scan_combined, ISSMChunkScanCombinedFn, issm_bidirectional_scan,  # noqa: F401
                             issm_bwd, issm_fwd, raise_on_device_error)
 from .layernorm_gated import LayerNorm, LayerNormFn, RMSNorm, layernorm_fn, rmsnorm_fn  # noqa: F401
+from .pointops import PointLiteConv, reorder_points  # noqa: F401

@@ -50,6 +50,16 @@ class IssmNormParams(C.Structure):
     )
 
 
+class IssmConvParams(C.Structure):
+    """Mirror of `issm_conv_params`."""
+    _fields_ = (
+        [(n, i32) for n in ("batch", "seqlen", "channels", "io_dtype")]
+        + [("x", vp), ("x_sb", i64), ("x_sl", i64), ("weight", vp), ("bias", vp), ("y", vp),
+           ("dy", vp), ("dy_sb", i64), ("dy_sl", i64), ("dx", vp), ("dweight", vp), ("dbias", vp),
+           ("workspace", vp), ("workspace_bytes", C.c_size_t)]
+    )
+
+
 class IssmError(RuntimeError):
     def __init__(self, code, what):
         self.code = code
@@ -72,7 +82,7 @@ def lib():
     L.issm_b200_version.restype = C.c_int
     L.issm_b200_strerror.restype = C.c_char_p
     L.issm_b200_strerror.argtypes = [C.c_int]
-    for name in ("issm_b200_sizeof_params", "issm_b200_sizeof_norm_params"):
+    for name in ("issm_b200_sizeof_params", "issm_b200_sizeof_norm_params", "issm_b200_sizeof_conv_params"):
         getattr(L, name).restype = C.c_size_t
     L.issm_b200_workspace_bytes.restype = C.c_size_t
     L.issm_b200_workspace_bytes.argtypes = [C.POINTER(IssmParams), C.c_int]
@@ -88,7 +98,16 @@ def lib():
     for name in ("issm_b200_norm_fwd", "issm_b200_norm_bwd"):
         getattr(L, name).restype = C.c_int
         getattr(L, name).argtypes = [C.POINTER(IssmNormParams), vp]
+    L.issm_b200_dwconv_workspace_bytes.restype = C.c_size_t
+    L.issm_b200_dwconv_workspace_bytes.argtypes = [C.POINTER(IssmConvParams)]
+    for name in ("issm_b200_dwconv7_silu_fwd", "issm_b200_dwconv7_silu_bwd"):
+        getattr(L, name).restype = C.c_int
+        getattr(L, name).argtypes = [C.POINTER(IssmConvParams), vp]
+    L.issm_b200_gather_rows.restype = C.c_int
+    L.issm_b200_gather_rows.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, vp]
     L.issm_b200_launch_count.restype = C.c_uint64
+    if L.issm_b200_sizeof_conv_params() != C.sizeof(IssmConvParams):
+        raise RuntimeError("libissm_b200.so and dest3d_b200/_lib.py disagree on issm_conv_params; rebuild")
     if L.issm_b200_sizeof_params() != C.sizeof(IssmParams) or L.issm_b200_sizeof_norm_params() != C.sizeof(IssmNormParams):
         raise RuntimeError("libissm_b200.so and dest3d_b200/_lib.py disagree on the parameter struct layout; rebuild")
     _lib = L

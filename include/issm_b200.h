@@ -179,6 +179,39 @@ int issm_b200_norm_bwd(const issm_norm_params* p, void* cuda_stream);
  *     GPU - different streams, or different host threads - race on it: serialise them. */
 int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* cuda_stream);
 
+/* ---- the point-wise steps on either side of the scan in the detector's ISSM block ----------------------- */
+
+/* Serialization gather (models/dest_module.py:378-397, points.gather(dim = 1, index)): for every batch b and
+ * output row i, dst[b, i, :] = src[b, index[b, i], :].  Rows are `row_bytes` contiguous bytes (even); dst is
+ * (batch, n_out, row_bytes) contiguous, src rows are src_row_bytes apart and batches src_batch_bytes apart; index is
+ * (batch, n_out) int64, contiguous.  An index outside [0, n_src) copies nothing for that row and ORs bit 1 (value 2)
+ * into *status (optional). */
+int issm_b200_gather_rows(const void* src, const int64_t* index, void* dst, int32_t batch, int32_t n_out, int32_t n_src,
+                          int64_t row_bytes, int64_t src_batch_bytes, int64_t src_row_bytes, int32_t* status, void* cuda_stream);
+
+/* PointLiteConv (models/dest_module.py:400-423): y = silu(conv + bias), conv a depthwise 1-D convolution with 7 taps
+ * and zero padding 3 along the point axis of a channels-last (batch, seqlen, channels) tensor - what the reference
+ * computes as nn.Conv1d(C, C, 7, padding = 3, groups = C) on the transposed tensor followed by nn.SiLU. */
+typedef struct issm_conv_params {
+  int32_t batch, seqlen, channels;
+  int32_t io_dtype;                       /* x, y, dy, dx */
+  const void* x; int64_t x_sb, x_sl;      /* element strides of batch and point; channel stride 1 */
+  const float* weight;                    /* (channels, 7): Conv1d's (C, 1, 7) weight as float */
+  const float* bias;                      /* (channels) or null */
+  void* y;                                /* (batch, seqlen, channels) contiguous */
+  /* backward */
+  const void* dy; int64_t dy_sb, dy_sl;
+  void* dx;                               /* contiguous */
+  float* dweight;                         /* (channels, 7) */
+  float* dbias;                           /* (channels) or null */
+  void* workspace; size_t workspace_bytes;/* backward only; 256-byte aligned */
+} issm_conv_params;
+
+size_t issm_b200_sizeof_conv_params(void);
+size_t issm_b200_dwconv_workspace_bytes(const issm_conv_params* p);
+int issm_b200_dwconv7_silu_fwd(const issm_conv_params* p, void* cuda_stream);
+int issm_b200_dwconv7_silu_bwd(const issm_conv_params* p, void* cuda_stream);
+
 /* Number of kernel launches the library has enqueued since load (monotonic, process-wide);
  * used by the benchmark to report how many of its own kernels ran inside a timed region. */
 uint64_t issm_b200_launch_count(void);
