@@ -120,3 +120,31 @@ def test_operators_refuse_cpu_tensors(built_lib):
     from dest3d_b200 import RMSNorm
     with pytest.raises(RuntimeError):
         RMSNorm(16)(torch.randn(2, 16))
+
+
+def test_point_ops_validation(built_lib):
+    """Serialization gather and PointLiteConv entry points: struct layout and the codes returned before any launch."""
+    import torch
+    from dest3d_b200 import PointLiteConv, _lib, reorder_points
+    L = _lib.lib()
+    assert L.issm_b200_sizeof_conv_params() == C.sizeof(_lib.IssmConvParams)
+    p = _lib.IssmConvParams()
+    assert L.issm_b200_dwconv7_silu_fwd(None, None) == 1
+    assert L.issm_b200_dwconv7_silu_fwd(C.byref(p), None) == 2                # zero sizes
+    p.batch, p.seqlen, p.channels = 2, 100, 290
+    assert L.issm_b200_dwconv7_silu_fwd(C.byref(p), None) == 1                # null pointers
+    p.io_dtype = 9
+    assert L.issm_b200_dwconv7_silu_fwd(C.byref(p), None) == 3
+    p.io_dtype = _lib.BF16
+    p.x = p.weight = p.dy = p.dx = p.dweight = 4096
+    assert L.issm_b200_dwconv7_silu_bwd(C.byref(p), None) == 4                # no workspace
+    need = L.issm_b200_dwconv_workspace_bytes(C.byref(p))
+    assert need >= 2 * 290 * 8 * 4 and need % 256 == 0
+    assert L.issm_b200_gather_rows(None, None, None, 1, 1, 1, 8, 8, 8, None, None) == 1
+    assert L.issm_b200_gather_rows(4096, 4096, 4096, 1, 4, 4, 7, 28, 7, None, None) == 2   # odd row bytes
+    with pytest.raises(RuntimeError):
+        PointLiteConv(8, 8)(None, torch.randn(1, 10, 8))
+    with pytest.raises(RuntimeError):
+        reorder_points(torch.randn(1, 10, 8), torch.zeros(1, 10, dtype=torch.int64))
+    with pytest.raises(ValueError):
+        PointLiteConv(8, 16)
