@@ -11,7 +11,6 @@ namespace issm {
 
 constexpr int CONV_K = 7, CONV_PAD = 3;
 
-__device__ __forceinline__ float fast_sigmoid_(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
 
 // ---- gather ----------------------------------------------------------------------------------------------
 // one warp per destination row; VEC = bytes per lane access (16, 4 or 2)
@@ -51,65 +50,94 @@ struct ConvArgs {
 constexpr int CONV_SEGS = 8;
 constexpr int CONV_R = 8;                                 // rows loaded ahead of their use
 
-__device__ __forceinline__ void ldv(const float* p, float (&v)[1]) { v[0] = *p; }
-__device__ __forceinline__ void ldv(const float* p, float (&v)[2]) { const float2 t = *(const float2*)p; v[0] = t.x; v[1] = t.y; }
-__device__ __forceinline__ void ldv(const bf16* p, float (&v)[1]) { v[0] = __bfloat162float(*p); }
-__device__ __forceinline__ void ldv(const bf16* p, float (&v)[2]) {
-  const float2 t = __bfloat1622float2(*(const __nv_bfloat162*)p); v[0] = t.x; v[1] = t.y;
+// The value a thread carries per row: one channel (float) or two adjacent ones (float2, packed fp32 arithmetic).
+template <int V> struct Val { using t = float; };
+template <> struct Val<2> { using t = float2; };
+
+__device__ __forceinline__ float ex2_ftz(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_ftz(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+__device__ __forceinline__ void vzero(float& v) { v = 0.f; }
+__device__ __forceinline__ void vzero(float2& v) { v = make_float2(0.f, 0.f); }
+__device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ float2 vfma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float vmul(float a, float b) { return a * b; }
+__device__ __forceinline__ float2 vmul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float vadd(float a, float b) { return a + b; }
+__device__ __forceinline__ float2 vadd(float2 a, float2 b) { return __fadd2_rn(a, b); }
+// 1 / (1 + 2^(-v log2 e)); exact 0 and 1 at the two ends of the range
+__device__ __forceinline__ float vsigmoid(float v) { return rcp_ftz(1.f + ex2_ftz(-1.4426950408889634f * v)); }
+__device__ __forceinline__ float2 vsigmoid(float2 v) {
+  const float2 t = __fmul2_rn(v, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  const float2 e = __fadd2_rn(make_float2(ex2_ftz(t.x), ex2_ftz(t.y)), make_float2(1.f, 1.f));
+  return make_float2(rcp_ftz(e.x), rcp_ftz(e.y));
 }
-__device__ __forceinline__ void stv(float* p, const float (&v)[1]) { *p = v[0]; }
-__device__ __forceinline__ void stv(float* p, const float (&v)[2]) { *(float2*)p = make_float2(v[0], v[1]); }
-__device__ __forceinline__ void stv(bf16* p, const float (&v)[1]) { *p = __float2bfloat16_rn(v[0]); }
-__device__ __forceinline__ void stv(bf16* p, const float (&v)[2]) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(v[0], v[1]); }
+// silu'(pre) = s (1 + pre (1 - s))
+__device__ __forceinline__ float vdsilu(float pre, float s) { return s * fmaf(pre, 1.f - s, 1.f); }
+__device__ __forceinline__ float2 vdsilu(float2 pre, float2 s) {
+  const float2 one = make_float2(1.f, 1.f);
+  return __fmul2_rn(s, __ffma2_rn(pre, make_float2(1.f - s.x, 1.f - s.y), one));
+}
+__device__ __forceinline__ float vlane(float v, int) { return v; }
+__device__ __forceinline__ float vlane(float2 v, int i) { return i ? v.y : v.x; }
+
+__device__ __forceinline__ void ldv(const float* p, float& v) { v = *p; }
+__device__ __forceinline__ void ldv(const float* p, float2& v) { v = *(const float2*)p; }
+__device__ __forceinline__ void ldv(const bf16* p, float& v) { v = __bfloat162float(*p); }
+__device__ __forceinline__ void ldv(const bf16* p, float2& v) { v = __bfloat1622float2(*(const __nv_bfloat162*)p); }
+__device__ __forceinline__ void stv(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stv(float* p, float2 v) { *(float2*)p = v; }
+__device__ __forceinline__ void stv(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void stv(bf16* p, float2 v) { *(__nv_bfloat162*)p = __float22bfloat162_rn(v); }
+__device__ __forceinline__ void ldw(const float* w, int C, int c, int stride, int k, float& v) { v = w[c * stride + k]; }
+__device__ __forceinline__ void ldw(const float* w, int C, int c, int stride, int k, float2& v) {
+  v = make_float2(w[c * stride + k], w[(c + 1) * stride + k]);
+}
 
 template <typename T, int V>
 __global__ void __launch_bounds__(256) k_dwconv7_silu_fwd(ConvArgs a) {
+  using F = typename Val<V>::t;
   constexpr int R = CONV_R;
   const int c = (blockIdx.x * 32 + threadIdx.x) * V;
   const int b = blockIdx.z;
   const int n0 = (blockIdx.y * CONV_SEGS + threadIdx.y) * a.tr, n1 = min(a.N, n0 + a.tr);
   if (c >= a.C || n0 >= a.N) return;
   const T* x = (const T*)a.x + b * a.x_sb + c;
-  T* y = (T*)a.y + (int64_t)b * a.N * a.C + c;
-  float w[CONV_K][V], bias[V];
+  T* y = (T*)a.y + ((int64_t)b * a.N + n0) * a.C + c;
+  F w[CONV_K], bias;
+  vzero(bias);
+  if (a.bias) ldw(a.bias, a.C, c, 1, 0, bias);
 #pragma unroll
-  for (int v = 0; v < V; ++v) {
-    bias[v] = a.bias ? a.bias[c + v] : 0.f;
-#pragma unroll
-    for (int k = 0; k < CONV_K; ++k) w[k][v] = a.w[(c + v) * CONV_K + k];
-  }
-  auto fetch = [&](int n, float (&d)[V]) {
+  for (int k = 0; k < CONV_K; ++k) ldw(a.w, a.C, c, CONV_K, k, w[k]);
+  auto fetch = [&](int n, F& d) {
     if (n >= 0 && n < a.N) ldv(x + (int64_t)n * a.x_sl, d);
-    else {
-#pragma unroll
-      for (int v = 0; v < V; ++v) d[v] = 0.f;
-    }
+    else vzero(d);
   };
   // rows n - 3 .. n + R + 2 of a batch of R output rows; the R loads of a batch are issued before any is used
-  float buf[CONV_K - 1 + R][V];
+  F buf[CONV_K - 1 + R];
 #pragma unroll
   for (int k = 0; k < CONV_K - 1; ++k) fetch(n0 - CONV_PAD + k, buf[k]);
   for (int n = n0; n < n1; n += R) {
+    if (n + CONV_PAD + R <= a.N) {                         // the whole batch lies inside the sequence: no per-row test
+      const T* px = x + (int64_t)(n + CONV_PAD) * a.x_sl;
 #pragma unroll
-    for (int r = 0; r < R; ++r) fetch(n + CONV_PAD + r, buf[CONV_K - 1 + r]);
+      for (int r = 0; r < R; ++r) ldv(px + (int64_t)r * a.x_sl, buf[CONV_K - 1 + r]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) fetch(n + CONV_PAD + r, buf[CONV_K - 1 + r]);
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (n + r < n1) {
-        float o[V];
+        F pre = bias;
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-          float pre = bias[v];
-#pragma unroll
-          for (int k = 0; k < CONV_K; ++k) pre = fmaf(w[k][v], buf[r + k][v], pre);
-          o[v] = pre * fast_sigmoid_(pre);
-        }
-        stv(y + (int64_t)(n + r) * a.C, o);
+        for (int k = 0; k < CONV_K; ++k) pre = vfma(w[k], buf[r + k], pre);
+        stv(y + (int64_t)r * a.C, vmul(pre, vsigmoid(pre)));
       }
     }
+    y += (int64_t)R * a.C;
 #pragma unroll
-    for (int k = 0; k < CONV_K - 1; ++k)
-#pragma unroll
-      for (int v = 0; v < V; ++v) buf[k][v] = buf[R + k][v];
+    for (int k = 0; k < CONV_K - 1; ++k) buf[k] = buf[R + k];
   }
 }
 
@@ -117,99 +145,86 @@ __global__ void __launch_bounds__(256) k_dwconv7_silu_fwd(ConvArgs a) {
 // and kept in a 7-row register window, so dx[n] = sum_k w[k] g[n - k + 3] needs no intermediate in global memory.
 template <typename T, int V>
 __global__ void __launch_bounds__(256) k_dwconv7_silu_bwd(ConvArgs a) {
+  using F = typename Val<V>::t;
+  constexpr int R = CONV_R;
   __shared__ float red[CONV_SEGS][8][32 * V];
   const int c = (blockIdx.x * 32 + threadIdx.x) * V;
   const int b = blockIdx.z;
   const int n0 = (blockIdx.y * CONV_SEGS + threadIdx.y) * a.tr, n1 = min(a.N, n0 + a.tr);
   const bool live = c < a.C && n0 < a.N;
-  float dw[CONV_K][V], db[V];
+  F dw[CONV_K], db;
+  vzero(db);
 #pragma unroll
-  for (int v = 0; v < V; ++v) {
-    db[v] = 0.f;
-#pragma unroll
-    for (int k = 0; k < CONV_K; ++k) dw[k][v] = 0.f;
-  }
+  for (int k = 0; k < CONV_K; ++k) vzero(dw[k]);
   if (live) {
     const T* x = (const T*)a.x + b * a.x_sb + c;
     const T* dy = (const T*)a.dy + b * a.dy_sb + c;
     T* dx = (T*)a.dx + (int64_t)b * a.N * a.C + c;
-    float w[CONV_K][V], bias[V];
+    F w[CONV_K], bias;
+    vzero(bias);
+    if (a.bias) ldw(a.bias, a.C, c, 1, 0, bias);
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-      bias[v] = a.bias ? a.bias[c + v] : 0.f;
-#pragma unroll
-      for (int k = 0; k < CONV_K; ++k) w[k][v] = a.w[(c + v) * CONV_K + k];
-    }
-    auto fetch = [&](const T* base, int64_t stride, int n, float (&d)[V]) {
+    for (int k = 0; k < CONV_K; ++k) ldw(a.w, a.C, c, CONV_K, k, w[k]);
+    auto fetch = [&](const T* base, int64_t stride, int n, F& d) {
       if (n >= 0 && n < a.N) ldv(base + (int64_t)n * stride, d);
-      else {
-#pragma unroll
-        for (int v = 0; v < V; ++v) d[v] = 0.f;
-      }
+      else vzero(d);
     };
-    float xb[CONV_K - 1 + CONV_R][V], gyb[CONV_R][V], gw[CONV_K][V];   // x[m - 3 .. m + R + 2]; dy[m .. m + R); g[m - 6 .. m]
+    F xb[CONV_K - 1 + R], gyb[R], gb[CONV_K - 1 + R];      // x[m - 3 .. m + R + 2]; dy[m .. m + R); g[m - 6 .. m + R)
     const int m0 = n0 - CONV_PAD, m1 = n1 + CONV_PAD;
 #pragma unroll
     for (int k = 0; k < CONV_K - 1; ++k) fetch(x, a.x_sl, m0 - CONV_PAD + k, xb[k]);
 #pragma unroll
-    for (int k = 0; k < CONV_K; ++k)
+    for (int k = 0; k < CONV_K - 1; ++k) vzero(gb[k]);
+    for (int mb = m0; mb < m1; mb += R) {
+      if (mb >= 0 && mb + CONV_PAD + R <= a.N) {           // whole batch inside the sequence
+        const T* px = x + (int64_t)(mb + CONV_PAD) * a.x_sl;
+        const T* pg = dy + (int64_t)mb * a.dy_sl;
 #pragma unroll
-      for (int v = 0; v < V; ++v) gw[k][v] = 0.f;
-    for (int mb = m0; mb < m1; mb += CONV_R) {
+        for (int r = 0; r < R; ++r) {
+          ldv(px + (int64_t)r * a.x_sl, xb[CONV_K - 1 + r]);
+          ldv(pg + (int64_t)r * a.dy_sl, gyb[r]);
+        }
+      } else {
 #pragma unroll
-      for (int r = 0; r < CONV_R; ++r) {
-        fetch(x, a.x_sl, mb + CONV_PAD + r, xb[CONV_K - 1 + r]);
-        fetch(dy, a.dy_sl, mb + r, gyb[r]);                // zero outside the sequence, so g is zero there too
+        for (int r = 0; r < R; ++r) {
+          fetch(x, a.x_sl, mb + CONV_PAD + r, xb[CONV_K - 1 + r]);
+          fetch(dy, a.dy_sl, mb + r, gyb[r]);              // zero outside the sequence, so g is zero there too
+        }
       }
 #pragma unroll
-      for (int r = 0; r < CONV_R; ++r) {
+      for (int r = 0; r < R; ++r) {
         const int m = mb + r;
         if (m < m1) {
+          F pre = bias;
 #pragma unroll
-          for (int k = 0; k < CONV_K - 1; ++k)
+          for (int k = 0; k < CONV_K; ++k) pre = vfma(w[k], xb[r + k], pre);
+          const F g = vmul(gyb[r], vdsilu(pre, vsigmoid(pre)));
+          gb[CONV_K - 1 + r] = g;
+          if (m >= n0 && m < n1) {                         // rows of this segment; halo rows belong to a neighbour
+            db = vadd(db, g);
 #pragma unroll
-            for (int v = 0; v < V; ++v) gw[k][v] = gw[k + 1][v];
-          const bool own = m >= n0 && m < n1;
-#pragma unroll
-          for (int v = 0; v < V; ++v) {
-            float pre = bias[v];
-#pragma unroll
-            for (int k = 0; k < CONV_K; ++k) pre = fmaf(w[k][v], xb[r + k][v], pre);
-            const float sg = fast_sigmoid_(pre);
-            const float g = gyb[r][v] * sg * (1.f + pre * (1.f - sg));
-            gw[CONV_K - 1][v] = g;
-            if (own) {
-              db[v] += g;
-#pragma unroll
-              for (int k = 0; k < CONV_K; ++k) dw[k][v] = fmaf(g, xb[r + k][v], dw[k][v]);
-            }
+            for (int k = 0; k < CONV_K; ++k) dw[k] = vfma(g, xb[r + k], dw[k]);
           }
-          const int n = m - CONV_PAD;                      // gw = g[n - 3 .. n + 3]
+          const int n = m - CONV_PAD;                      // gb[r .. r + 6] = g[n - 3 .. n + 3]
           if (n >= n0) {
-            float o[V];
+            F acc;
+            vzero(acc);
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-              float acc = 0.f;
-#pragma unroll
-              for (int k = 0; k < CONV_K; ++k) acc = fmaf(w[k][v], gw[CONV_K - 1 - k][v], acc);
-              o[v] = acc;
-            }
-            stv(dx + (int64_t)n * a.C, o);
+            for (int k = 0; k < CONV_K; ++k) acc = vfma(w[k], gb[r + CONV_K - 1 - k], acc);
+            stv(dx + (int64_t)n * a.C, acc);
           }
         }
       }
 #pragma unroll
-      for (int k = 0; k < CONV_K - 1; ++k)
-#pragma unroll
-        for (int v = 0; v < V; ++v) xb[k][v] = xb[CONV_R + k][v];
+      for (int k = 0; k < CONV_K - 1; ++k) { xb[k] = xb[R + k]; gb[k] = gb[R + k]; }
     }
   }
   // the block's 8 segments, summed in a fixed order
 #pragma unroll
   for (int v = 0; v < V; ++v) {
 #pragma unroll
-    for (int k = 0; k < CONV_K; ++k) red[threadIdx.y][k][threadIdx.x * V + v] = dw[k][v];
-    red[threadIdx.y][7][threadIdx.x * V + v] = db[v];
+    for (int k = 0; k < CONV_K; ++k) red[threadIdx.y][k][threadIdx.x * V + v] = vlane(dw[k], v);
+    red[threadIdx.y][7][threadIdx.x * V + v] = vlane(db, v);
   }
   __syncthreads();
   const int t = threadIdx.y * 32 + threadIdx.x;
@@ -261,7 +276,8 @@ static ConvPlan conv_plan(const issm_conv_params& p, bool bwd) {
   const int slots = (p.channels + pl.V - 1) / pl.V;
   const int gx = (slots + 31) / 32;
   auto gy = [&](int tr) { return (p.seqlen + tr * CONV_SEGS - 1) / (tr * CONV_SEGS); };
-  pl.tr = ((int64_t)gx * gy(64) * p.batch >= 148 * 4) ? 64 : 16;   // short rows of work when the problem is small
+  // long segments (fewer halo rows) when there are enough blocks to fill the GPU several times over
+  pl.tr = ((int64_t)gx * gy(128) * p.batch >= 148 * 8) ? 128 : ((int64_t)gx * gy(64) * p.batch >= 148 * 4) ? 64 : 16;
   pl.grid = dim3(gx, gy(pl.tr), p.batch);
   return pl;
 }
