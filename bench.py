@@ -45,6 +45,12 @@ WORKLOADS = {
     "c2": dict(batch1=16, global_multi=64, L=4096, H=8, P=36, N=512, Q=128, kind="stack_fwd", layers=6,
                desc="6 stacked bidirectional ISSM layers, forward only, final states of a layer are the next layer's "
                     "initial states (the six layers share x, B, C, dt and differ in A, D and the incoming states)"),
+    "scene": dict(batch1=1, global_multi=8, L=40000, H=8, P=36, N=256, Q=256, kind="layer",
+                  desc="ONE large scene per GPU, fwd+bwd, bidirectional: 8 (sample, head) streams for 148 SMs unless the "
+                       "sequence is cut into slices (--slices)"),
+    "scene16": dict(batch1=1, global_multi=8, L=640000, H=8, P=36, N=256, Q=256, kind="layer",
+                    desc="one sequence of 640000 points (16 scenes' worth), fwd+bwd, bidirectional; meant for --slices / "
+                         "--sequence-parallel"),
     "c0": dict(batch1=2, global_multi=2, L=1024, H=8, P=36, N=256, Q=256, kind="layer", desc="CPU-runnable reference case"),
 }
 METRIC, UNIT = "issm_fwd_bwd_points_states_per_s", "points*states/s"
@@ -171,9 +177,26 @@ def _two_directions(call_f, call_b):
     return yf, sf, yb, sb
 
 
+SEQPAR = False  # --sequence-parallel: the ranks hold consecutive parts of ONE sequence (dest3d_b200.seqpar)
+SLICES = 1      # --slices: cut every sequence into this many slices run as extra batch entries (0 = chosen from the sizes)
+
+
 def layer_step(dev, par, dfinal, w, path):
     """One step of the workload through the public interface.  Returns (out, final states, parameter gradients)."""
     from dest3d_b200 import ISSM_chunk_scan_combined, rmsnorm_fn
+    if SEQPAR:
+        from dest3d_b200.seqpar import issm_scan_sequence_parallel
+
+        def ISSM_chunk_scan_combined(*a, return_final_states=True, **k):   # noqa: F811
+            return issm_scan_sequence_parallel(*a, slices=SLICES or None, **k)
+    elif SLICES != 1:
+        from dest3d_b200.seqpar import issm_scan_chunk_parallel
+        plain = ISSM_chunk_scan_combined
+
+        def ISSM_chunk_scan_combined(*a, **k):             # noqa: F811  (same signature plus the slice count)
+            if w["kind"] == "stack_fwd":
+                return plain(*a, **k)
+            return issm_scan_chunk_parallel(*a, slices=SLICES or None, **k)
     main = torch.cuda.current_stream()
     s1, s2 = _streams()
     kind = w["kind"]
@@ -226,8 +249,23 @@ def run_mine(args):
     dtype = DTYPES[args.dtype]
     gbatch = w["batch1"] if world == 1 else w["global_multi"]
     mine = shard_samples(gbatch, world, rank)
+    seqpar = SEQPAR and world > 1
+    if seqpar:                                             # every rank: all samples, 1 / world of the points
+        gbatch = w["batch1"]
+        mine = range(0, gbatch)
     batch = len(mine)
-    host, par, dfinal = make_batch(w, batch, mine.start, pin=True, dtype=dtype)
+    L_total = w["L"]
+    # With several ranks pulling their inputs from host memory at once, pin each rank's buffers on its GPU's NUMA
+    # node (skipped at one GPU, where the CPU baseline leg wants every core; ISSM_BENCH_NUMA=0 switches it off).
+    numa_cpus = 0
+    if world > 1 and os.environ.get("ISSM_BENCH_NUMA", "1") != "0":
+        from dest3d_b200.dist import bind_to_gpu_numa_node
+        numa_cpus = bind_to_gpu_numa_node(local)
+    host, par, dfinal = make_batch(w, batch, mine.start, pin=not seqpar, dtype=dtype)
+    if seqpar:
+        lo, hi = L_total * rank // world, L_total * (rank + 1) // world
+        host = {k: (v if k == "init" else v[:, lo:hi].contiguous()).pin_memory() for k, v in host.items()}
+        w = dict(w, L=hi - lo)
     dev = {k: v.to(device, non_blocking=True) for k, v in host.items()}
     par = {k: v.to(device) for k, v in par.items()}
     dfinal = dfinal.to(device)
@@ -276,7 +314,7 @@ def run_mine(args):
     clocks = sampler.stop() if rank == 0 else None
     status = status_or_die("the timed region")
     L, H, P, N = w["L"], w["H"], w["P"], w["N"]
-    value = gbatch * L * N * nl * args.steps / (ms * 1e-3)
+    value = gbatch * L_total * N * nl * args.steps / (ms * 1e-3)
 
     # The same step replayed from a CUDA graph (one GPU, --graph): at the detector's size a step is ~20 short launches
     # and the eager number is bound by launch latency; a training loop with static shapes can capture it once.
@@ -302,7 +340,7 @@ def run_mine(args):
             torch.cuda.synchronize()
             gms = e0.elapsed_time(e1) / args.steps
             status_or_die("the graph replay")
-            graph_info = {"ms_per_step": gms, "value": gbatch * L * N * nl / (gms * 1e-3), "unit": UNIT}
+            graph_info = {"ms_per_step": gms, "value": gbatch * L_total * N * nl / (gms * 1e-3), "unit": UNIT}
             del graph
         except Exception as exc:                            # a capture that is refused is reported, not fatal
             graph_info = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
@@ -350,7 +388,7 @@ def run_mine(args):
     e1.record()
     sync_all()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1), device)
-    e2e_value = gbatch * L * N * nl * e2e_steps / (ms_e2e * 1e-3)
+    e2e_value = gbatch * L_total * N * nl * e2e_steps / (ms_e2e * 1e-3)
     status_or_die("the end-to-end region")
 
     # roofline of the dominant kernel, timed live with CUDA events on the launching stream
@@ -362,18 +400,20 @@ def run_mine(args):
     if rank == 0:
         line = {"metric": METRIC if w["kind"] != "stack_fwd" else "issm_fwd_points_states_per_s", "value": value, "unit": UNIT,
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if seqpar else "weak",
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
                 "config": {"workload": f"{args.workload}: {w['desc']}", "global_batch": gbatch, "per_gpu_batch": batch,
-                           "seqlen": L, "nheads": H, "headdim": P, "dstate": N, "chunk_size": w["Q"], "directions": 2,
-                           "layers": nl, "path": path, "resolved_path": roof.get("resolved_path") if roof else None,
+                           "seqlen": L_total, "points_per_gpu": L if seqpar else None, "nheads": H, "headdim": P, "dstate": N, "chunk_size": w["Q"], "directions": 2,
+                           "layers": nl, "path": path, "slices_per_sequence": SLICES, "resolved_path": roof.get("resolved_path") if roof else None,
                            "l2": "inputs larger than L2 (no flush needed)",
                            "scaling_note": "N = 1 runs batch 16, N > 1 a global batch of 64 split over the ranks: compare "
                                            "points*states/s across N, not step times",
-                           "parallelism": f"dp{world} by sample, both directions on one GPU"},
+                           "parallelism": (f"sp{world}: every rank holds 1/{world} of the points of every sequence" if seqpar
+                                           else f"dp{world} by sample, both directions on one GPU")},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
-                        "pipelining": "H2D of step i+1 overlaps the layer of step i (two device buffer sets)"},
+                        "pipelining": "H2D of step i+1 overlaps the layer of step i (two device buffer sets)",
+                        "host_numa_bound_cpus": numa_cpus},
                 "gpu_launches": int(launches), "cuda_graph": graph_info, "device_status": status, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -568,8 +608,13 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES))
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="N > 1: the ranks hold consecutive parts of the same sequences instead of different samples")
+    ap.add_argument("--slices", type=int, default=1, help="slices per sequence run as extra batch entries (0 = automatic)")
     ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph (one GPU)")
     args = ap.parse_args()
+    global SLICES, SEQPAR
+    SLICES, SEQPAR = args.slices, args.sequence_parallel
     if args.impl == "reference":
         run_reference(args)
     else:

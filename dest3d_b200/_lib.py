@@ -105,6 +105,8 @@ def lib():
         getattr(L, name).argtypes = [C.POINTER(IssmConvParams), vp]
     L.issm_b200_gather_rows.restype = C.c_int
     L.issm_b200_gather_rows.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, vp]
+    L.issm_b200_dt_sum.restype = C.c_int
+    L.issm_b200_dt_sum.argtypes = [vp, i32, i32, i32, i32, i32, i64, i64, i64, vp, i32, f32, f32, i32, vp, vp]
     L.issm_b200_launch_count.restype = C.c_uint64
     if L.issm_b200_sizeof_conv_params() != C.sizeof(IssmConvParams):
         raise RuntimeError("libissm_b200.so and dest3d_b200/_lib.py disagree on issm_conv_params; rebuild")

@@ -35,13 +35,20 @@ class PackedParamGrads:
             off += n
 
     def load(self, grads):
-        """Copy (and cast to float32) the given gradients into the flat buffer; missing names are zeroed."""
+        """Copy (and cast to float32) the given gradients into the flat buffer; missing names are zeroed.
+        All present gradients go in ONE multi-tensor copy launch."""
+        dst, src, absent = [], [], []
         for k in self.names:
             g = grads.get(k)
             if g is None:
-                self.views[k].zero_()
+                absent.append(self.views[k])
             else:
-                self.views[k].copy_(g.reshape(self.shapes[k]))
+                dst.append(self.views[k])
+                src.append(g.detach().reshape(self.shapes[k]))
+        if absent:
+            torch._foreach_zero_(absent)
+        if dst:
+            torch._foreach_copy_(dst, src)
         return self
 
     def all_reduce(self, group=None, average=False):
@@ -59,3 +66,23 @@ def max_over_ranks(value, device):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def bind_to_gpu_numa_node(device_index):
+    """Restrict this process to the CPUs NVML reports as local to the GPU, so that host memory pinned afterwards
+    (first touch by this thread) lies on the GPU's NUMA node.  Returns the number of CPUs bound to, or 0 when NVML,
+    the affinity query or an overlap with the CPUs this process may use is missing (nothing is changed then)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+    except Exception:
+        return 0
+    local = {64 * i + bit for i, word in enumerate(words) for bit in range(64) if (int(word) >> bit) & 1}
+    usable = local & os.sched_getaffinity(0)
+    if not usable:
+        return 0
+    os.sched_setaffinity(0, usable)
+    return len(usable)

@@ -212,6 +212,18 @@ size_t issm_b200_dwconv_workspace_bytes(const issm_conv_params* p);
 int issm_b200_dwconv7_silu_fwd(const issm_conv_params* p, void* cuda_stream);
 int issm_b200_dwconv7_silu_bwd(const issm_conv_params* p, void* cuda_stream);
 
+/* ---- one sequence cut into slices (several GPUs, or extra batch entries on one GPU) ----------------------- */
+
+/* Sums of the transformed step size over segments of `rows_per_part` points:
+ *   part[seg, b, h, n] = sum_l clamp(softplus?(dt[b, l, h, n] + dt_bias[h, n]), dt_min, dt_max),
+ * part is (ceil(seqlen / rows_per_part), batch, nheads, dstate) float, contiguous; dt has element strides dt_sb, dt_sl,
+ * dt_sh and state stride 1; dt_bias is (nheads, dstate) float or null.  exp(A * sum over a slice) is the factor the
+ * slice applies to the state entering it - what dA_cumsum[..., -1] of a chunk is to the reference's state passing
+ * (issm_triton/issm_state_passing.py:92-107). */
+int issm_b200_dt_sum(const void* dt, int32_t dt_dtype, int32_t batch, int32_t seqlen, int32_t nheads, int32_t dstate,
+                     int64_t dt_sb, int64_t dt_sl, int64_t dt_sh, const float* dt_bias, int32_t dt_softplus, float dt_min,
+                     float dt_max, int32_t rows_per_part, float* part, void* cuda_stream);
+
 /* Number of kernel launches the library has enqueued since load (monotonic, process-wide);
  * used by the benchmark to report how many of its own kernels ran inside a timed region. */
 uint64_t issm_b200_launch_count(void);
