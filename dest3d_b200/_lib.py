@@ -60,6 +60,16 @@ class IssmConvParams(C.Structure):
     )
 
 
+class IssmGlueParams(C.Structure):
+    """Mirror of `issm_glue_params`."""
+    _fields_ = (
+        [(n, i32) for n in ("batch", "seqlen", "nstates", "nfeat", "nheads", "ngroups", "has_back", "io_dtype")]
+        + [("dist", vp), ("dist_sb", i64), ("dist_sl", i64), ("dist_sk", i64), ("weight", vp), ("tok", vp), ("mask", vp),
+           ("dt", vp), ("bc", vp), ("ddt", vp), ("dbc", vp), ("ddist", vp), ("dweight", vp), ("dtok", vp),
+           ("workspace", vp), ("workspace_bytes", C.c_size_t)]
+    )
+
+
 class IssmError(RuntimeError):
     def __init__(self, code, what):
         self.code = code
@@ -105,6 +115,14 @@ def lib():
         getattr(L, name).argtypes = [C.POINTER(IssmConvParams), vp]
     L.issm_b200_gather_rows.restype = C.c_int
     L.issm_b200_gather_rows.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, vp]
+    L.issm_b200_sizeof_glue_params.restype = C.c_size_t
+    L.issm_b200_glue_workspace_bytes.restype = C.c_size_t
+    L.issm_b200_glue_workspace_bytes.argtypes = [C.POINTER(IssmGlueParams)]
+    for name in ("issm_b200_glue_fwd", "issm_b200_glue_bwd"):
+        getattr(L, name).restype = C.c_int
+        getattr(L, name).argtypes = [C.POINTER(IssmGlueParams), vp]
+    if L.issm_b200_sizeof_glue_params() != C.sizeof(IssmGlueParams):
+        raise RuntimeError("libissm_b200.so and dest3d_b200/_lib.py disagree on issm_glue_params; rebuild")
     L.issm_b200_dt_sum.restype = C.c_int
     L.issm_b200_dt_sum.argtypes = [vp, i32, i32, i32, i32, i32, i64, i64, i64, vp, i32, f32, f32, i32, vp, vp]
     L.issm_b200_launch_count.restype = C.c_uint64

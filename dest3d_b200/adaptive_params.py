@@ -1,0 +1,95 @@
+"""dt, B and C of the scan from the query-to-point distance features, as `MultiHeadISSMScan.forward` builds them
+(models/dest_module.py:541-559), in one fused pass over `dist` instead of two Linear layers, two transposes and four
+elementwise passes:
+
+    bc = bc_proj(dist);  B = b_base^T + b_bias[..., None];  C = c_base^T + c_bias[..., None]   (and the *_back pair)
+    dt = softplus(dt_proj(dist)^T + dt_bias_tok[..., None] + dt_bias[None, None, :, None]);  dt = dt * mask[:, :, None]
+
+`adaptive_dt_bc` returns them in the layouts the scan takes: dt (b, L, H, K), B / C (b, L, G, K) (views of one buffer).
+Requires the built CUDA library; there is no fallback."""
+import ctypes as ct
+
+import torch
+
+from . import _lib
+
+
+def _params(dist, w, tok, mask, H, G, back):
+    p = _lib.IssmGlueParams()
+    p.batch, p.seqlen, p.nstates, p.nfeat = dist.shape
+    p.nheads, p.ngroups, p.has_back = H, G, int(back)
+    p.io_dtype = _lib.dtype_code(dist.dtype)
+    p.dist, p.dist_sb, p.dist_sl, p.dist_sk = dist.data_ptr(), dist.stride(0), dist.stride(1), dist.stride(2)
+    p.weight, p.tok, p.mask = w.data_ptr(), tok.data_ptr(), _lib.ptr(mask)
+    return p
+
+
+class AdaptiveDtBcFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dist, w_dt, w_bc, tok, mask, H, G, back):
+        if not dist.is_cuda:
+            raise RuntimeError("dest3d_b200.adaptive_params runs on CUDA tensors only")
+        if dist.stride(3) != 1:
+            dist = dist.contiguous()
+        b, L, K, M = dist.shape
+        w = torch.cat([w_dt.detach().float(), w_bc.detach().float()], dim=0).contiguous()
+        tokf = tok.detach().float().contiguous()
+        maskf = None if mask is None else mask.float().contiguous()
+        nb = (4 if back else 2) * G
+        dt = torch.empty((b, L, H, K), dtype=dist.dtype, device=dist.device)
+        bc = torch.empty((b, L, nb, K), dtype=dist.dtype, device=dist.device)
+        p = _params(dist, w, tokf, maskf, H, G, back)
+        p.dt, p.bc = dt.data_ptr(), bc.data_ptr()
+        with torch.cuda.device(dist.device):
+            rc = _lib.lib().issm_b200_glue_fwd(ct.byref(p), _lib.stream_ptr(dist.device))
+        if rc:
+            raise _lib.IssmError(rc, "issm_b200_glue_fwd")
+        ctx.save_for_backward(dist, w, tokf, maskf)
+        ctx.meta = (H, G, back, w_dt.dtype, w_bc.dtype, tok.dtype)
+        return dt, bc
+
+    @staticmethod
+    def backward(ctx, ddt, dbc):
+        dist, w, tokf, maskf = ctx.saved_tensors
+        H, G, back, wdt_t, wbc_t, tok_t = ctx.meta
+        b, L, K, M = dist.shape
+        RW = H + 2 * G
+        ddist = torch.empty((b, L, K, M), dtype=dist.dtype, device=dist.device)
+        dw = torch.empty((RW, M), dtype=torch.float32, device=dist.device)
+        dtok = torch.empty(tokf.shape, dtype=torch.float32, device=dist.device)
+        p = _params(dist, w, tokf, maskf, H, G, back)
+        keep = []
+        for name, g in (("ddt", ddt), ("dbc", dbc)):
+            if g is not None:
+                g = g.to(dist.dtype).contiguous()
+                keep.append(g)
+                setattr(p, name, g.data_ptr())
+        p.ddist, p.dweight, p.dtok = ddist.data_ptr(), dw.data_ptr(), dtok.data_ptr()
+        need = _lib.lib().issm_b200_glue_workspace_bytes(ct.byref(p))
+        ws = torch.empty(need, dtype=torch.uint8, device=dist.device)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), need
+        with torch.cuda.device(dist.device):
+            rc = _lib.lib().issm_b200_glue_bwd(ct.byref(p), _lib.stream_ptr(dist.device))
+        if rc:
+            raise _lib.IssmError(rc, "issm_b200_glue_bwd")
+        return ddist, dw[:H].to(wdt_t), dw[H:].to(wbc_t), dtok.to(tok_t), None, None, None, None
+
+
+def adaptive_dt_bc(dist, dt_proj_weight, bc_proj_weight, dt_bias_tok, dt_bias, b_bias, c_bias, b_bias_back=None,
+                   c_bias_back=None, mask=None):
+    """dist (b, L, K, M); dt_proj_weight (H, M); bc_proj_weight (2 G, M); dt_bias_tok (b, L, H) and the parameter dt_bias
+    (H,); b_bias / c_bias (b, L, G) (and the second direction's).  `mask` (b, L, K): a float mask multiplies dt, a bool
+    mask zeroes dt where it is True (models/dest_module.py:554-558).  Returns (dt, B, C) or (dt, B, C, B_back, C_back)."""
+    H, G = dt_proj_weight.shape[0], bc_proj_weight.shape[0] // 2
+    back = b_bias_back is not None
+    terms = [dt_bias_tok.float() + dt_bias.float(), b_bias.float(), c_bias.float()]
+    if back:
+        terms += [b_bias_back.float(), c_bias_back.float()]
+    tok = torch.cat(terms, dim=-1)
+    if mask is not None and mask.dtype == torch.bool:
+        mask = (~mask).float()
+    dt, bc = AdaptiveDtBcFn.apply(dist, dt_proj_weight, bc_proj_weight, tok, mask, H, G, back)
+    parts = [dt, bc[:, :, 0:G], bc[:, :, G:2 * G]]
+    if back:
+        parts += [bc[:, :, 2 * G:3 * G], bc[:, :, 3 * G:4 * G]]
+    return tuple(parts)

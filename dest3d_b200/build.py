@@ -14,7 +14,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libissm_b200.so")
 TORCH_LIB = os.path.join(PKG, "libissm_b200_torch.so")
 TORCH_SRC = os.path.join(CSRC, "issm_torch.cpp")
-SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "issm_tensor_bwd.cu", "issm_pointops.cu", "issm_seqpar.cu"]
+SOURCES = ["issm_abi.cu", "issm_simt.cu", "issm_norm.cu", "issm_tensor.cu", "issm_tensor_bwd.cu", "issm_pointops.cu", "issm_seqpar.cu", "issm_glue.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 

@@ -1,5 +1,5 @@
-"""Timing of the serialization gather and PointLiteConv kernels against their torch formulation
-(models/dest_module.py:378-423) with CUDA events on the current stream:
+"""Timing of the serialization gather, PointLiteConv and dt / B / C generation kernels against their torch
+formulation (models/dest_module.py:378-423, 541-559) with CUDA events on the current stream:
 
     python -m dest3d_b200.pointops_bench [--batch 64] [--points 16384] [--channels 290] [--reps 10] [--no-torch]
 
@@ -25,6 +25,46 @@ def _ms(fn, reps):
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) / reps
+
+
+def glue(args):
+    """dt / B / C (both directions) from dist (16 x 4096 points x 256 states x 16 features): forward, and backward to dist,
+    the two projection weights and the per-token terms."""
+    from .adaptive_params import adaptive_dt_bc
+    b, L, K, M, H = min(args.batch, 16), 4096, 256, 16, 8
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    res = {"batch": b, "points": L, "states": K, "features": M, "heads": H}
+    for dt_, name in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        rn = lambda *s: torch.randn(*s, device="cuda", generator=gen).to(dt_)
+        dist = rn(b, L, K, M).requires_grad_(True)
+        w_dt, w_bc = (rn(H, M).float() * 0.3).requires_grad_(True), (rn(2, M).float() * 0.3).requires_grad_(True)
+        tok = [rn(b, L, H).requires_grad_(True)] + [rn(b, L, 1).requires_grad_(True) for _ in range(4)]
+        bias = (rn(H).float() - 2.0).requires_grad_(True)
+        mask = (torch.rand(b, L, K, device="cuda", generator=gen) > 0.3).float()
+        leaves = [dist, w_dt, w_bc, bias] + tok
+
+        def mine():
+            return adaptive_dt_bc(dist, w_dt, w_bc, tok[0], bias, tok[1], tok[2], tok[3], tok[4], mask)
+
+        def ref():
+            bc = F.linear(dist, w_bc.to(dt_))
+            bb, cb = bc[..., :1].transpose(-1, -2), bc[..., 1:].transpose(-1, -2)
+            d = F.softplus(F.linear(dist, w_dt.to(dt_)).transpose(-1, -2) + tok[0].unsqueeze(-1) + bias.to(dt_).reshape(1, 1, -1, 1))
+            return (d * mask.unsqueeze(2).to(dt_), bb + tok[1].unsqueeze(-1), cb + tok[2].unsqueeze(-1), bb + tok[3].unsqueeze(-1),
+                    cb + tok[4].unsqueeze(-1))
+        douts = [torch.randn_like(o) for o in mine()]
+        es = dist.element_size()
+        n = b * L * K
+        fwd = _ms(mine, args.reps)
+        bwd = _ms(lambda: torch.autograd.grad(mine(), leaves, douts), args.reps) - fwd
+        r = {"fwd_ms": fwd, "fwd_gbs": n * (M + H + 4) * es / fwd / 1e6,                 # dist in; dt and four B / C rows out
+             "bwd_ms": bwd, "bwd_gbs": n * (2 * M + H + 4) * es / bwd / 1e6}             # dist, ddt, dbc in; ddist out
+        if not args.no_torch:
+            tf = _ms(ref, args.reps)
+            r["torch_fwd_ms"] = tf
+            r["torch_bwd_ms"] = _ms(lambda: torch.autograd.grad(ref(), leaves, douts), args.reps) - tf
+        res[name] = r
+    return res
 
 
 def main():
@@ -62,6 +102,7 @@ def main():
             r["torch_conv_bwd_ms"] = _ms(lambda: torch.autograd.grad(ref(), (x, conv.weight, conv.bias), dy), args.reps) - tf
             r["torch_gather_ms"] = _ms(lambda: pts.gather(1, order.unsqueeze(-1).expand(-1, -1, C)), args.reps)
         out[name] = r
+    out["glue"] = glue(args)
     print(json.dumps(out))
 
 

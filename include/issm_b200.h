@@ -212,6 +212,39 @@ size_t issm_b200_dwconv_workspace_bytes(const issm_conv_params* p);
 int issm_b200_dwconv7_silu_fwd(const issm_conv_params* p, void* cuda_stream);
 int issm_b200_dwconv7_silu_bwd(const issm_conv_params* p, void* cuda_stream);
 
+/* ---- the parameter generation in front of the scan (models/dest_module.py:541-559) ------------------------- */
+
+/* dt, B, C (and the second direction's B, C) from the query-to-point distance features in ONE pass over them:
+ *   pre[r]  = dist[b, l, k, :] . weight[r, :]            r = 0 .. nheads + 2 ngroups - 1   (dt_proj rows, then bc_proj rows)
+ *   dt[b, l, h, k]  = softplus(pre[h] + tok[b, l, h]) * mask[b, l, k]                       (softplus threshold 20)
+ *   bc[b, l, i, k]  = pre[nheads + i] + tok[b, l, nheads + i]                i < 2 ngroups: B rows then C rows
+ *   bc[b, l, 2 ngroups + i, k] = pre[nheads + i] + tok[b, l, nheads + 2 ngroups + i]        only when has_back
+ * tok holds the per-token terms the caller adds (key_proj's dt_bias split plus the dt_bias parameter; b_bias, c_bias;
+ * their second-direction counterparts), float, (batch, seqlen, nheads + 2 ngroups [+ 2 ngroups]).
+ * Backward: ddt / dbc (either may be null) -> ddist (batch, seqlen, nstates, nfeat), dweight (shape of weight; the
+ * second direction's B / C rows add to the rows they share) and dtok (shape of tok); needs a workspace of
+ * issm_b200_glue_workspace_bytes() for the per-block partial weight gradients, summed in a fixed order. */
+typedef struct issm_glue_params {
+  int32_t batch, seqlen, nstates, nfeat;  /* nfeat = 4, 8 or 16 */
+  int32_t nheads, ngroups, has_back;
+  int32_t io_dtype;                       /* dist, dt, bc, ddt, dbc, ddist, grow */
+  const void* dist; int64_t dist_sb, dist_sl, dist_sk;   /* element strides; feature stride 1; 16-byte aligned rows */
+  const float* weight;                    /* (nheads + 2 ngroups, nfeat) */
+  const float* tok;
+  const float* mask;                      /* (batch, seqlen, nstates) multiplier or null */
+  void* dt;                               /* (batch, seqlen, nheads, nstates) contiguous */
+  void* bc;                               /* (batch, seqlen, 2 ngroups [+ 2 ngroups], nstates) contiguous */
+  /* backward */
+  const void* ddt; const void* dbc;
+  void* ddist; float* dweight; float* dtok;
+  void* workspace; size_t workspace_bytes;
+} issm_glue_params;
+
+size_t issm_b200_sizeof_glue_params(void);
+size_t issm_b200_glue_workspace_bytes(const issm_glue_params* p);
+int issm_b200_glue_fwd(const issm_glue_params* p, void* cuda_stream);
+int issm_b200_glue_bwd(const issm_glue_params* p, void* cuda_stream);
+
 /* ---- one sequence cut into slices (several GPUs, or extra batch entries on one GPU) ----------------------- */
 
 /* Sums of the transformed step size over segments of `rows_per_part` points:

@@ -148,3 +148,32 @@ def test_point_ops_validation(built_lib):
         reorder_points(torch.randn(1, 10, 8), torch.zeros(1, 10, dtype=torch.int64))
     with pytest.raises(ValueError):
         PointLiteConv(8, 16)
+
+
+def test_parameter_generation_and_slice_entry_points_validate(built_lib):
+    """issm_b200_glue_* and issm_b200_dt_sum: struct layout and the codes returned before any launch."""
+    import torch
+    from dest3d_b200 import _lib
+    from dest3d_b200.adaptive_params import adaptive_dt_bc
+    L = _lib.lib()
+    assert L.issm_b200_sizeof_glue_params() == C.sizeof(_lib.IssmGlueParams)
+    p = _lib.IssmGlueParams()
+    assert L.issm_b200_glue_fwd(None, None) == 1
+    p.batch, p.seqlen, p.nstates, p.nfeat, p.nheads, p.ngroups = 2, 10, 256, 5, 8, 1
+    assert L.issm_b200_glue_fwd(C.byref(p), None) == 2                        # 5 features: not 4, 8 or 16
+    p.nfeat, p.nheads = 16, 15
+    assert L.issm_b200_glue_fwd(C.byref(p), None) == 2                        # more rows than a thread holds
+    p.nheads, p.io_dtype = 8, _lib.BF16
+    assert L.issm_b200_glue_fwd(C.byref(p), None) == 1                        # null pointers
+    p.dist = p.weight = p.tok = p.dt = p.bc = p.ddist = p.dweight = p.dtok = 4096
+    p.dist_sb, p.dist_sl, p.dist_sk = 10 * 256 * 16, 256 * 16, 16
+    assert L.issm_b200_glue_bwd(C.byref(p), None) == 4                        # no workspace
+    p.dist = 4098
+    assert L.issm_b200_glue_fwd(C.byref(p), None) == 5                        # feature rows must be 16-byte aligned
+    assert L.issm_b200_glue_workspace_bytes(C.byref(p)) % 256 == 0
+    assert L.issm_b200_dt_sum(None, 0, 1, 1, 1, 1, 1, 1, 1, None, 0, 0.0, 1.0, 256, None, None) == 1
+    assert L.issm_b200_dt_sum(4096, 0, 1, 0, 1, 1, 1, 1, 1, None, 0, 0.0, 1.0, 256, 4096, None) == 2
+    assert L.issm_b200_dt_sum(4096, 7, 1, 8, 1, 1, 1, 1, 1, None, 0, 0.0, 1.0, 256, 4096, None) == 3
+    with pytest.raises(RuntimeError):
+        adaptive_dt_bc(torch.randn(1, 4, 8, 4), torch.randn(2, 4), torch.randn(2, 4), torch.randn(1, 4, 2), torch.randn(2),
+                       torch.randn(1, 4, 1), torch.randn(1, 4, 1))
