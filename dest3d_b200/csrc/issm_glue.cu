@@ -77,10 +77,23 @@ __device__ __forceinline__ void store_feats(T* p, const float (&d)[M]) {
 
 __device__ __forceinline__ float glue_sigmoid(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
 
-// one block per point (b, l); threads over the states k
+// softplus with threshold 20 in the log2 domain (hardware ex2 / lg2); below -4 the series of log1p in u = e^v, where
+// lg2(1 + u) would lose the low bits of u
+__device__ __forceinline__ float glue_softplus(float v) {
+  float u, s;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(u) : "f"(v * 1.4426950408889634f));
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(1.f + u));
+  const float series = u * fmaf(u, fmaf(u, 0.33333333f, -0.5f), 1.f);
+  const float r = v < -4.f ? series : s * 0.6931471805599453f;
+  return v <= 20.f ? r : v;
+}
+
+// one block per point (b, l); a thread owns two adjacent states and computes them with packed fp32 instructions,
+// reading four weights per shared-memory access
 template <typename T, int M>
 __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
-  __shared__ float sw[GLUE_MAX_ROWS * M], stok[GLUE_MAX_ROWS + 4 * 2];
+  __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
+  __shared__ float stok[GLUE_MAX_ROWS + 8];
   const int l = blockIdx.x, b = blockIdx.y;
   for (int i = threadIdx.x; i < a.RW * M; i += blockDim.x) sw[i] = a.w[i];
   for (int i = threadIdx.x; i < a.RO; i += blockDim.x) stok[i] = a.tok[((int64_t)b * a.L + l) * a.RO + i];
@@ -89,20 +102,44 @@ __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
   const int64_t row = (int64_t)b * a.L + l;
   T* dt = (T*)a.dt + row * a.H * a.K;
   T* bc = (T*)a.bc + row * (a.RO - a.H) * a.K;
-  for (int k = threadIdx.x; k < a.K; k += blockDim.x) {
-    float d[M];
-    load_feats<T, M>(drow + (int64_t)k * a.d_sk, d);
-    const float mk = a.mask ? a.mask[row * a.K + k] : 1.f;
-    for (int r = 0; r < a.RW; ++r) {
-      float pre = 0.f;
+  const bool pair_store = !(a.K & 1);                      // rows of an even number of states keep pairs aligned
+  for (int k = 2 * threadIdx.x; k < a.K; k += 2 * blockDim.x) {
+    const bool two = k + 1 < a.K;
+    float d0[M], d1[M];
+    load_feats<T, M>(drow + (int64_t)k * a.d_sk, d0);
+    load_feats<T, M>(drow + (int64_t)(two ? k + 1 : k) * a.d_sk, d1);
+    float2 dp[M];
 #pragma unroll
-      for (int j = 0; j < M; ++j) pre = fmaf(d[j], sw[r * M + j], pre);
-      if (r < a.H) {
-        const float v = pre + stok[r];
-        stf(dt + (int64_t)r * a.K + k, (v <= 20.f ? log1pf(__expf(v)) : v) * mk);
+    for (int j = 0; j < M; ++j) dp[j] = make_float2(d0[j], d1[j]);
+    float2 mk = make_float2(1.f, 1.f);
+    if (a.mask) mk = make_float2(a.mask[row * a.K + k], a.mask[row * a.K + (two ? k + 1 : k)]);
+    auto put = [&](T* p, float2 v) {
+      if (pair_store) {
+        if constexpr (sizeof(T) == 2) *(__nv_bfloat162*)p = __float22bfloat162_rn(v);
+        else *(float2*)p = v;
       } else {
-        stf(bc + (int64_t)(r - a.H) * a.K + k, pre + stok[r]);
-        if (a.back) stf(bc + (int64_t)(r - a.H + 2 * a.G) * a.K + k, pre + stok[r + 2 * a.G]);
+        stf(p, v.x);
+        if (two) stf(p + 1, v.y);
+      }
+    };
+    for (int r = 0; r < a.RW; ++r) {
+      float2 pre = make_float2(stok[r], stok[r]);
+#pragma unroll
+      for (int c = 0; c < M / 4; ++c) {
+        const float4 w4 = *(const float4*)&sw[r * M + c * 4];
+        pre = __ffma2_rn(dp[c * 4], make_float2(w4.x, w4.x), pre);
+        pre = __ffma2_rn(dp[c * 4 + 1], make_float2(w4.y, w4.y), pre);
+        pre = __ffma2_rn(dp[c * 4 + 2], make_float2(w4.z, w4.z), pre);
+        pre = __ffma2_rn(dp[c * 4 + 3], make_float2(w4.w, w4.w), pre);
+      }
+      if (r < a.H) {
+        put(dt + (int64_t)r * a.K + k, __fmul2_rn(make_float2(glue_softplus(pre.x), glue_softplus(pre.y)), mk));
+      } else {
+        put(bc + (int64_t)(r - a.H) * a.K + k, pre);
+        if (a.back) {
+          const float dlt = stok[r + 2 * a.G] - stok[r];
+          put(bc + (int64_t)(r - a.H + 2 * a.G) * a.K + k, __fadd2_rn(pre, make_float2(dlt, dlt)));
+        }
       }
     }
   }
@@ -111,12 +148,42 @@ __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
 constexpr int GLUE_KT = 256;                               // states per shared-memory tile of the weight-gradient product
 constexpr int GLUE_BWD_BLOCKS = 148 * 8;
 
-// A block walks points (b, l) with a grid stride.  Per point: (1) threads over the states form g, ddist and the token
-// sums, and park g and the features in shared memory; (2) thread (r, j) adds sum_k g[r, k] dist[k, j] to its
-// accumulator of the weight gradient.  The accumulators go out once per block and are summed in a fixed order.
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gsrc, int bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  if (bytes == 16) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+  else if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gsrc) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One stage of the backward's input pipeline: everything a (point, tile of 256 states) needs, as raw bytes.  The
+// number of gradient rows is the call's (RO), so the layout is computed at run time.
 template <typename T, int M>
-__global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints) {
-  __shared__ float sw[GLUE_MAX_ROWS * M], stok[GLUE_MAX_ROWS + 8], sred[4][GLUE_MAX_ROWS + 8];
+struct GlueStage {
+  unsigned char* base;
+  int ro;
+  __host__ __device__ static size_t bytes(int ro) {
+    return ((size_t)GLUE_KT * M * sizeof(T) + (size_t)ro * GLUE_KT * sizeof(T) + GLUE_KT * 4 + (GLUE_MAX_ROWS + 8) * 4 + 15) / 16 * 16;
+  }
+  __device__ T* dist(int kk) const { return (T*)base + (size_t)kk * M; }                       // [GLUE_KT][M]
+  __device__ T* grad(int r) const { return (T*)base + (size_t)GLUE_KT * M + (size_t)r * GLUE_KT; }   // ddt rows, then the B / C rows
+  __device__ float* mask() const { return (float*)(base + (size_t)GLUE_KT * (M + ro) * sizeof(T)); }
+  __device__ float* tok() const { return mask() + GLUE_KT; }
+};
+
+// A block walks (point, tile of 256 states) items with a grid stride over the points, two items in flight: the
+// inputs of the next item are copied into shared memory (cp.async) while the current one is computed.  Per item:
+// (1) a thread takes two adjacent states: g, ddist, token sums; g and the features are parked in shared memory;
+// (2) thread (row r, four features, a range of the tile's states) adds sum_k g[r, k] dist[k, j] to its accumulators of
+// the weight gradient.  The accumulators go out once per block and are summed in a fixed order.
+template <typename T, int M>
+__global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int vec_ok) {
+  extern __shared__ __align__(16) unsigned char glue_dyn[];
+  const size_t stage_bytes = GlueStage<T, M>::bytes(a.RO);
+  auto stage_of = [&](int it) { return GlueStage<T, M>{glue_dyn + (it & 1) * stage_bytes, a.RO}; };
+  __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
+  __shared__ float sred[4][GLUE_MAX_ROWS + 8];
   __shared__ float sg[GLUE_MAX_ROWS][GLUE_KT + 1];
   __shared__ __align__(16) float sd[GLUE_KT][M + 4];         // rows 16 bytes apart from a power of two: 128-bit accesses without conflicts
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -128,92 +195,161 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints) {
   const int wr = tile / JQ, wj = (tile % JQ) * 4;
   const int kspan = (GLUE_KT + NKG - 1) / NKG;
   float wacc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int pt = blockIdx.x; pt < npoints; pt += gridDim.x) {
+  const int ntile = (a.K + GLUE_KT - 1) / GLUE_KT;
+  const int my_points = blockIdx.x < npoints ? (npoints - blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int nitems = my_points * ntile;
+
+  // copies of item `it` into stage `st`.  vec_ok: every row of states starts on a 16-byte boundary, so the gradient rows
+  // and the mask go in 16-byte pieces; otherwise element by element through registers.
+  auto issue = [&](int it, const GlueStage<T, M>& st) {
+    const int pt = blockIdx.x + (it / ntile) * gridDim.x, k0 = (it % ntile) * GLUE_KT;
     const int b = pt / a.L, l = pt - b * a.L;
-    __syncthreads();                                       // the previous point's tiles and token terms are consumed
-    for (int i = threadIdx.x; i < a.RO; i += blockDim.x) stok[i] = a.tok[(int64_t)pt * a.RO + i];
-    __syncthreads();
-    const T* drow = (const T*)a.dist + b * a.d_sb + l * a.d_sl;
+    const int nk = min(GLUE_KT, a.K - k0);
+    const T* drow = (const T*)a.dist + b * a.d_sb + l * a.d_sl + (int64_t)k0 * a.d_sk;
+    constexpr int RB = M * (int)sizeof(T), CS = RB >= 16 ? 16 : RB, CH = RB / CS;     // bytes per state, per piece, pieces per state
+    for (int c = threadIdx.x; c < nk * CH; c += blockDim.x) {
+      const int kk = c / CH, part = c % CH;
+      cp_async((char*)st.dist(kk) + part * CS, (const char*)(drow + (int64_t)kk * a.d_sk) + part * CS, CS);
+    }
+    const int nrow = a.RO;
+    const T* ddt = a.ddt ? (const T*)a.ddt + (int64_t)pt * a.H * a.K + k0 : nullptr;
+    const T* dbc = a.dbc ? (const T*)a.dbc + (int64_t)pt * (a.RO - a.H) * a.K + k0 : nullptr;
+    constexpr int EPC = 16 / (int)sizeof(T);               // elements per 16-byte piece
+    if (vec_ok) {
+      const int pieces = nk / EPC;                         // K is a multiple of EPC here
+      for (int c = threadIdx.x; c < nrow * pieces; c += blockDim.x) {
+        const int ro = c / pieces, q = c % pieces;
+        const T* src = ro < a.H ? (ddt ? ddt + (int64_t)ro * a.K : nullptr) : (dbc ? dbc + (int64_t)(ro - a.H) * a.K : nullptr);
+        if (src) cp_async(st.grad(ro) + q * EPC, src + q * EPC, 16);
+      }
+      if (a.mask)
+        for (int c = threadIdx.x; c < nk / 4; c += blockDim.x) cp_async(st.mask() + c * 4, a.mask + (int64_t)pt * a.K + k0 + c * 4, 16);
+    } else {
+      for (int c = threadIdx.x; c < nrow * nk; c += blockDim.x) {
+        const int ro = c / nk, kk = c % nk;
+        const T* src = ro < a.H ? (ddt ? ddt + (int64_t)ro * a.K : nullptr) : (dbc ? dbc + (int64_t)(ro - a.H) * a.K : nullptr);
+        if (src) st.grad(ro)[kk] = src[kk];
+      }
+      if (a.mask)
+        for (int c = threadIdx.x; c < nk; c += blockDim.x) st.mask()[c] = a.mask[(int64_t)pt * a.K + k0 + c];
+    }
+    for (int i = threadIdx.x; i < a.RO; i += blockDim.x) cp_async(st.tok() + i, a.tok + (int64_t)pt * a.RO + i, 4);
+    cp_async_commit();
+  };
+
+  float tsum[GLUE_MAX_ROWS + 8];                            // per output row: sum over this thread's states of the point
+#pragma unroll
+  for (int r = 0; r < GLUE_MAX_ROWS + 8; ++r) tsum[r] = 0.f;
+  if (nitems > 0) issue(0, stage_of(0));
+  for (int it = 0; it < nitems; ++it) {
+    const GlueStage<T, M> st = stage_of(it);
+    if (it + 1 < nitems) { issue(it + 1, stage_of(it + 1)); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();                                       // this item's inputs are in shared memory
+    const int pt = blockIdx.x + (it / ntile) * gridDim.x, k0 = (it % ntile) * GLUE_KT;
     const int64_t row = pt;
-    const T* ddt = a.ddt ? (const T*)a.ddt + row * a.H * a.K : nullptr;
-    const T* dbc = a.dbc ? (const T*)a.dbc + row * (a.RO - a.H) * a.K : nullptr;
     T* ddist = (T*)a.ddist + row * a.K * M;
-    float tsum[GLUE_MAX_ROWS + 8];                          // per output row: sum over this thread's states
+    {                                                      // two adjacent states per thread: 128 threads cover the tile
+      const int kk = 2 * threadIdx.x, k = k0 + kk;
+      const bool in0 = k < a.K, in1 = k + 1 < a.K;
+      float d0[M], d1[M];
 #pragma unroll
-    for (int r = 0; r < GLUE_MAX_ROWS + 8; ++r) tsum[r] = 0.f;
-    for (int k0 = 0; k0 < a.K; k0 += GLUE_KT) {
-      if (k0) __syncthreads();
-      for (int kk = threadIdx.x; kk < GLUE_KT; kk += blockDim.x) {
-        const int k = k0 + kk;
-        const bool in = k < a.K;
-        float d[M], dd[M];
-        if (in) load_feats<T, M>(drow + (int64_t)k * a.d_sk, d);
-        else {
+      for (int j = 0; j < M; ++j) { d0[j] = 0.f; d1[j] = 0.f; }
+      if (in0) load_feats<T, M>(st.dist(kk), d0);
+      if (in1) load_feats<T, M>(st.dist(kk + 1), d1);
+      float2 dp[M], dd[M];
 #pragma unroll
-          for (int j = 0; j < M; ++j) d[j] = 0.f;
-        }
+      for (int j = 0; j < M; ++j) { dp[j] = make_float2(d0[j], d1[j]); dd[j] = make_float2(0.f, 0.f); }
 #pragma unroll
-        for (int j = 0; j < M; ++j) dd[j] = 0.f;
+      for (int c = 0; c < M / 4; ++c) {
+        *(float4*)&sd[kk][c * 4] = make_float4(d0[c * 4], d0[c * 4 + 1], d0[c * 4 + 2], d0[c * 4 + 3]);
+        *(float4*)&sd[kk + 1][c * 4] = make_float4(d1[c * 4], d1[c * 4 + 1], d1[c * 4 + 2], d1[c * 4 + 3]);
+      }
+      const float2 inm = make_float2(in0 ? 1.f : 0.f, in1 ? 1.f : 0.f);
+      float2 mk = inm;
+      if (a.mask) mk = make_float2(in0 ? st.mask()[kk] : 0.f, in1 ? st.mask()[kk + 1] : 0.f);
+      auto get = [&](int ro) {                             // the pair (k, k + 1) of one gradient row; zero outside the row
+        float2 v;
+        if constexpr (sizeof(T) == 2) v = __bfloat1622float2(*(const __nv_bfloat162*)(st.grad(ro) + kk));
+        else v = *(const float2*)(st.grad(ro) + kk);
+        return make_float2(in0 ? v.x : 0.f, in1 ? v.y : 0.f);
+      };
 #pragma unroll
-        for (int c = 0; c < M / 4; ++c) *(float4*)&sd[kk][c * 4] = make_float4(d[c * 4], d[c * 4 + 1], d[c * 4 + 2], d[c * 4 + 3]);
-        const float mk = (in && a.mask) ? a.mask[row * a.K + k] : 1.f;
+      for (int r = 0; r < GLUE_MAX_ROWS; ++r) {
+        if (r < a.RW) {
+          float2 g = make_float2(0.f, 0.f);
+          if (r < a.H) {
+            if (a.ddt) {
+              float2 pre = make_float2(st.tok()[r], st.tok()[r]);
 #pragma unroll
-        for (int r = 0; r < GLUE_MAX_ROWS; ++r) {
-          if (r < a.RW) {
-            float g = 0.f;
-            if (in) {
-              if (r < a.H) {
-                if (ddt) {
-                  float pre = stok[r];
-#pragma unroll
-                  for (int j = 0; j < M; ++j) pre = fmaf(d[j], sw[r * M + j], pre);
-                  g = ldf(ddt + (int64_t)r * a.K + k) * mk * (pre <= 20.f ? glue_sigmoid(pre) : 1.f);
-                }
-                tsum[r] += g;
-              } else if (dbc) {
-                g = ldf(dbc + (int64_t)(r - a.H) * a.K + k);
-                if (a.back) g += ldf(dbc + (int64_t)(r - a.H + 2 * a.G) * a.K + k);   // both directions share the weight row
+              for (int c = 0; c < M / 4; ++c) {
+                const float4 w4 = *(const float4*)&sw[r * M + c * 4];
+                pre = __ffma2_rn(dp[c * 4], make_float2(w4.x, w4.x), pre);
+                pre = __ffma2_rn(dp[c * 4 + 1], make_float2(w4.y, w4.y), pre);
+                pre = __ffma2_rn(dp[c * 4 + 2], make_float2(w4.z, w4.z), pre);
+                pre = __ffma2_rn(dp[c * 4 + 3], make_float2(w4.w, w4.w), pre);
               }
+              const float2 sg2 = make_float2(pre.x <= 20.f ? glue_sigmoid(pre.x) : 1.f, pre.y <= 20.f ? glue_sigmoid(pre.y) : 1.f);
+              g = __fmul2_rn(__fmul2_rn(get(r), mk), sg2);
             }
-            sg[r][kk] = g;
+            tsum[r] += g.x + g.y;
+          } else if (a.dbc) {
+            g = get(r);
+            if (a.back) g = __fadd2_rn(g, get(r + 2 * a.G));   // both directions share the weight row
+          }
+          sg[r][kk] = g.x;
+          sg[r][kk + 1] = g.y;
 #pragma unroll
-            for (int j = 0; j < M; ++j) dd[j] = fmaf(g, sw[r * M + j], dd[j]);
+          for (int c = 0; c < M / 4; ++c) {
+            const float4 w4 = *(const float4*)&sw[r * M + c * 4];
+            dd[c * 4] = __ffma2_rn(g, make_float2(w4.x, w4.x), dd[c * 4]);
+            dd[c * 4 + 1] = __ffma2_rn(g, make_float2(w4.y, w4.y), dd[c * 4 + 1]);
+            dd[c * 4 + 2] = __ffma2_rn(g, make_float2(w4.z, w4.z), dd[c * 4 + 2]);
+            dd[c * 4 + 3] = __ffma2_rn(g, make_float2(w4.w, w4.w), dd[c * 4 + 3]);
           }
         }
-        if (in) {
-          store_feats<T, M>(ddist + (int64_t)k * M, dd);
-          if (dbc) {                                       // token terms of the B / C rows (each output row has its own)
+      }
 #pragma unroll
-            for (int ro = 0; ro < GLUE_MAX_ROWS + 8; ++ro)
-              if (ro >= a.H && ro < a.RO) tsum[ro] += ldf(dbc + (int64_t)(ro - a.H) * a.K + k);
+      for (int j = 0; j < M; ++j) { d0[j] = dd[j].x; d1[j] = dd[j].y; }
+      if (in0) store_feats<T, M>(ddist + (int64_t)k * M, d0);
+      if (in1) store_feats<T, M>(ddist + (int64_t)(k + 1) * M, d1);
+      if (a.dbc) {                                         // token terms of the B / C rows (each output row has its own)
+#pragma unroll
+        for (int ro = 0; ro < GLUE_MAX_ROWS + 8; ++ro)
+          if (ro >= a.H && ro < a.RO) {
+            const float2 v = get(ro);
+            tsum[ro] += v.x + v.y;
           }
+      }
+    }
+    __syncthreads();
+    if (kg < NKG) {
+      const int k1 = min(GLUE_KT, (kg + 1) * kspan);
+#pragma unroll 4
+      for (int kk = kg * kspan; kk < k1; ++kk) {
+        const float g = sg[wr][kk];
+        const float4 f = *(const float4*)&sd[kk][wj];
+        wacc[0] = fmaf(g, f.x, wacc[0]); wacc[1] = fmaf(g, f.y, wacc[1]);
+        wacc[2] = fmaf(g, f.z, wacc[2]); wacc[3] = fmaf(g, f.w, wacc[3]);
+      }
+    }
+    if (k0 + GLUE_KT >= a.K) {
+      // last tile of the point: token terms, summed over the states by warp shuffles, then the four warps in a fixed order
+#pragma unroll
+      for (int r = 0; r < GLUE_MAX_ROWS + 8; ++r) {
+        if (r < a.RO) {
+          float v = tsum[r];
+#pragma unroll
+          for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0) sred[warp][r] = v;
         }
+        tsum[r] = 0.f;
       }
       __syncthreads();
-      if (kg < NKG) {
-        const int k1 = min(GLUE_KT, (kg + 1) * kspan);
-#pragma unroll 4
-        for (int kk = kg * kspan; kk < k1; ++kk) {
-          const float g = sg[wr][kk];
-          const float4 f = *(const float4*)&sd[kk][wj];
-          wacc[0] = fmaf(g, f.x, wacc[0]); wacc[1] = fmaf(g, f.y, wacc[1]);
-          wacc[2] = fmaf(g, f.z, wacc[2]); wacc[3] = fmaf(g, f.w, wacc[3]);
-        }
-      }
+      for (int r = threadIdx.x; r < a.RO; r += blockDim.x)
+        a.dtok[row * a.RO + r] = ((sred[0][r] + sred[1][r]) + sred[2][r]) + sred[3][r];
     }
-    // token terms: sum over the states, warp shuffles then the four warps in a fixed order
-#pragma unroll
-    for (int r = 0; r < GLUE_MAX_ROWS + 8; ++r) {
-      if (r < a.RO) {
-        float v = tsum[r];
-#pragma unroll
-        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) sred[warp][r] = v;
-      }
-    }
-    __syncthreads();
-    for (int r = threadIdx.x; r < a.RO; r += blockDim.x)
-      a.dtok[row * a.RO + r] = ((sred[0][r] + sred[1][r]) + sred[2][r]) + sred[3][r];
+    __syncthreads();                                       // sg / sd / sred and this stage may be overwritten
   }
   // the NKG ranges of a tile are summed in a fixed order through shared memory, then one partial per block goes out
   __syncthreads();
@@ -323,7 +459,17 @@ extern "C" int issm_b200_glue_bwd(const issm_glue_params* p, void* stream) {
   const GlueArgs a = glue_args(*p);
   const int blocks = glue_bwd_blocks(p), npoints = p->batch * p->seqlen;
   cudaStream_t s = (cudaStream_t)stream;
-#define GLUE_BWD(TT, MM) ISSM_LAUNCH((k_glue_bwd<TT, MM>), blocks, 128, 0, s, a, npoints)
+  const size_t es = p->io_dtype == ISSM_F32 ? 4 : 2;
+  // 16-byte copies of the gradient rows and the mask need every row of states to start on a 16-byte boundary
+  const int vec_ok = !((p->nstates * es) % 16) && !(p->nstates % 4) && !((uintptr_t)p->ddt % 16) && !((uintptr_t)p->dbc % 16) &&
+                     !((uintptr_t)p->mask % 16);
+#define GLUE_BWD(TT, MM)                                                                              \
+  do {                                                                                                \
+    const size_t dyn = 2 * GlueStage<TT, MM>::bytes(a.RO);                                            \
+    struct Tag {};                                                                                    \
+    if (int rc2 = SmemAttrOnce<Tag>::set(k_glue_bwd<TT, MM>, 2 * GlueStage<TT, MM>::bytes(GLUE_MAX_ROWS + 8))) return rc2; \
+    ISSM_LAUNCH((k_glue_bwd<TT, MM>), blocks, 128, dyn, s, a, npoints, vec_ok);                       \
+  } while (0)
   if (p->io_dtype == ISSM_F32) {
     if (p->nfeat == 16) GLUE_BWD(float, 16); else if (p->nfeat == 8) GLUE_BWD(float, 8); else GLUE_BWD(float, 4);
   } else {
