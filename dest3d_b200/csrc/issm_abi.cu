@@ -38,6 +38,24 @@ static int validate_ptrs(const issm_params* p, int pass) {
   return ISSM_OK;
 }
 
+// The stride of a dimension of size 1 is never used, and frameworks report arbitrary values there (a (b, L, 1, N) sum
+// of broadcast views comes back with group stride 1): give such strides the value a contiguous tensor would have, so
+// that they cannot fail an alignment rule or be taken for a gap between rows.
+static issm_params canonical(const issm_params& in) {
+  issm_params p = in;
+  if (p.nheads == 1) { p.x_sh = p.z_sh = p.out_sh = p.dout_sh = p.headdim; p.dt_sh = p.dstate; }
+  if (p.ngroups == 1) p.B_sg = p.C_sg = p.dstate;
+  if (p.seqlen == 1) {
+    p.x_sl = p.nheads * p.x_sh; p.z_sl = p.nheads * p.z_sh; p.out_sl = p.nheads * p.out_sh; p.dout_sl = p.nheads * p.dout_sh;
+    p.dt_sl = p.nheads * p.dt_sh; p.B_sl = p.ngroups * p.B_sg; p.C_sl = p.ngroups * p.C_sg;
+  }
+  if (p.batch == 1) {
+    p.x_sb = p.seqlen * p.x_sl; p.z_sb = p.seqlen * p.z_sl; p.out_sb = p.seqlen * p.out_sl; p.dout_sb = p.seqlen * p.dout_sl;
+    p.dt_sb = p.seqlen * p.dt_sl; p.B_sb = p.seqlen * p.B_sl; p.C_sb = p.seqlen * p.C_sl;
+  }
+  return p;
+}
+
 static int resolve(const issm_params& p, int pass) {
   if (p.path == ISSM_PATH_SIMT) return ISSM_PATH_SIMT;
   const bool ok = tensor_path_supported(p, pass);
@@ -72,25 +90,28 @@ extern "C" uint64_t issm_b200_launch_count(void) { return g_launches.load(); }
 
 extern "C" int issm_b200_resolve_path(const issm_params* p) {
   if (validate(p, 0)) return -1;
-  return resolve(*p, 0);
+  return resolve(canonical(*p), 0);
 }
 extern "C" int issm_b200_resolve_path_pass(const issm_params* p, int pass) {
   if (validate(p, pass) || (pass != 0 && pass != 1)) return -1;
-  return resolve(*p, pass);
+  return resolve(canonical(*p), pass);
 }
 
 extern "C" size_t issm_b200_workspace_bytes(const issm_params* p, int pass) {
   if (validate(p, pass) || (pass != 0 && pass != 1)) return 0;
-  const int path = resolve(*p, pass);
+  const issm_params q = canonical(*p);
+  const int path = resolve(q, pass);
   if (path < 0) return 0;
-  return path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(*p, pass) : simt_workspace_bytes(*p, pass);
+  return path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(q, pass) : simt_workspace_bytes(q, pass);
 }
 
-static int run(const issm_params* p, void* stream, int pass) {
-  int rc = validate(p, pass);
+static int run(const issm_params* in, void* stream, int pass) {
+  int rc = validate(in, pass);
   if (rc) return rc;
-  rc = validate_ptrs(p, pass);
+  rc = validate_ptrs(in, pass);
   if (rc) return rc;
+  const issm_params q = canonical(*in);
+  const issm_params* p = &q;
   const int path = resolve(*p, pass);
   if (path < 0) return ISSM_ERR_UNSUPPORTED;
   const size_t need = path == ISSM_PATH_TENSOR ? tensor_workspace_bytes(*p, pass) : simt_workspace_bytes(*p, pass);

@@ -733,20 +733,24 @@ bool tensor_path_supported(const issm_params& p, int pass) {
   if (p.io_dtype != ISSM_BF16) return false;
   // the tile-I/O warps move 4 head-dim elements (8 bytes) at a time; the backward's dx tile holds 40 columns
   if (p.headdim > 40 || (p.headdim & 3)) return false;
-  if ((p.x_sb | p.x_sl | p.x_sh | p.out_sb | p.out_sl | p.out_sh | p.dout_sb | p.dout_sl | p.dout_sh) & 3) return false;
-  if (p.has_z && ((p.z_sb | p.z_sl | p.z_sh) & 3)) return false;
+  // strides of dimensions of size 1 take no part in the rules (the entry points canonicalise them; direct callers of this
+  // function get the same treatment here)
+  const int64_t mb = p.batch > 1 ? -1 : 0, mh = p.nheads > 1 ? -1 : 0, mg = p.ngroups > 1 ? -1 : 0, ml = p.seqlen > 1 ? -1 : 0;
+  if (((p.x_sb & mb) | (p.x_sl & ml) | (p.x_sh & mh) | (p.out_sb & mb) | (p.out_sl & ml) | (p.out_sh & mh) | (p.dout_sb & mb) |
+       (p.dout_sl & ml) | (p.dout_sh & mh)) & 3) return false;
+  if (p.has_z && (((p.z_sb & mb) | (p.z_sl & ml) | (p.z_sh & mh)) & 3)) return false;
   if (((uintptr_t)p.x | (uintptr_t)p.z | (uintptr_t)p.out | (uintptr_t)p.out_x | (uintptr_t)p.dout | (uintptr_t)p.dx | (uintptr_t)p.dz) & 7) return false;
   const int slices = state_slices(p.dstate);
   if (slices == 0) return false;
   // bulk (TMA) row copies need 16-byte aligned rows of B, C and (bf16) dt
   if (p.B && (!aligned16(p.B) || !aligned16(p.C))) return false;
-  if ((p.B_sb | p.B_sl | p.B_sg | p.C_sb | p.C_sl | p.C_sg) & 7) return false;
+  if (((p.B_sb & mb) | (p.B_sl & ml) | (p.B_sg & mg) | (p.C_sb & mb) | (p.C_sl & ml) | (p.C_sg & mg)) & 7) return false;
   if (p.dt_dtype == ISSM_BF16) {
     if (p.dt && !aligned16(p.dt)) return false;
-    if ((p.dt_sb | p.dt_sl | p.dt_sh) & 7) return false;
+    if (((p.dt_sb & mb) | (p.dt_sl & ml) | (p.dt_sh & mh)) & 7) return false;
   } else {
     // float dt is read from global memory two adjacent states (8 bytes) at a time
-    if (((uintptr_t)p.dt & 7) || ((p.dt_sb | p.dt_sl | p.dt_sh) & 1)) return false;
+    if (((uintptr_t)p.dt & 7) || (((p.dt_sb & mb) | (p.dt_sl & ml) | (p.dt_sh & mh)) & 1)) return false;
   }
   return true;
 }

@@ -177,3 +177,26 @@ def test_parameter_generation_and_slice_entry_points_validate(built_lib):
     with pytest.raises(RuntimeError):
         adaptive_dt_bc(torch.randn(1, 4, 8, 4), torch.randn(2, 4), torch.randn(2, 4), torch.randn(1, 4, 2), torch.randn(2),
                        torch.randn(1, 4, 1), torch.randn(1, 4, 1))
+
+
+def test_strides_of_size_one_dimensions_do_not_select_the_slow_path(built_lib):
+    """A (b, L, 1, N) sum of broadcast views reaches the library with group stride 1, and a batch of one with any batch
+    stride: neither is ever used for addressing, so neither may fail the tensor-core path's alignment rules
+    (models/dest_module.py:546-547 builds B and C exactly like that)."""
+    from dest3d_b200 import _lib
+    p = _params(batch=1, seqlen=384, nheads=8, headdim=36, dstate=256, ngroups=1, chunk_size=256, io_dtype=_lib.BF16, dt_dtype=_lib.F32,
+                path=_lib.PATH_AUTO)
+    p.x_sb, p.x_sl, p.x_sh = 384 * 288, 288, 36
+    p.out_sb, p.out_sl, p.out_sh = 384 * 288, 288, 36
+    p.dout_sb, p.dout_sl, p.dout_sh = 384 * 288, 288, 36
+    p.dt_sb, p.dt_sl, p.dt_sh = 384 * 2048, 2048, 256
+    p.B_sb, p.B_sl, p.B_sg = 384 * 256, 256, 256
+    p.C_sb, p.C_sl, p.C_sg = 384 * 256, 256, 256
+    assert built_lib.issm_b200_resolve_path_pass(C.byref(p), 0) == _lib.PATH_TENSOR
+    p.B_sg = p.C_sg = 1                                                        # what torch reports for the size-one group axis
+    p.x_sb = p.dt_sb = p.B_sb = 7                                              # and any value for a batch of one
+    assert built_lib.issm_b200_resolve_path_pass(C.byref(p), 0) == _lib.PATH_TENSOR
+    assert built_lib.issm_b200_resolve_path_pass(C.byref(p), 1) == _lib.PATH_TENSOR
+    p.ngroups, p.nheads = 2, 8                                                 # with two groups the stride is real again
+    p.B_sl = p.C_sl = 512
+    assert built_lib.issm_b200_resolve_path_pass(C.byref(p), 0) == _lib.PATH_SIMT

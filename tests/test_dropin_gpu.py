@@ -113,9 +113,15 @@ def test_reference_caller_through_the_shim(dest_module, dtype):
     seen = []
     real = dm.ISSM_chunk_scan_combined
 
-    def spy(x, dt, *a, **k):
+    def spy(x, dt, A, B, C, *a, **k):
         seen.append((x.dtype, dt.dtype))
-        return real(x, dt, *a, **k)
+        if dtype == torch.bfloat16:                          # the reference's own tensors must reach the tensor-core kernels
+            import ctypes as ct
+            from dest3d_b200 import _lib, issm_combined
+            p, keep = issm_combined._fill_common(x, dt, A, B, C, k.get("chunk_size", a[0] if a else 256), k.get("D"), None, None,
+                                                 k.get("initial_states"), False, (0.0, float("inf")), False, "auto")
+            assert _lib.lib().issm_b200_resolve_path_pass(ct.byref(p), 0) == _lib.PATH_TENSOR, (B.stride(), C.stride(), dt.stride())
+        return real(x, dt, A, B, C, *a, **k)
 
     dm.ISSM_chunk_scan_combined = spy
     try:
@@ -134,3 +140,20 @@ def test_reference_caller_through_the_shim(dest_module, dtype):
         assert p.grad is not None, name
         parity.close(p.grad, ref_grads[name].grad, dtype, "d" + name, rep, loosen, literal=False)
     print("MultiHeadISSMScan through the shim:", parity.format_report(rep))
+
+    # the same block assembled from this library's kernels (fused PointLiteConv, dt / B / C generation, reverse scan
+    # without flips): the reference's state_dict loads unchanged, results against the same float64 run
+    from dest3d_b200.issm_block import MultiHeadISSMScan as NativeBlock
+    mine = NativeBlock(**kw)
+    mine.load_state_dict(state)
+    mine = mine.cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+        ok2, oq2 = mine(c(in_key), c(in_query), c(dist), c(xyz), mask.cuda())
+    ((ok2.float() * gk.cuda()).sum() + (oq2.float() * gq.cuda()).sum()).backward()
+    rep = []
+    parity.close(ok2, ok_ref, dtype, "out_key", rep, loosen, literal=False)
+    parity.close(oq2, oq_ref, dtype, "out_query", rep, loosen, literal=False)
+    for name, p in mine.named_parameters():
+        assert p.grad is not None, name
+        parity.close(p.grad, ref_grads[name].grad, dtype, "d" + name, rep, loosen, literal=False)
+    print("the block on this library's kernels:", parity.format_report(rep))
