@@ -285,6 +285,7 @@ static ConvPlan conv_plan(const issm_conv_params& p, bool bwd) {
 static int conv_validate(const issm_conv_params* p, bool bwd) {
   if (!p) return ISSM_ERR_NULL;
   if (p->batch <= 0 || p->seqlen <= 0 || p->channels <= 0 || p->batch > 65535) return ISSM_ERR_SHAPE;
+  if (((int64_t)p->seqlen + 16 * CONV_SEGS - 1) / (16 * CONV_SEGS) > 65535) return ISSM_ERR_SHAPE;   // grid.y of the shortest segments
   if (p->io_dtype != ISSM_F32 && p->io_dtype != ISSM_BF16) return ISSM_ERR_DTYPE;
   if (!p->x || !p->weight) return ISSM_ERR_NULL;
   if (!bwd && !p->y) return ISSM_ERR_NULL;
