@@ -322,7 +322,7 @@ class ISSMChunkScanCombinedFn(torch.autograd.Function):
 
 def ISSM_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
                              seq_idx=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
-                             return_final_states=False, *, reverse=False, path="auto"):
+                             return_final_states=False, *, reverse=False, path="auto", slices=1):
     """
     Argument:
         x: (batch, seqlen, nheads, headdim)
@@ -337,9 +337,16 @@ def ISSM_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias
         initial_states: (batch, nheads, headdim, dstate)
         seq_idx: (batch, seqlen) or None; sequences packed along seqlen, no state crosses a change of seq_idx
         dt_softplus: Whether to apply softplus to dt
+        slices (extension): cut every sequence into this many slices that run as extra batch entries (two passes; for
+            few, long sequences - one CTA serves one (sample, head) stream); "auto" picks the count from the sizes
     Return:
         out: (batch, seqlen, nheads, headdim), or (out, final_states (batch, nheads, headdim, dstate) fp32)
     """
+    if slices != 1 and seq_idx is None:
+        from .seqpar import issm_scan_chunk_parallel
+        return issm_scan_chunk_parallel(x, dt, A, B, C, chunk_size, D=D, z=z, dt_bias=dt_bias, initial_states=initial_states,
+                                        dt_softplus=dt_softplus, dt_limit=dt_limit, return_final_states=return_final_states,
+                                        reverse=reverse, path=path, slices=None if slices == "auto" else int(slices))
     if seq_idx is not None:
         return _scan_packed(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
                             return_final_states, reverse, path)

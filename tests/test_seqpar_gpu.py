@@ -34,6 +34,24 @@ def test_chunk_parallel_on_one_gpu_matches_whole_sequence(dtype, path, L, slices
     print(parity.format_report(parity.compare(got, ref, dtype)))
 
 
+def test_slices_keyword_of_the_public_call():
+    from dest3d_b200 import ISSM_chunk_scan_combined
+    inp = O.make_inputs(1, 1024, 2, 36, 256, seed=23, dtype=torch.bfloat16)
+    t = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    args = (t["x"], t["dt"], t["A"], t["B"], t["C"], 64)
+    kw = dict(D=t["D"], z=t["z"], dt_bias=t["dt_bias"], initial_states=t["initial_states"], return_final_states=True, **OPTS)
+    from dest3d_b200 import _lib
+    n0 = _lib.launch_count()
+    y1, s1 = ISSM_chunk_scan_combined(*args, **kw)
+    n1 = _lib.launch_count()
+    y4, s4 = ISSM_chunk_scan_combined(*args, slices=4, **kw)
+    assert _lib.launch_count() - n1 > n1 - n0               # two passes plus the decay sums: the sliced route was taken
+    ya, sa = ISSM_chunk_scan_combined(*args, slices="auto", **kw)          # 2 heads x 1 sample: cut into 2 (512 points each)
+    for y, s in ((y4, s4), (ya, sa)):
+        torch.testing.assert_close(y.float(), y1.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(s, s1, rtol=2e-2, atol=2e-2)
+
+
 def test_automatic_slice_count_falls_back_to_the_plain_scan():
     from dest3d_b200.seqpar import issm_scan_chunk_parallel
     inp = O.make_inputs(2, 300, 8, 36, 256, seed=2, dtype=torch.bfloat16)
