@@ -100,17 +100,20 @@ template <> struct Vec16<float> {
 };
 
 // Chunk c of lane `lane` covers features [(c * 32 + lane) * V, +V); CH chunks per lane cover up to 32 * V * CH features.
-template <typename T, int CH>
-__global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
-  constexpr int V = Vec16<T>::N;
+// TL = 1: the row is CH full chunks plus 32 more features, one per lane (feature CH * 32 * V + lane) - the detector's
+// 288 = 256 + 32 - instead of one more chunk in which 4 lanes of 32 would work.
+template <typename T, int CH, int TL>
+__global__ void __launch_bounds__(256, CH == 1 ? 4 : 2) k_norm_fwd_vec(issm_norm_params np) {
+  constexpr int V = Vec16<T>::N, FT = CH * 32 * V;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int H = np.hidden;
   const bool has_z = np.has_z != 0;
   const bool pre_gate = has_z && !np.norm_before_gate, post_gate = has_z && np.norm_before_gate;
   // a warp walks rows first, first + warps, ...; the 16-byte loads of the next row are issued (kept packed, 4 registers
-  // per chunk) before the current row is worked on
+  // per chunk) before the current row is worked on (two rows ahead measured slower: 121 registers, fewer resident warps)
   uint4 nx[CH], nz[CH];
+  float nxt = 0.f, nzt = 0.f;
   auto issue = [&](int row) {
     const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
     const T* z = has_z ? (const T*)np.z + (int64_t)row * np.z_sr : nullptr;
@@ -121,6 +124,10 @@ __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
         nx[c] = *(const uint4*)(x + f0);
         if (has_z) nz[c] = *(const uint4*)(z + f0);
       }
+    }
+    if constexpr (TL) {
+      nxt = ldf(x + FT + lane);
+      if (has_z) nzt = ldf(z + FT + lane);
     }
   };
   int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -136,6 +143,7 @@ __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
         if (has_z) Vec16<T>::unpack(nz[c], zg[c]);
       }
     }
+    float vt = nxt, zgt = nzt;                             // the lane's tail feature (TL)
     if (row + warps < np.rows) issue(row + warps);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
@@ -148,6 +156,12 @@ __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
           s2 = fmaf(v[c][i], v[c][i], s2);
         }
       }
+    }
+    if constexpr (TL) {
+      if (has_z) zgt = siluf_(zgt);
+      if (pre_gate) vt *= zgt;
+      s1 += vt;
+      s2 = fmaf(vt, vt, s2);
     }
     s1 = warp_sum(s1);
     s2 = warp_sum(s2);
@@ -163,6 +177,7 @@ __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
 #pragma unroll
           for (int i = 0; i < V; ++i) sv = fmaf(v[c][i] - mean, v[c][i] - mean, sv);
         }
+      if constexpr (TL) sv = fmaf(vt - mean, vt - mean, sv);
       var = warp_sum(sv) / H;
     }
     const float rstd = rsqrtf(var + np.eps);
@@ -186,16 +201,22 @@ __global__ void __launch_bounds__(256) k_norm_fwd_vec(issm_norm_params np) {
         Vec16<T>::store(y + f0, o);
       }
     }
+    if constexpr (TL) {
+      float o = (vt - mean) * rstd * np.weight[FT + lane];
+      if (np.has_bias) o += np.bias[FT + lane];
+      if (post_gate) o *= zgt;
+      stf(y + FT + lane, o);
+    }
   }
 }
 
 constexpr int NORM_BWD_WARPS = 4;
 
 // grid = nblk blocks of NORM_BWD_WARPS warps; block i handles rows [i*rpb, (i+1)*rpb); partial dw/db -> (nblk, hidden)
-template <typename T, int CH>
+template <typename T, int CH, int TL>
 __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_params np, int rpb, float* __restrict__ dwpart,
                                                                         float* __restrict__ dbpart) {
-  constexpr int V = Vec16<T>::N;
+  constexpr int V = Vec16<T>::N, FT = CH * 32 * V;       // TL: one more feature per lane behind the CH full chunks
   extern __shared__ float sm[];                          // [2][NORM_BWD_WARPS][hidden]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = np.hidden;
@@ -207,11 +228,14 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
 #pragma unroll
     for (int i = 0; i < V; ++i) { dwacc[c][i] = 0.f; dbacc[c][i] = 0.f; w[c][i] = f0 < H ? np.weight[f0 + i] : 0.f; }
   }
+  float dwt = 0.f, dbt = 0.f;
+  const float wt = TL ? np.weight[FT + lane] : 0.f;
   const int r_end = min(np.rows, (int)(blockIdx.x + 1) * rpb);
   const bool has_z = np.has_z != 0;
   // the 16-byte loads of the warp's next row are issued (kept packed, 4 registers per chunk) before the current row is
   // worked on
   uint4 nx[CH], ng[CH], nz[CH];
+  float nxt = 0.f, ngt = 0.f, nzt = 0.f;
   float nrstd = 0.f, nmean = 0.f;
   auto issue = [&](int row) {
     const T* x = (const T*)np.x + (int64_t)row * np.x_sr;
@@ -225,6 +249,11 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
         ng[c] = *(const uint4*)(dy + f0);
         if (has_z) nz[c] = *(const uint4*)(zp + f0);
       }
+    }
+    if constexpr (TL) {
+      nxt = ldf(x + FT + lane);
+      ngt = ldf(dy + FT + lane);
+      if (has_z) nzt = ldf(zp + FT + lane);
     }
     nrstd = np.rstd[row];
     nmean = np.is_rms ? 0.f : np.mean[row];
@@ -246,6 +275,7 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
         if (has_z) Vec16<T>::unpack(nz[c], zv[c]);
       }
     }
+    const float xrt = nxt, got = ngt, zvt = nzt;           // the lane's tail feature (TL)
     if (row + NORM_BWD_WARPS < r_end) issue(row + NORM_BWD_WARPS);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
@@ -261,6 +291,12 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
           c2 += wdy;
         }
       }
+    }
+    if constexpr (TL) {
+      const float vv = pre_gate ? xrt * siluf_(zvt) : xrt;
+      const float g_out = post_gate ? got * siluf_(zvt) : got;
+      c1 = fmaf((vv - mean) * rstd, g_out * wt, c1);
+      c2 += g_out * wt;
     }
     c1 = warp_sum(c1) / H;
     c2 = np.is_rms ? 0.f : warp_sum(c2) / H;
@@ -296,6 +332,29 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
         if (z) Vec16<T>::store(dz + f0, odz);
       }
     }
+    if constexpr (TL) {
+      const float zz = z ? zvt : 0.f;
+      const float sgm = z ? fast_sigmoid(zz) : 1.f;
+      const float sz = z ? zz * sgm : 1.f;
+      const float dsz = sgm * (1.f + zz * (1.f - sgm));
+      const float vv = pre_gate ? xrt * sz : xrt;
+      const float xh = (vv - mean) * rstd;
+      const float g_out = post_gate ? got * sz : got;
+      const float dv = (g_out * wt - xh * c1 - c2) * rstd;
+      dwt = fmaf(g_out, xh, dwt);
+      dbt += g_out;
+      if (pre_gate) {
+        stf(dx + FT + lane, dv * sz);
+        stf(dz + FT + lane, dv * xrt * dsz);
+      } else {
+        stf(dx + FT + lane, dv);
+        if (z) {
+          float yv = xh * wt;
+          if (np.has_bias) yv += np.bias[FT + lane];
+          stf(dz + FT + lane, post_gate ? got * yv * dsz : 0.f);
+        }
+      }
+    }
   }
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
@@ -307,6 +366,10 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
         sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + f0 + i] = dbacc[c][i];
       }
     }
+  }
+  if constexpr (TL) {
+    sm[(size_t)warp * H + FT + lane] = dwt;
+    sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + FT + lane] = dbt;
   }
   __syncthreads();
   for (int f = threadIdx.x; f < H; f += blockDim.x) {
@@ -328,6 +391,8 @@ static int norm_vec_chunks(const issm_norm_params& p, bool bwd) {
   if (!ok(p.x, p.x_sr) || (p.has_z && !ok(p.z, p.z_sr)) || ((uintptr_t)p.weight % 16)) return 0;
   if (!bwd && !ok(p.y, p.y_sr)) return 0;
   if (bwd && (!ok(p.dy, p.dy_sr) || !ok(p.dx, p.hidden) || (p.has_z && !ok(p.dz, p.hidden)))) return 0;
+  // full chunks plus exactly 32 more features: those go one per lane (returned as chunks + 16)
+  if (p.hidden % (32 * V) == 32 && p.hidden / (32 * V) >= 1 && p.hidden / (32 * V) <= 2) return p.hidden / (32 * V) + 16;
   const int need = (p.hidden + 32 * V - 1) / (32 * V);
   return need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 0;
 }
@@ -445,9 +510,11 @@ static int launch_norm_bwd_main(const issm_norm_params& p, int nblk, int rpb, fl
   const int ch = norm_vec_chunks(p, true);
 #define ISSM_NORM_BWD_VEC(T)                                                                                          \
   do {                                                                                                                \
-    if (ch == 1) ISSM_LAUNCH((k_norm_bwd_vec<T, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);      \
-    else if (ch == 2) ISSM_LAUNCH((k_norm_bwd_vec<T, 2>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart); \
-    else ISSM_LAUNCH((k_norm_bwd_vec<T, 4>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);              \
+    if (ch == 17) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);      \
+    else if (ch == 18) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart); \
+    else if (ch == 1) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
+    else ISSM_LAUNCH((k_norm_bwd_vec<T, 4, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);               \
   } while (0)
   if (ch) {                                               // rows of at most 1024 (bf16) / 512 (float) features: 32 KiB of shared memory at most
     if (p.io_dtype == ISSM_F32) ISSM_NORM_BWD_VEC(float); else ISSM_NORM_BWD_VEC(bf16);
@@ -478,9 +545,11 @@ extern "C" int issm_b200_norm_fwd(const issm_norm_params* p, void* stream) {
   const unsigned vgrid = grid < 148u * 4u ? grid : 148u * 4u;   // the vector kernel walks the rows with a grid stride (one resident wave)
 #define ISSM_NORM_FWD_VEC(T)                                                                                   \
   do {                                                                                                         \
-    if (ch == 1) ISSM_LAUNCH((k_norm_fwd_vec<T, 1>), vgrid, wpb * 32, 0, s, *p);                               \
-    else if (ch == 2) ISSM_LAUNCH((k_norm_fwd_vec<T, 2>), vgrid, wpb * 32, 0, s, *p);                          \
-    else ISSM_LAUNCH((k_norm_fwd_vec<T, 4>), vgrid, wpb * 32, 0, s, *p);                                       \
+    if (ch == 17) ISSM_LAUNCH((k_norm_fwd_vec<T, 1, 1>), vgrid, wpb * 32, 0, s, *p);                           \
+    else if (ch == 18) ISSM_LAUNCH((k_norm_fwd_vec<T, 2, 1>), vgrid, wpb * 32, 0, s, *p);                      \
+    else if (ch == 1) ISSM_LAUNCH((k_norm_fwd_vec<T, 1, 0>), vgrid, wpb * 32, 0, s, *p);                       \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_fwd_vec<T, 2, 0>), vgrid, wpb * 32, 0, s, *p);                       \
+    else ISSM_LAUNCH((k_norm_fwd_vec<T, 4, 0>), vgrid, wpb * 32, 0, s, *p);                                    \
   } while (0)
   if (ch) {
     if (p->io_dtype == ISSM_F32) ISSM_NORM_FWD_VEC(float); else ISSM_NORM_FWD_VEC(bf16);

@@ -67,6 +67,25 @@ def glue(args):
     return res
 
 
+def norm(args):
+    """z-gated RMSNorm (layernorm_gated.py:35-95) over 2^18 rows x 288 features, forward and backward, kernel launches
+    only (preallocated leaves): the detector's key_norm at a size larger than L2."""
+    from . import rmsnorm_fn
+    rows, H = 1 << 18, 288
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    res = {"rows": rows, "hidden": H}
+    for dt_, name in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        x = torch.randn(rows, H, device="cuda", generator=gen).to(dt_).requires_grad_(True)
+        z = torch.randn(rows, H, device="cuda", generator=gen).to(dt_).requires_grad_(True)
+        w = (1 + 0.02 * torch.randn(H, device="cuda", generator=gen)).requires_grad_(True)
+        dy = torch.randn(rows, H, device="cuda", generator=gen).to(dt_)
+        es = x.element_size()
+        fwd = _ms(lambda: rmsnorm_fn(x, w, None, z, eps=1e-5, norm_before_gate=False), args.reps)
+        bwd = _ms(lambda: torch.autograd.grad(rmsnorm_fn(x, w, None, z, eps=1e-5, norm_before_gate=False), (x, z, w), dy), args.reps) - fwd
+        res[name] = {"fwd_ms": fwd, "fwd_gbs": 3 * rows * H * es / fwd / 1e6, "bwd_ms": bwd, "bwd_gbs": 5 * rows * H * es / bwd / 1e6}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
@@ -103,6 +122,7 @@ def main():
             r["torch_gather_ms"] = _ms(lambda: pts.gather(1, order.unsqueeze(-1).expand(-1, -1, C)), args.reps)
         out[name] = r
     out["glue"] = glue(args)
+    out["norm"] = norm(args)
     print(json.dumps(out))
 
 
