@@ -46,6 +46,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--points", type=int, default=1024)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph")
     ap.add_argument("--reference", default=os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref"))
     args = ap.parse_args()
     from .issm_block import MultiHeadISSMScan
@@ -69,6 +70,20 @@ def main():
 
     out = {"batch": b, "points": L, "states": K, "d_model": d_model, "dtype": "bf16 autocast",
            "native_block_ms": _ms(step(mine), args.reps)}
+    if args.graph:
+        # the same step captured once into a CUDA graph and replayed (the step is launch-bound at the detector's size)
+        run = step(mine)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run()
+        out["native_block_graph_replay_ms"] = _ms(graph.replay, args.reps)
     ref_cls = _reference_class(args.reference)
     if ref_cls is not None:
         ref = ref_cls(**kw)
