@@ -213,8 +213,9 @@ __global__ void __launch_bounds__(256, CH == 1 ? 4 : 2) k_norm_fwd_vec(issm_norm
 constexpr int NORM_BWD_WARPS = 4;
 
 // grid = nblk blocks of NORM_BWD_WARPS warps; block i handles rows [i*rpb, (i+1)*rpb); partial dw/db -> (nblk, hidden)
-template <typename T, int CH, int TL>
-__global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_params np, int rpb, float* __restrict__ dwpart,
+// HB = 0: the call has no bias, so no bias-gradient accumulators are kept (a register per owned feature less).
+template <typename T, int CH, int TL, int HB>
+__global__ void __launch_bounds__(NORM_BWD_WARPS * 32, (CH == 1 && !HB) ? 5 : 0) k_norm_bwd_vec(issm_norm_params np, int rpb, float* __restrict__ dwpart,
                                                                         float* __restrict__ dbpart) {
   constexpr int V = Vec16<T>::N, FT = CH * 32 * V;       // TL: one more feature per lane behind the CH full chunks
   extern __shared__ float sm[];                          // [2][NORM_BWD_WARPS][hidden]
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
           const float wdy = g_out * w[c][i];
           const float dv = (wdy - xh * c1 - c2) * rstd;
           dwacc[c][i] = fmaf(g_out, xh, dwacc[c][i]);
-          dbacc[c][i] += g_out;
+          if constexpr (HB) dbacc[c][i] += g_out;
           if (pre_gate) {
             odx[i] = dv * sz;
             odz[i] = dv * xr[c][i] * dsz;
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
       const float g_out = post_gate ? got * sz : got;
       const float dv = (g_out * wt - xh * c1 - c2) * rstd;
       dwt = fmaf(g_out, xh, dwt);
-      dbt += g_out;
+      if constexpr (HB) dbt += g_out;
       if (pre_gate) {
         stf(dx + FT + lane, dv * sz);
         stf(dz + FT + lane, dv * xrt * dsz);
@@ -363,13 +364,13 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32) k_norm_bwd_vec(issm_norm_
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         sm[(size_t)warp * H + f0 + i] = dwacc[c][i];
-        sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + f0 + i] = dbacc[c][i];
+        sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + f0 + i] = HB ? dbacc[c][i] : 0.f;
       }
     }
   }
   if constexpr (TL) {
     sm[(size_t)warp * H + FT + lane] = dwt;
-    sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + FT + lane] = dbt;
+    sm[(size_t)NORM_BWD_WARPS * H + (size_t)warp * H + FT + lane] = HB ? dbt : 0.f;
   }
   __syncthreads();
   for (int f = threadIdx.x; f < H; f += blockDim.x) {
@@ -489,8 +490,9 @@ __global__ void __launch_bounds__(256) k_norm_reduce(const float* __restrict__ p
   }
 }
 
-static int norm_blocks(const issm_norm_params& p) {
-  const int want = 148 * 4;
+// blocks of the backward: one resident wave (five blocks of four warps per SM fit the bias-free vector kernel; the
+// workspace-free entry point keeps to its built-in scratch of 148 * 4 partial rows)
+static int norm_blocks(const issm_norm_params& p, int want = 148 * 5) {
   return p.rows < want ? (p.rows > 0 ? p.rows : 1) : want;
 }
 
@@ -508,13 +510,18 @@ static int norm_validate(const issm_norm_params* p, bool bwd) {
 // the backward main kernel of one call (vector kernels when the call qualifies, see norm_vec_chunks)
 static int launch_norm_bwd_main(const issm_norm_params& p, int nblk, int rpb, float* dwpart, float* dbpart, size_t smem, cudaStream_t s) {
   const int ch = norm_vec_chunks(p, true);
+#define ISSM_NORM_BWD_VEC2(T, HBV)                                                                                            \
+  do {                                                                                                                      \
+    if (ch == 17) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 1, HBV>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);      \
+    else if (ch == 18) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 1, HBV>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart); \
+    else if (ch == 1) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 0, HBV>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
+    else if (ch == 2) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 0, HBV>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
+    else ISSM_LAUNCH((k_norm_bwd_vec<T, 4, 0, HBV>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);               \
+  } while (0)
 #define ISSM_NORM_BWD_VEC(T)                                                                                          \
   do {                                                                                                                \
-    if (ch == 17) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);      \
-    else if (ch == 18) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 1>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart); \
-    else if (ch == 1) ISSM_LAUNCH((k_norm_bwd_vec<T, 1, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
-    else if (ch == 2) ISSM_LAUNCH((k_norm_bwd_vec<T, 2, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);  \
-    else ISSM_LAUNCH((k_norm_bwd_vec<T, 4, 0>), nblk, NORM_BWD_WARPS * 32, smem, s, p, rpb, dwpart, dbpart);               \
+    /* the bias-free variant exists for one-chunk rows; wider rows keep the general one */                           \
+    if (p.has_bias || (ch != 1 && ch != 17)) ISSM_NORM_BWD_VEC2(T, 1); else ISSM_NORM_BWD_VEC2(T, 0);                 \
   } while (0)
   if (ch) {                                               // rows of at most 1024 (bf16) / 512 (float) features: 32 KiB of shared memory at most
     if (p.io_dtype == ISSM_F32) ISSM_NORM_BWD_VEC(float); else ISSM_NORM_BWD_VEC(bf16);
@@ -566,7 +573,9 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
   if (p->rows == 0) return ISSM_OK;
   if (!p->workspace || p->workspace_bytes < issm_b200_norm_workspace_bytes(p, 1)) return ISSM_ERR_WORKSPACE;
   cudaStream_t s = (cudaStream_t)stream;
-  const int nblk = norm_blocks(*p);
+  // five resident blocks per SM only fit the kernel variant that was built for them (one chunk, no bias)
+  const int vch = norm_vec_chunks(*p, true);
+  const int nblk = norm_blocks(*p, ((vch == 1 || vch == 17) && !p->has_bias) ? 148 * 5 : 148 * 4);
   const int rpb = (p->rows + nblk - 1) / nblk;
   float* dwpart = (float*)p->workspace;
   float* dbpart = dwpart + (size_t)nblk * p->hidden;
@@ -598,7 +607,7 @@ extern "C" int issm_b200_norm_bwd(const issm_norm_params* p, void* stream) {
 // ---------------------------------------------------------------------------------------------
 namespace issm {
 constexpr int kNoAllocMaxHidden = 1024;                 // widest row the built-in scratch covers
-constexpr int kNoAllocMaxBlocks = 148 * 4;              // == the largest grid norm_blocks() returns
+constexpr int kNoAllocMaxBlocks = 148 * 4;              // the grid limit handed to norm_blocks() below
 static __device__ __align__(256) float g_norm_scratch[2 * kNoAllocMaxBlocks * kNoAllocMaxHidden];
 
 // The array's name is only a host-side handle; kernels need its device address, which differs per
@@ -631,7 +640,7 @@ extern "C" int issm_b200_norm_bwd_noalloc(const issm_norm_params* p, void* strea
   float* scratch = norm_scratch_address(&rc);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  const int nblk = norm_blocks(*p);                      // <= kNoAllocMaxBlocks
+  const int nblk = norm_blocks(*p, kNoAllocMaxBlocks);
   const int rpb = (p->rows + nblk - 1) / nblk;
   float* dwpart = scratch;
   float* dbpart = scratch + (size_t)nblk * p->hidden;
