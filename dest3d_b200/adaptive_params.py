@@ -14,6 +14,11 @@ import torch
 from . import _lib
 
 
+def _empty(shape, dtype, device):
+    """Every output and workspace of this module is allocated here (the guard-band tests substitute it)."""
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
 def _params(dist, w, tok, mask, H, G, back):
     p = _lib.IssmGlueParams()
     p.batch, p.seqlen, p.nstates, p.nfeat = dist.shape
@@ -36,8 +41,8 @@ class AdaptiveDtBcFn(torch.autograd.Function):
         tokf = tok.detach().float().contiguous()
         maskf = None if mask is None else mask.float().contiguous()
         nb = (4 if back else 2) * G
-        dt = torch.empty((b, L, H, K), dtype=dist.dtype, device=dist.device)
-        bc = torch.empty((b, L, nb, K), dtype=dist.dtype, device=dist.device)
+        dt = _empty((b, L, H, K), dist.dtype, dist.device)
+        bc = _empty((b, L, nb, K), dist.dtype, dist.device)
         p = _params(dist, w, tokf, maskf, H, G, back)
         p.dt, p.bc = dt.data_ptr(), bc.data_ptr()
         with torch.cuda.device(dist.device):
@@ -54,9 +59,9 @@ class AdaptiveDtBcFn(torch.autograd.Function):
         H, G, back, wdt_t, wbc_t, tok_t = ctx.meta
         b, L, K, M = dist.shape
         RW = H + 2 * G
-        ddist = torch.empty((b, L, K, M), dtype=dist.dtype, device=dist.device)
-        dw = torch.empty((RW, M), dtype=torch.float32, device=dist.device)
-        dtok = torch.empty(tokf.shape, dtype=torch.float32, device=dist.device)
+        ddist = _empty((b, L, K, M), dist.dtype, dist.device)
+        dw = _empty((RW, M), torch.float32, dist.device)
+        dtok = _empty(tokf.shape, torch.float32, dist.device)
         p = _params(dist, w, tokf, maskf, H, G, back)
         keep = []
         for name, g in (("ddt", ddt), ("dbc", dbc)):
@@ -66,7 +71,7 @@ class AdaptiveDtBcFn(torch.autograd.Function):
                 setattr(p, name, g.data_ptr())
         p.ddist, p.dweight, p.dtok = ddist.data_ptr(), dw.data_ptr(), dtok.data_ptr()
         need = _lib.lib().issm_b200_glue_workspace_bytes(ct.byref(p))
-        ws = torch.empty(need, dtype=torch.uint8, device=dist.device)
+        ws = _empty((need,), torch.uint8, dist.device)
         p.workspace, p.workspace_bytes = ws.data_ptr(), need
         with torch.cuda.device(dist.device):
             rc = _lib.lib().issm_b200_glue_bwd(ct.byref(p), _lib.stream_ptr(dist.device))

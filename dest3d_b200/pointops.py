@@ -16,6 +16,11 @@ from torch import nn
 from . import _lib
 
 
+def _empty(shape, dtype, device):
+    """Every output and workspace of this module is allocated here (the guard-band tests substitute it)."""
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
 def _gather_rows(src, index):
     if not src.is_cuda:
         raise RuntimeError("dest3d_b200.pointops runs on CUDA tensors only")
@@ -26,7 +31,7 @@ def _gather_rows(src, index):
     index = index.to(torch.int64).contiguous()
     B, N, Cc = src.shape
     M = index.shape[1]
-    dst = torch.empty((B, M, Cc), dtype=src.dtype, device=src.device)
+    dst = _empty((B, M, Cc), src.dtype, src.device)
     status = torch.zeros(1, dtype=torch.int32, device=src.device)
     if dst.numel() == 0:
         return dst, status
@@ -92,7 +97,7 @@ class DwConv7SiluFn(torch.autograd.Function):
             x = x.contiguous()
         wf = weight.detach().reshape(-1, 7).float().contiguous()
         bf = None if bias is None else bias.detach().float().contiguous()
-        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        y = _empty(x.shape, x.dtype, x.device)
         if y.numel():
             p = _conv_params(x, wf, bf)
             p.y = y.data_ptr()
@@ -111,15 +116,19 @@ class DwConv7SiluFn(torch.autograd.Function):
         dy = dy.to(x.dtype)
         wf = weight.detach().reshape(-1, 7).float().contiguous()
         bf = None if bias is None else bias.detach().float().contiguous()
-        dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        dw = torch.zeros(wf.shape, dtype=torch.float32, device=x.device)
-        db = None if bias is None else torch.zeros(bias.shape, dtype=torch.float32, device=x.device)
-        if x.numel():
+        dx = _empty(x.shape, x.dtype, x.device)
+        dw = _empty(wf.shape, torch.float32, x.device)
+        db = None if bias is None else _empty(bias.shape, torch.float32, x.device)
+        if not x.numel():
+            dw.zero_()
+            if db is not None:
+                db.zero_()
+        else:
             p = _conv_params(x, wf, bf)
             p.dy, p.dy_sb, p.dy_sl = dy.data_ptr(), dy.stride(0), dy.stride(1)
             p.dx, p.dweight, p.dbias = dx.data_ptr(), dw.data_ptr(), _lib.ptr(db)
             need = _lib.lib().issm_b200_dwconv_workspace_bytes(ct.byref(p))
-            ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+            ws = _empty((need,), torch.uint8, x.device)
             p.workspace, p.workspace_bytes = ws.data_ptr(), need
             with torch.cuda.device(x.device):
                 rc = _lib.lib().issm_b200_dwconv7_silu_bwd(ct.byref(p), _lib.stream_ptr(x.device))
