@@ -129,7 +129,8 @@ class _StatusMirror:
     """Pinned host copy of one device's status word.  After every call an asynchronous 4-byte copy of the word
     is enqueued behind the call's kernels; the next call on that device (or `raise_on_device_error`) looks at the
     copy once it has landed.  An expired device-side wait therefore surfaces as a Python exception at the first
-    call made after the failing kernels have finished, without this module ever blocking on the device."""
+    call made after the failing kernels have finished and a copy enqueued behind them has landed (one copy is in flight
+    at a time), without this module ever blocking on the device."""
 
     def __init__(self, device):
         self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -175,7 +176,8 @@ def _check_status(device, what):
         if torch.cuda.is_current_stream_capturing():     # inside a CUDA-graph capture: neither query nor copy
             return
         m.poll(what)
-        m.refresh()
+        if not m.pending:                                # one copy in flight at a time: a step of several calls enqueues one
+            m.refresh()
 
 
 def raise_on_device_error(device=None, what="ISSM"):

@@ -79,3 +79,30 @@ def test_bounded_wait_runs_out_and_the_device_stays_usable():
     opts = dict(dt_softplus=True, dt_limit=(1e-3, 1e-1))
     parity.compare(parity.cuda_run(inp, 256, opts, path="tensor"), parity.oracle_run(inp, 256, opts), torch.bfloat16)
     assert issm_combined.device_status() == 0
+
+
+def test_expired_wait_surfaces_without_a_synchronising_check():
+    """The default route: the status word is mirrored to pinned host memory behind the calls, and an ISSM call made after
+    the failing kernels finished raises (within a few calls: one mirror copy is in flight at a time)."""
+    from dest3d_b200 import issm_combined
+    from oracle import issm_oracle as O
+    from tests import parity
+    L = selftest_lib()
+    L.issm_b200_selftest_bounded_wait.restype = ct.c_int
+    inp = O.make_inputs(1, 100, 2, 36, 256, seed=4, dtype=torch.bfloat16)
+    opts = dict(dt_softplus=True, dt_limit=(1e-3, 1e-1), return_final=False, dfinal=False)
+    issm_combined.device_status()                                   # clear
+    parity.cuda_run(inp, 256, opts, path="tensor")                  # a healthy call: mirror copy in flight
+    word = issm_combined._status_word(torch.cuda.current_device())
+    expired = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert L.issm_b200_selftest_bounded_wait(ct.c_uint32(1000), ct.c_void_p(word.data_ptr()), ct.c_void_p(expired.data_ptr()),
+                                             ct.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        for _ in range(4):
+            parity.cuda_run(inp, 256, opts, path="tensor")
+            torch.cuda.synchronize()
+    assert issm_combined.device_status() == 0                       # raising cleared the word
+    parity.cuda_run(inp, 256, opts, path="tensor")                  # and the device goes on working
+    torch.cuda.synchronize()
+    assert issm_combined.device_status() & 1 == 0
