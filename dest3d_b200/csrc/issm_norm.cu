@@ -99,6 +99,14 @@ template <> struct Vec16<float> {
   static __device__ __forceinline__ void store(float* p, const float* v) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
 };
 
+// 16 bytes of a row whose start is only known to be 4-byte aligned (the gate z of the detector is a column slice of a
+// wider projection output: its rows start 4 bytes off a 16-byte boundary)
+__device__ __forceinline__ uint4 ld16(const void* p, bool aligned16) {
+  if (aligned16) return *(const uint4*)p;
+  const uint32_t* q = (const uint32_t*)p;
+  return make_uint4(q[0], q[1], q[2], q[3]);
+}
+
 // Chunk c of lane `lane` covers features [(c * 32 + lane) * V, +V); CH chunks per lane cover up to 32 * V * CH features.
 // TL = 1: the row is CH full chunks plus 32 more features, one per lane (feature CH * 32 * V + lane) - the detector's
 // 288 = 256 + 32 - instead of one more chunk in which 4 lanes of 32 would work.
@@ -109,6 +117,7 @@ __global__ void __launch_bounds__(256, CH == 1 ? 4 : 2) k_norm_fwd_vec(issm_norm
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int H = np.hidden;
   const bool has_z = np.has_z != 0;
+  const bool z16 = !(((uintptr_t)np.z | (uintptr_t)(np.z_sr * (int64_t)sizeof(T))) & 15);
   const bool pre_gate = has_z && !np.norm_before_gate, post_gate = has_z && np.norm_before_gate;
   // a warp walks rows first, first + warps, ...; the 16-byte loads of the next row are issued (kept packed, 4 registers
   // per chunk) before the current row is worked on (two rows ahead measured slower: 121 registers, fewer resident warps)
@@ -122,7 +131,7 @@ __global__ void __launch_bounds__(256, CH == 1 ? 4 : 2) k_norm_fwd_vec(issm_norm
       const int f0 = (c * 32 + lane) * V;
       if (f0 < H) {
         nx[c] = *(const uint4*)(x + f0);
-        if (has_z) nz[c] = *(const uint4*)(z + f0);
+        if (has_z) nz[c] = ld16(z + f0, z16);
       }
     }
     if constexpr (TL) {
@@ -233,6 +242,7 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32, (CH == 1 && !HB) ? 5 : 0)
   const float wt = TL ? np.weight[FT + lane] : 0.f;
   const int r_end = min(np.rows, (int)(blockIdx.x + 1) * rpb);
   const bool has_z = np.has_z != 0;
+  const bool z16 = !(((uintptr_t)np.z | (uintptr_t)(np.z_sr * (int64_t)sizeof(T))) & 15);
   // the 16-byte loads of the warp's next row are issued (kept packed, 4 registers per chunk) before the current row is
   // worked on
   uint4 nx[CH], ng[CH], nz[CH];
@@ -248,7 +258,7 @@ __global__ void __launch_bounds__(NORM_BWD_WARPS * 32, (CH == 1 && !HB) ? 5 : 0)
       if (f0 < H) {
         nx[c] = *(const uint4*)(x + f0);
         ng[c] = *(const uint4*)(dy + f0);
-        if (has_z) nz[c] = *(const uint4*)(zp + f0);
+        if (has_z) nz[c] = ld16(zp + f0, z16);
       }
     }
     if constexpr (TL) {
@@ -389,7 +399,9 @@ static int norm_vec_chunks(const issm_norm_params& p, bool bwd) {
   const int V = p.io_dtype == ISSM_BF16 ? 8 : 4, esz = p.io_dtype == ISSM_BF16 ? 2 : 4;
   if (p.group_size != p.hidden || p.hidden % V) return 0;
   auto ok = [&](const void* ptr, int64_t stride) { return ((uintptr_t)ptr % 16 == 0) && ((stride * esz) % 16 == 0); };
-  if (!ok(p.x, p.x_sr) || (p.has_z && !ok(p.z, p.z_sr)) || ((uintptr_t)p.weight % 16)) return 0;
+  auto ok4 = [&](const void* ptr, int64_t stride) { return ((uintptr_t)ptr % 4 == 0) && ((stride * esz) % 4 == 0); };
+  // the gate may start its rows on any 4-byte boundary (read as four 4-byte words then)
+  if (!ok(p.x, p.x_sr) || (p.has_z && !ok4(p.z, p.z_sr)) || ((uintptr_t)p.weight % 16)) return 0;
   if (!bwd && !ok(p.y, p.y_sr)) return 0;
   if (bwd && (!ok(p.dy, p.dy_sr) || !ok(p.dx, p.hidden) || (p.has_z && !ok(p.dz, p.hidden)))) return 0;
   // full chunks plus exactly 32 more features: those go one per lane (returned as chunks + 16)

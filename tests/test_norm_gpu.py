@@ -88,3 +88,30 @@ def test_module_interface_and_determinism():
     y2 = m(x, z)
     y2.sum().backward()
     assert torch.equal(y1, y2) and torch.equal(g1, x.grad) and torch.equal(w1, m.weight.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("nbg", [False, True], ids=["gate_first", "norm_first"])
+def test_gate_as_a_column_slice_of_the_projection(dtype, nbg):
+    """The detector's gate: z = zxbcdt[..., :288] of a (b, L, 586) projection output (models/dest_module.py:528-529),
+    rows 1172 bytes apart in bfloat16, i.e. starting 4 bytes off a 16-byte boundary; also a slice that starts inside
+    the row.  Same results as with a contiguous copy, bit for bit (the vector kernels read such a gate as 4-byte words)."""
+    from dest3d_b200 import _lib, rmsnorm_fn
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(5, 40, 288, generator=g).to(dtype).cuda().requires_grad_()
+    wide = torch.randn(5, 40, 586, generator=g).to(dtype).cuda()
+    w = (1 + 0.02 * torch.randn(288, generator=g)).cuda().requires_grad_()
+    dy = torch.randn(5, 40, 288, generator=g).to(dtype).cuda()
+    for lo in (0, 2):
+        zv = wide[..., lo:lo + 288].detach().requires_grad_()          # a leaf that is itself a strided view
+        zc = wide[..., lo:lo + 288].contiguous().requires_grad_()
+        n0 = _lib.launch_count()
+        y1 = rmsnorm_fn(x, w, None, zv, eps=1e-5, norm_before_gate=nbg)
+        g1 = torch.autograd.grad(y1, (x, w, zv), dy)
+        used = _lib.launch_count() - n0
+        y2 = rmsnorm_fn(x, w, None, zc, eps=1e-5, norm_before_gate=nbg)
+        g2 = torch.autograd.grad(y2, (x, w, zc), dy)
+        assert torch.equal(y1, y2)
+        for a, b in zip(g1, g2):
+            assert torch.equal(a, b)
+        assert used == 3                                        # forward, backward, one fixed-order reduction
