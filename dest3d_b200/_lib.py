@@ -63,7 +63,7 @@ class IssmConvParams(C.Structure):
 class IssmGlueParams(C.Structure):
     """Mirror of `issm_glue_params`."""
     _fields_ = (
-        [(n, i32) for n in ("batch", "seqlen", "nstates", "nfeat", "nheads", "ngroups", "has_back", "io_dtype")]
+        [(n, i32) for n in ("batch", "seqlen", "nstates", "nfeat", "nheads", "ngroups", "has_back", "io_dtype", "dist_dtype")]
         + [("dist", vp), ("dist_sb", i64), ("dist_sl", i64), ("dist_sk", i64), ("weight", vp), ("tok", vp), ("mask", vp),
            ("dt", vp), ("bc", vp), ("ddt", vp), ("dbc", vp), ("ddist", vp), ("dweight", vp), ("dtok", vp),
            ("workspace", vp), ("workspace_bytes", C.c_size_t)]

@@ -90,7 +90,9 @@ __device__ __forceinline__ float glue_softplus(float v) {
 
 // one block per point (b, l); a thread owns two adjacent states and computes them with packed fp32 instructions,
 // reading four weights per shared-memory access
-template <typename T, int M>
+// TD: element type of dist (and ddist), T: of dt / bc and their gradients (float dist with bfloat16 outputs is what
+// autocast hands the block: the features stay float32, the activations are bfloat16)
+template <typename TD, typename T, int M>
 __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
   __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
   __shared__ float stok[GLUE_MAX_ROWS + 8];
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
   for (int i = threadIdx.x; i < a.RW * M; i += blockDim.x) sw[i] = a.w[i];
   for (int i = threadIdx.x; i < a.RO; i += blockDim.x) stok[i] = a.tok[((int64_t)b * a.L + l) * a.RO + i];
   __syncthreads();
-  const T* drow = (const T*)a.dist + b * a.d_sb + l * a.d_sl;
+  const TD* drow = (const TD*)a.dist + b * a.d_sb + l * a.d_sl;
   const int64_t row = (int64_t)b * a.L + l;
   T* dt = (T*)a.dt + row * a.H * a.K;
   T* bc = (T*)a.bc + row * (a.RO - a.H) * a.K;
@@ -106,8 +108,8 @@ __global__ void __launch_bounds__(128) k_glue_fwd(GlueArgs a) {
   for (int k = 2 * threadIdx.x; k < a.K; k += 2 * blockDim.x) {
     const bool two = k + 1 < a.K;
     float d0[M], d1[M];
-    load_feats<T, M>(drow + (int64_t)k * a.d_sk, d0);
-    load_feats<T, M>(drow + (int64_t)(two ? k + 1 : k) * a.d_sk, d1);
+    load_feats<TD, M>(drow + (int64_t)k * a.d_sk, d0);
+    load_feats<TD, M>(drow + (int64_t)(two ? k + 1 : k) * a.d_sk, d1);
     float2 dp[M];
 #pragma unroll
     for (int j = 0; j < M; ++j) dp[j] = make_float2(d0[j], d1[j]);
@@ -159,16 +161,16 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 // One stage of the backward's input pipeline: everything a (point, tile of 256 states) needs, as raw bytes.  The
 // number of gradient rows is the call's (RO), so the layout is computed at run time.
-template <typename T, int M>
+template <typename TD, typename T, int M>
 struct GlueStage {
   unsigned char* base;
   int ro;
   __host__ __device__ static size_t bytes(int ro) {
-    return ((size_t)GLUE_KT * M * sizeof(T) + (size_t)ro * GLUE_KT * sizeof(T) + GLUE_KT * 4 + (GLUE_MAX_ROWS + 8) * 4 + 15) / 16 * 16;
+    return ((size_t)GLUE_KT * M * sizeof(TD) + (size_t)ro * GLUE_KT * sizeof(T) + GLUE_KT * 4 + (GLUE_MAX_ROWS + 8) * 4 + 15) / 16 * 16;
   }
-  __device__ T* dist(int kk) const { return (T*)base + (size_t)kk * M; }                       // [GLUE_KT][M]
-  __device__ T* grad(int r) const { return (T*)base + (size_t)GLUE_KT * M + (size_t)r * GLUE_KT; }   // ddt rows, then the B / C rows
-  __device__ float* mask() const { return (float*)(base + (size_t)GLUE_KT * (M + ro) * sizeof(T)); }
+  __device__ TD* dist(int kk) const { return (TD*)base + (size_t)kk * M; }                       // [GLUE_KT][M]
+  __device__ T* grad(int r) const { return (T*)(base + (size_t)GLUE_KT * M * sizeof(TD)) + (size_t)r * GLUE_KT; }   // ddt rows, then the B / C rows
+  __device__ float* mask() const { return (float*)(base + (size_t)GLUE_KT * (M * sizeof(TD) + ro * sizeof(T))); }
   __device__ float* tok() const { return mask() + GLUE_KT; }
 };
 
@@ -177,11 +179,11 @@ struct GlueStage {
 // (1) a thread takes two adjacent states: g, ddist, token sums; g and the features are parked in shared memory;
 // (2) thread (row r, four features, a range of the tile's states) adds sum_k g[r, k] dist[k, j] to its accumulators of
 // the weight gradient.  The accumulators go out once per block and are summed in a fixed order.
-template <typename T, int M>
+template <typename TD, typename T, int M>
 __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int vec_ok) {
   extern __shared__ __align__(16) unsigned char glue_dyn[];
-  const size_t stage_bytes = GlueStage<T, M>::bytes(a.RO);
-  auto stage_of = [&](int it) { return GlueStage<T, M>{glue_dyn + (it & 1) * stage_bytes, a.RO}; };
+  const size_t stage_bytes = GlueStage<TD, T, M>::bytes(a.RO);
+  auto stage_of = [&](int it) { return GlueStage<TD, T, M>{glue_dyn + (it & 1) * stage_bytes, a.RO}; };
   __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
   __shared__ float sred[4][GLUE_MAX_ROWS + 8];
   __shared__ float sg[GLUE_MAX_ROWS][GLUE_KT + 1];
@@ -201,12 +203,12 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
 
   // copies of item `it` into stage `st`.  vec_ok: every row of states starts on a 16-byte boundary, so the gradient rows
   // and the mask go in 16-byte pieces; otherwise element by element through registers.
-  auto issue = [&](int it, const GlueStage<T, M>& st) {
+  auto issue = [&](int it, const GlueStage<TD, T, M>& st) {
     const int pt = blockIdx.x + (it / ntile) * gridDim.x, k0 = (it % ntile) * GLUE_KT;
     const int b = pt / a.L, l = pt - b * a.L;
     const int nk = min(GLUE_KT, a.K - k0);
-    const T* drow = (const T*)a.dist + b * a.d_sb + l * a.d_sl + (int64_t)k0 * a.d_sk;
-    constexpr int RB = M * (int)sizeof(T), CS = RB >= 16 ? 16 : RB, CH = RB / CS;     // bytes per state, per piece, pieces per state
+    const TD* drow = (const TD*)a.dist + b * a.d_sb + l * a.d_sl + (int64_t)k0 * a.d_sk;
+    constexpr int RB = M * (int)sizeof(TD), CS = RB >= 16 ? 16 : RB, CH = RB / CS;     // bytes per state, per piece, pieces per state
     for (int c = threadIdx.x; c < nk * CH; c += blockDim.x) {
       const int kk = c / CH, part = c % CH;
       cp_async((char*)st.dist(kk) + part * CS, (const char*)(drow + (int64_t)kk * a.d_sk) + part * CS, CS);
@@ -242,21 +244,21 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
   for (int r = 0; r < GLUE_MAX_ROWS + 8; ++r) tsum[r] = 0.f;
   if (nitems > 0) issue(0, stage_of(0));
   for (int it = 0; it < nitems; ++it) {
-    const GlueStage<T, M> st = stage_of(it);
+    const GlueStage<TD, T, M> st = stage_of(it);
     if (it + 1 < nitems) { issue(it + 1, stage_of(it + 1)); cp_async_wait<1>(); }
     else cp_async_wait<0>();
     __syncthreads();                                       // this item's inputs are in shared memory
     const int pt = blockIdx.x + (it / ntile) * gridDim.x, k0 = (it % ntile) * GLUE_KT;
     const int64_t row = pt;
-    T* ddist = (T*)a.ddist + row * a.K * M;
+    TD* ddist = (TD*)a.ddist + row * a.K * M;
     {                                                      // two adjacent states per thread: 128 threads cover the tile
       const int kk = 2 * threadIdx.x, k = k0 + kk;
       const bool in0 = k < a.K, in1 = k + 1 < a.K;
       float d0[M], d1[M];
 #pragma unroll
       for (int j = 0; j < M; ++j) { d0[j] = 0.f; d1[j] = 0.f; }
-      if (in0) load_feats<T, M>(st.dist(kk), d0);
-      if (in1) load_feats<T, M>(st.dist(kk + 1), d1);
+      if (in0) load_feats<TD, M>(st.dist(kk), d0);
+      if (in1) load_feats<TD, M>(st.dist(kk + 1), d1);
       float2 dp[M], dd[M];
 #pragma unroll
       for (int j = 0; j < M; ++j) { dp[j] = make_float2(d0[j], d1[j]); dd[j] = make_float2(0.f, 0.f); }
@@ -311,8 +313,8 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
       }
 #pragma unroll
       for (int j = 0; j < M; ++j) { d0[j] = dd[j].x; d1[j] = dd[j].y; }
-      if (in0) store_feats<T, M>(ddist + (int64_t)k * M, d0);
-      if (in1) store_feats<T, M>(ddist + (int64_t)(k + 1) * M, d1);
+      if (in0) store_feats<TD, M>(ddist + (int64_t)k * M, d0);
+      if (in1) store_feats<TD, M>(ddist + (int64_t)(k + 1) * M, d1);
       if (a.dbc) {                                         // token terms of the B / C rows (each output row has its own)
 #pragma unroll
         for (int ro = 0; ro < GLUE_MAX_ROWS + 8; ++ro)
@@ -395,10 +397,11 @@ static int glue_validate(const issm_glue_params* p, bool bwd) {
   if (p->nfeat != 4 && p->nfeat != 8 && p->nfeat != 16) return ISSM_ERR_SHAPE;
   if (p->nheads + 2 * p->ngroups > GLUE_MAX_ROWS || p->nheads + 4 * p->ngroups > GLUE_MAX_ROWS + 8) return ISSM_ERR_SHAPE;
   if (p->io_dtype != ISSM_F32 && p->io_dtype != ISSM_BF16) return ISSM_ERR_DTYPE;
+  if (p->dist_dtype != p->io_dtype && !(p->dist_dtype == ISSM_F32 && p->io_dtype == ISSM_BF16)) return ISSM_ERR_DTYPE;
   if (!p->dist || !p->weight || !p->tok) return ISSM_ERR_NULL;
   if (!bwd && (!p->dt || !p->bc)) return ISSM_ERR_NULL;
   if (bwd && (!p->ddist || !p->dweight || !p->dtok)) return ISSM_ERR_NULL;
-  const size_t es = p->io_dtype == ISSM_F32 ? 4 : 2;
+  const size_t es = p->dist_dtype == ISSM_F32 ? 4 : 2;
   if (((uintptr_t)p->dist % 16) || (p->dist_sb * es) % 16 || (p->dist_sl * es) % 16 || (p->dist_sk * es) % (p->nfeat * es >= 16 ? 16 : p->nfeat * es))
     return ISSM_ERR_ALIGN;
   return ISSM_OK;
@@ -416,19 +419,19 @@ static GlueArgs glue_args(const issm_glue_params& p) {
 
 using namespace issm;
 
+#define GLUE_DISPATCH_M(KERNEL, TD, T)                                                                \
+  do {                                                                                                \
+    if (p->nfeat == 16) ISSM_LAUNCH((KERNEL<TD, T, 16>), grid, 128, 0, s, a);                         \
+    else if (p->nfeat == 8) ISSM_LAUNCH((KERNEL<TD, T, 8>), grid, 128, 0, s, a);                      \
+    else ISSM_LAUNCH((KERNEL<TD, T, 4>), grid, 128, 0, s, a);                                         \
+  } while (0)
 #define GLUE_DISPATCH(KERNEL)                                                                         \
   do {                                                                                                \
     const dim3 grid(p->seqlen, p->batch);                                                             \
     cudaStream_t s = (cudaStream_t)stream;                                                            \
-    if (p->io_dtype == ISSM_F32) {                                                                    \
-      if (p->nfeat == 16) ISSM_LAUNCH((KERNEL<float, 16>), grid, 128, 0, s, a);                       \
-      else if (p->nfeat == 8) ISSM_LAUNCH((KERNEL<float, 8>), grid, 128, 0, s, a);                    \
-      else ISSM_LAUNCH((KERNEL<float, 4>), grid, 128, 0, s, a);                                       \
-    } else {                                                                                          \
-      if (p->nfeat == 16) ISSM_LAUNCH((KERNEL<bf16, 16>), grid, 128, 0, s, a);                        \
-      else if (p->nfeat == 8) ISSM_LAUNCH((KERNEL<bf16, 8>), grid, 128, 0, s, a);                     \
-      else ISSM_LAUNCH((KERNEL<bf16, 4>), grid, 128, 0, s, a);                                        \
-    }                                                                                                 \
+    if (p->io_dtype == ISSM_F32) GLUE_DISPATCH_M(KERNEL, float, float);                               \
+    else if (p->dist_dtype == ISSM_F32) GLUE_DISPATCH_M(KERNEL, float, bf16);                         \
+    else GLUE_DISPATCH_M(KERNEL, bf16, bf16);                                                         \
   } while (0)
 
 extern "C" size_t issm_b200_sizeof_glue_params(void) { return sizeof(issm_glue_params); }
@@ -463,18 +466,21 @@ extern "C" int issm_b200_glue_bwd(const issm_glue_params* p, void* stream) {
   // 16-byte copies of the gradient rows and the mask need every row of states to start on a 16-byte boundary
   const int vec_ok = !((p->nstates * es) % 16) && !(p->nstates % 4) && !((uintptr_t)p->ddt % 16) && !((uintptr_t)p->dbc % 16) &&
                      !((uintptr_t)p->mask % 16);
-#define GLUE_BWD(TT, MM)                                                                              \
+#define GLUE_BWD(TD, TT, MM)                                                                          \
   do {                                                                                                \
-    const size_t dyn = 2 * GlueStage<TT, MM>::bytes(a.RO);                                            \
+    const size_t dyn = 2 * GlueStage<TD, TT, MM>::bytes(a.RO);                                        \
     struct Tag {};                                                                                    \
-    if (int rc2 = SmemAttrOnce<Tag>::set(k_glue_bwd<TT, MM>, 2 * GlueStage<TT, MM>::bytes(GLUE_MAX_ROWS + 8))) return rc2; \
-    ISSM_LAUNCH((k_glue_bwd<TT, MM>), blocks, 128, dyn, s, a, npoints, vec_ok);                       \
+    if (int rc2 = SmemAttrOnce<Tag>::set(k_glue_bwd<TD, TT, MM>, 2 * GlueStage<TD, TT, MM>::bytes(GLUE_MAX_ROWS + 8))) return rc2; \
+    ISSM_LAUNCH((k_glue_bwd<TD, TT, MM>), blocks, 128, dyn, s, a, npoints, vec_ok);                   \
   } while (0)
-  if (p->io_dtype == ISSM_F32) {
-    if (p->nfeat == 16) GLUE_BWD(float, 16); else if (p->nfeat == 8) GLUE_BWD(float, 8); else GLUE_BWD(float, 4);
-  } else {
-    if (p->nfeat == 16) GLUE_BWD(bf16, 16); else if (p->nfeat == 8) GLUE_BWD(bf16, 8); else GLUE_BWD(bf16, 4);
-  }
+#define GLUE_BWD_M(TD, TT)                                                                            \
+  do {                                                                                                \
+    if (p->nfeat == 16) GLUE_BWD(TD, TT, 16); else if (p->nfeat == 8) GLUE_BWD(TD, TT, 8); else GLUE_BWD(TD, TT, 4); \
+  } while (0)
+  if (p->io_dtype == ISSM_F32) GLUE_BWD_M(float, float);
+  else if (p->dist_dtype == ISSM_F32) GLUE_BWD_M(float, bf16);
+  else GLUE_BWD_M(bf16, bf16);
+#undef GLUE_BWD_M
 #undef GLUE_BWD
   const int n = a.RW * p->nfeat;
   ISSM_LAUNCH(k_glue_reduce, (n + 31) / 32, dim3(32, 8), 0, s, a.dwpart, blocks, GLUE_MAX_ROWS * p->nfeat, n, p->dweight);

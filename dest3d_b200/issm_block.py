@@ -66,8 +66,9 @@ class MultiHeadISSMScan(nn.Module):
         initial_states = initial_states.reshape(bsz, K, H, P).permute(0, 2, 3, 1)           # b l (h hd) -> b h hd l
         A = (-torch.exp(self.A_log.float()))[:, None].expand(H, self.d_state)
         # dt, B, C (and the second direction's B, C) in the scan's layouts, in the activations' dtype
-        outs = adaptive_dt_bc(dist.to(x.dtype), self.dt_proj.weight, self.bc_proj.weight, dt_tok, self.dt_bias, b_bias, c_bias,
-                              back[1], back[2], mask)
+        feats = dist if (dist.dtype == x.dtype or (dist.dtype == torch.float32 and x.dtype == torch.bfloat16)) else dist.to(x.dtype)
+        outs = adaptive_dt_bc(feats, self.dt_proj.weight, self.bc_proj.weight, dt_tok, self.dt_bias, b_bias, c_bias,
+                              back[1], back[2], mask, out_dtype=x.dtype)
         kw = {} if self.dt_limit == (0.0, float("inf")) else dict(dt_limit=self.dt_limit)
         heads = lambda t: t.reshape(t.shape[0], t.shape[1], H, P)
         if self.use_biscan:

@@ -227,7 +227,8 @@ int issm_b200_dwconv7_silu_bwd(const issm_conv_params* p, void* cuda_stream);
 typedef struct issm_glue_params {
   int32_t batch, seqlen, nstates, nfeat;  /* nfeat = 4, 8 or 16 */
   int32_t nheads, ngroups, has_back;
-  int32_t io_dtype;                       /* dist, dt, bc, ddt, dbc, ddist, grow */
+  int32_t io_dtype;                       /* dt, bc, ddt, dbc */
+  int32_t dist_dtype;                     /* dist, ddist: io_dtype, or ISSM_F32 next to ISSM_BF16 outputs (float features, bfloat16 activations) */
   const void* dist; int64_t dist_sb, dist_sl, dist_sk;   /* element strides; feature stride 1; 16-byte aligned rows */
   const float* weight;                    /* (nheads + 2 ngroups, nfeat) */
   const float* tok;

@@ -78,3 +78,37 @@ def test_outputs_feed_the_scan_without_copies():
     y = ISSM_chunk_scan_combined(x, dt, A, B, C, 64, path="tensor")
     y2 = ISSM_chunk_scan_combined(x, dt, A, B.contiguous(), C.contiguous(), 64, path="tensor")
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("b,L,K,M,H,G,back", [(2, 37, 256, 16, 8, 1, True), (1, 9, 130, 8, 2, 2, False), (1, 300, 256, 4, 4, 1, True)])
+def test_float_features_with_bfloat16_outputs(b, L, K, M, H, G, back):
+    """What autocast hands the block: dist stays float32, dt / B / C come out in bfloat16, ddist goes back in float32."""
+    from dest3d_b200.adaptive_params import adaptive_dt_bc
+    g = torch.Generator().manual_seed(L + K)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    host = dict(dist=rn(b, L, K, M), w_dt=rn(H, M) * 0.3, w_bc=rn(2 * G, M) * 0.3, dt_tok=rn(b, L, H).bfloat16(), dt_bias=rn(H) - 2.0,
+                b_bias=rn(b, L, G).bfloat16(), c_bias=rn(b, L, G).bfloat16())
+    if back:
+        host.update(b_back=rn(b, L, G).bfloat16(), c_back=rn(b, L, G).bfloat16())
+    m = (torch.rand(b, L, K, generator=g) > 0.3).float()
+    dev = {k: v.cuda().requires_grad_() for k, v in host.items()}
+    got = adaptive_dt_bc(dev["dist"], dev["w_dt"], dev["w_bc"], dev["dt_tok"], dev["dt_bias"], dev["b_bias"], dev["c_bias"],
+                         dev.get("b_back"), dev.get("c_back"), m.cuda(), out_dtype=torch.bfloat16)
+    assert all(o.dtype == torch.bfloat16 for o in got)
+    r = {k: v.double().requires_grad_() for k, v in host.items()}
+    ref = _reference(r["dist"], r["w_dt"], r["w_bc"], r["dt_tok"], r["dt_bias"], r["b_bias"], r["c_bias"], r.get("b_back"), r.get("c_back"), m, G)
+    douts = [rn(*o.shape) for o in ref]
+    for o, want in zip(got, ref):
+        torch.testing.assert_close(o.double().cpu(), want.detach(), rtol=2e-2, atol=2e-2)
+    sum((o.float() * d.cuda()).sum() for o, d in zip(got, douts)).backward()
+    sum((o * d.double()).sum() for o, d in zip(ref, douts)).backward()
+    assert dev["dist"].grad.dtype == torch.float32
+    # the incoming gradients are rounded to bfloat16 on their way into the kernel; everything else is float32
+    torch.testing.assert_close(dev["dist"].grad.double().cpu(), r["dist"].grad, rtol=2e-2, atol=2e-2)
+    for k in host:
+        if k != "dist":
+            want = r[k].grad
+            assert (dev[k].grad.double().cpu() - want).abs().max().item() <= 3e-2 * (want.abs().max().item() + 1e-6), k
+    with pytest.raises(TypeError):
+        adaptive_dt_bc(dev["dist"].detach().bfloat16(), dev["w_dt"], dev["w_bc"], dev["dt_tok"], dev["dt_bias"], dev["b_bias"], dev["c_bias"],
+                       out_dtype=torch.float32)
