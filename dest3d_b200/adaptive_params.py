@@ -53,11 +53,18 @@ class AdaptiveDtBcFn(torch.autograd.Function):
             raise _lib.IssmError(rc, "issm_b200_glue_fwd")
         ctx.save_for_backward(dist, w, tokf, maskf)
         ctx.meta = (H, G, back, w_dt.dtype, w_bc.dtype, tok.dtype, out_dtype)
-        return dt, bc
+        # B, C (and the second direction's) go out as separate views of the one buffer, so that their gradients come back
+        # one by one and are joined by ONE concatenation (slicing a single output would cost a zero fill and an add each)
+        return (dt,) + tuple(bc[:, :, i * G:(i + 1) * G] for i in range(nb // G))
 
     @staticmethod
-    def backward(ctx, ddt, dbc):
+    def backward(ctx, ddt, *dparts):
         dist, w, tokf, maskf = ctx.saved_tensors
+        dbc = None
+        if any(g is not None for g in dparts):
+            shape = next(g for g in dparts if g is not None).shape
+            dbc = torch.cat([g if g is not None else torch.zeros(shape, dtype=ctx.meta[6], device=dist.device) for g in
+                             (gg if gg is None else gg.to(ctx.meta[6]) for gg in dparts)], dim=2)
         H, G, back, wdt_t, wbc_t, tok_t, out_dtype = ctx.meta
         b, L, K, M = dist.shape
         RW = H + 2 * G
@@ -96,8 +103,4 @@ def adaptive_dt_bc(dist, dt_proj_weight, bc_proj_weight, dt_bias_tok, dt_bias, b
     tok = torch.cat(terms, dim=-1)
     if mask is not None and mask.dtype == torch.bool:
         mask = (~mask).float()
-    dt, bc = AdaptiveDtBcFn.apply(dist, dt_proj_weight, bc_proj_weight, tok, mask, H, G, back, out_dtype or dist.dtype)
-    parts = [dt, bc[:, :, 0:G], bc[:, :, G:2 * G]]
-    if back:
-        parts += [bc[:, :, 2 * G:3 * G], bc[:, :, 3 * G:4 * G]]
-    return tuple(parts)
+    return AdaptiveDtBcFn.apply(dist, dt_proj_weight, bc_proj_weight, tok, mask, H, G, back, out_dtype or dist.dtype)
