@@ -66,6 +66,7 @@ def main():
                 ok, oq = mod(in_key, in_query, dist, xyz, mask)
             ((ok.float() * gk).sum() + (oq.float() * gq).sum()).backward()
             mod.zero_grad(set_to_none=True)
+            in_key.grad = in_query.grad = dist.grad = None     # assigned, not accumulated, in the next step
         return run
 
     out = {"batch": b, "points": L, "states": K, "d_model": d_model, "dtype": "bf16 autocast",

@@ -187,7 +187,10 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
   __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
   __shared__ float sred[4][GLUE_MAX_ROWS + 8];
   __shared__ float sg[GLUE_MAX_ROWS][GLUE_KT + 1];
-  __shared__ __align__(16) float sd[GLUE_KT][M + 4];         // rows 16 bytes apart from a power of two: 128-bit accesses without conflicts
+  // float copy of the tile's features for the weight gradient (rows 16 bytes apart from a power of two: 128-bit accesses
+  // without conflicts); float features are read from the stage itself
+  constexpr bool kCopy = sizeof(TD) != 4;
+  __shared__ __align__(16) float sd[kCopy ? GLUE_KT : 1][M + 4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < a.RW * M; i += blockDim.x) sw[i] = a.w[i];
   // weight gradient: thread = (row r, four features 4 jq .. 4 jq + 3, one of NKG ranges of the tile's states)
@@ -262,10 +265,12 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
       float2 dp[M], dd[M];
 #pragma unroll
       for (int j = 0; j < M; ++j) { dp[j] = make_float2(d0[j], d1[j]); dd[j] = make_float2(0.f, 0.f); }
+      if constexpr (kCopy) {
 #pragma unroll
-      for (int c = 0; c < M / 4; ++c) {
-        *(float4*)&sd[kk][c * 4] = make_float4(d0[c * 4], d0[c * 4 + 1], d0[c * 4 + 2], d0[c * 4 + 3]);
-        *(float4*)&sd[kk + 1][c * 4] = make_float4(d1[c * 4], d1[c * 4 + 1], d1[c * 4 + 2], d1[c * 4 + 3]);
+        for (int c = 0; c < M / 4; ++c) {
+          *(float4*)&sd[kk][c * 4] = make_float4(d0[c * 4], d0[c * 4 + 1], d0[c * 4 + 2], d0[c * 4 + 3]);
+          *(float4*)&sd[kk + 1][c * 4] = make_float4(d1[c * 4], d1[c * 4 + 1], d1[c * 4 + 2], d1[c * 4 + 3]);
+        }
       }
       const float2 inm = make_float2(in0 ? 1.f : 0.f, in1 ? 1.f : 0.f);
       float2 mk = inm;
@@ -326,11 +331,13 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
     }
     __syncthreads();
     if (kg < NKG) {
-      const int k1 = min(GLUE_KT, (kg + 1) * kspan);
+      const int k1 = min(min(GLUE_KT, a.K - k0), (kg + 1) * kspan);   // states of the tile that exist (the stage holds nothing valid beyond)
 #pragma unroll 4
       for (int kk = kg * kspan; kk < k1; ++kk) {
         const float g = sg[wr][kk];
-        const float4 f = *(const float4*)&sd[kk][wj];
+        float4 f;
+        if constexpr (kCopy) f = *(const float4*)&sd[kk][wj];
+        else f = *(const float4*)((const float*)st.dist(kk) + wj);
         wacc[0] = fmaf(g, f.x, wacc[0]); wacc[1] = fmaf(g, f.y, wacc[1]);
         wacc[2] = fmaf(g, f.z, wacc[2]); wacc[3] = fmaf(g, f.w, wacc[3]);
       }
