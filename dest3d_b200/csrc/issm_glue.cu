@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
   auto stage_of = [&](int it) { return GlueStage<TD, T, M>{glue_dyn + (it & 1) * stage_bytes, a.RO}; };
   __shared__ __align__(16) float sw[GLUE_MAX_ROWS * M];
   __shared__ float sred[4][GLUE_MAX_ROWS + 8];
-  __shared__ float sg[GLUE_MAX_ROWS][GLUE_KT + 1];
+  __shared__ __align__(16) float sg[GLUE_MAX_ROWS][GLUE_KT + 4];   // g of the tile, read four states at a time
   // float copy of the tile's features for the weight gradient (rows 16 bytes apart from a power of two: 128-bit accesses
   // without conflicts); float features are read from the stage itself
   constexpr bool kCopy = sizeof(TD) != 4;
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
   const int tiles = a.RW * JQ, NKG = 128 / tiles > 0 ? 128 / tiles : 1;
   const int tile = threadIdx.x % tiles, kg = threadIdx.x / tiles;
   const int wr = tile / JQ, wj = (tile % JQ) * 4;
-  const int kspan = (GLUE_KT + NKG - 1) / NKG;
+  const int kspan = ((GLUE_KT + NKG - 1) / NKG + 3) & ~3;  // a multiple of four states
   float wacc[4] = {0.f, 0.f, 0.f, 0.f};
   const int ntile = (a.K + GLUE_KT - 1) / GLUE_KT;
   const int my_points = blockIdx.x < npoints ? (npoints - blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -271,6 +271,12 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
           *(float4*)&sd[kk][c * 4] = make_float4(d0[c * 4], d0[c * 4 + 1], d0[c * 4 + 2], d0[c * 4 + 3]);
           *(float4*)&sd[kk + 1][c * 4] = make_float4(d1[c * 4], d1[c * 4 + 1], d1[c * 4 + 2], d1[c * 4 + 3]);
         }
+      } else {                                             // rows of the stage beyond the last state: zero, not stale
+#pragma unroll
+        for (int c = 0; c < M / 4; ++c) {
+          if (!in0) *(float4*)((float*)st.dist(kk) + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (!in1) *(float4*)((float*)st.dist(kk + 1) + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
       const float2 inm = make_float2(in0 ? 1.f : 0.f, in1 ? 1.f : 0.f);
       float2 mk = inm;
@@ -285,16 +291,18 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
       for (int r = 0; r < GLUE_MAX_ROWS; ++r) {
         if (r < a.RW) {
           float2 g = make_float2(0.f, 0.f);
+          float4 wrow[M / 4];                              // the row's weights: read once, used for pre and for ddist
+#pragma unroll
+          for (int c = 0; c < M / 4; ++c) wrow[c] = *(const float4*)&sw[r * M + c * 4];
           if (r < a.H) {
             if (a.ddt) {
               float2 pre = make_float2(st.tok()[r], st.tok()[r]);
 #pragma unroll
               for (int c = 0; c < M / 4; ++c) {
-                const float4 w4 = *(const float4*)&sw[r * M + c * 4];
-                pre = __ffma2_rn(dp[c * 4], make_float2(w4.x, w4.x), pre);
-                pre = __ffma2_rn(dp[c * 4 + 1], make_float2(w4.y, w4.y), pre);
-                pre = __ffma2_rn(dp[c * 4 + 2], make_float2(w4.z, w4.z), pre);
-                pre = __ffma2_rn(dp[c * 4 + 3], make_float2(w4.w, w4.w), pre);
+                pre = __ffma2_rn(dp[c * 4], make_float2(wrow[c].x, wrow[c].x), pre);
+                pre = __ffma2_rn(dp[c * 4 + 1], make_float2(wrow[c].y, wrow[c].y), pre);
+                pre = __ffma2_rn(dp[c * 4 + 2], make_float2(wrow[c].z, wrow[c].z), pre);
+                pre = __ffma2_rn(dp[c * 4 + 3], make_float2(wrow[c].w, wrow[c].w), pre);
               }
               const float2 sg2 = make_float2(pre.x <= 20.f ? glue_sigmoid(pre.x) : 1.f, pre.y <= 20.f ? glue_sigmoid(pre.y) : 1.f);
               g = __fmul2_rn(__fmul2_rn(get(r), mk), sg2);
@@ -304,15 +312,13 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
             g = get(r);
             if (a.back) g = __fadd2_rn(g, get(r + 2 * a.G));   // both directions share the weight row
           }
-          sg[r][kk] = g.x;
-          sg[r][kk + 1] = g.y;
+          *(float2*)&sg[r][kk] = g;
 #pragma unroll
           for (int c = 0; c < M / 4; ++c) {
-            const float4 w4 = *(const float4*)&sw[r * M + c * 4];
-            dd[c * 4] = __ffma2_rn(g, make_float2(w4.x, w4.x), dd[c * 4]);
-            dd[c * 4 + 1] = __ffma2_rn(g, make_float2(w4.y, w4.y), dd[c * 4 + 1]);
-            dd[c * 4 + 2] = __ffma2_rn(g, make_float2(w4.z, w4.z), dd[c * 4 + 2]);
-            dd[c * 4 + 3] = __ffma2_rn(g, make_float2(w4.w, w4.w), dd[c * 4 + 3]);
+            dd[c * 4] = __ffma2_rn(g, make_float2(wrow[c].x, wrow[c].x), dd[c * 4]);
+            dd[c * 4 + 1] = __ffma2_rn(g, make_float2(wrow[c].y, wrow[c].y), dd[c * 4 + 1]);
+            dd[c * 4 + 2] = __ffma2_rn(g, make_float2(wrow[c].z, wrow[c].z), dd[c * 4 + 2]);
+            dd[c * 4 + 3] = __ffma2_rn(g, make_float2(wrow[c].w, wrow[c].w), dd[c * 4 + 3]);
           }
         }
       }
@@ -331,15 +337,19 @@ __global__ void __launch_bounds__(128) k_glue_bwd(GlueArgs a, int npoints, int v
     }
     __syncthreads();
     if (kg < NKG) {
-      const int k1 = min(min(GLUE_KT, a.K - k0), (kg + 1) * kspan);   // states of the tile that exist (the stage holds nothing valid beyond)
-#pragma unroll 4
-      for (int kk = kg * kspan; kk < k1; ++kk) {
-        const float g = sg[wr][kk];
-        float4 f;
-        if constexpr (kCopy) f = *(const float4*)&sd[kk][wj];
-        else f = *(const float4*)((const float*)st.dist(kk) + wj);
-        wacc[0] = fmaf(g, f.x, wacc[0]); wacc[1] = fmaf(g, f.y, wacc[1]);
-        wacc[2] = fmaf(g, f.z, wacc[2]); wacc[3] = fmaf(g, f.w, wacc[3]);
+      const int k1 = min(GLUE_KT, (kg + 1) * kspan);       // rows beyond the last state hold g = 0 and zero features
+#pragma unroll 2
+      for (int kk = kg * kspan; kk < k1; kk += 4) {
+        const float4 g4 = *(const float4*)&sg[wr][kk];
+        const float gs[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float4 f;
+          if constexpr (kCopy) f = *(const float4*)&sd[kk + i][wj];
+          else f = *(const float4*)((const float*)st.dist(kk + i) + wj);
+          wacc[0] = fmaf(gs[i], f.x, wacc[0]); wacc[1] = fmaf(gs[i], f.y, wacc[1]);
+          wacc[2] = fmaf(gs[i], f.z, wacc[2]); wacc[3] = fmaf(gs[i], f.w, wacc[3]);
+        }
       }
     }
     if (k0 + GLUE_KT >= a.K) {
