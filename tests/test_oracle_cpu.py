@@ -126,3 +126,28 @@ def test_reference_arithmetic_in_the_unbounded_dt_regime():
     r64 = parity.oracle_run(inp, 64, opts, torch.float64)
     r = parity.oracle_run(inp, 64, dict(opts, scan_kw=dict(operand_rounding=torch.bfloat16)), torch.float32)
     parity.compare(r, r64, torch.bfloat16)
+
+
+def test_pointops_oracle_matches_the_reference_fixture():
+    """oracle/pointops_oracle.py against outputs of the reference's own PointLiteConv, Serialization gather and of the dt /
+    B / C lines of MultiHeadISSMScan.forward (tests/golden/make_golden_pointops.py), float64."""
+    import numpy as np
+    from oracle import pointops_oracle as P
+    g = {k: torch.from_numpy(v) for k, v in np.load(os.path.join(os.path.dirname(__file__), "golden", "pointops_golden.npz")).items()}
+    tol = dict(rtol=1e-12, atol=1e-13)
+    x, w, b = (g[k].clone().requires_grad_() for k in ("conv_x", "conv_w", "conv_b"))
+    y = P.point_lite_conv(x, w, b)
+    torch.testing.assert_close(y.detach(), g["conv_y"], **tol)
+    for got, want in zip(torch.autograd.grad(y, (x, w, b), g["conv_dy"]), (g["conv_dx"], g["conv_dw"], g["conv_db"])):
+        torch.testing.assert_close(got, want, **tol)
+    assert torch.equal(P.reorder_points(g["gather_points"], g["gather_index"]), g["gather_out"])
+    assert torch.equal(P.reorder_points(g["gather_out"], g["gather_inverse"]), g["gather_points"])
+    outs = P.adaptive_dt_bc(g["glue_dist"], g["glue_w_dt"], g["glue_w_bc"], g["glue_dt_tok"], g["glue_dt_bias"], g["glue_b_bias"],
+                            g["glue_c_bias"], g["glue_b_back"], g["glue_c_back"], g["glue_mask"])
+    for got, name in zip(outs, ("glue_dt", "glue_B", "glue_C", "glue_B_back", "glue_C_back")):
+        torch.testing.assert_close(got, g[name], **tol)
+    # the bool-mask branch (models/dest_module.py:558-559) against the float one with the complementary mask
+    keep = g["glue_mask"] > 0
+    dt_bool = P.adaptive_dt_bc(g["glue_dist"], g["glue_w_dt"], g["glue_w_bc"], g["glue_dt_tok"], g["glue_dt_bias"], g["glue_b_bias"],
+                               g["glue_c_bias"], mask=~keep)[0]
+    torch.testing.assert_close(dt_bool, g["glue_dt"], **tol)
